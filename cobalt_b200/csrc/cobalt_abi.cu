@@ -1,0 +1,336 @@
+// C ABI of libcobalt_b200.so: argument validation, launch configuration, kernel launches.
+// See include/cobalt_b200.h for the contract of every entry point.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "walk_kernels.cuh"
+#include "gemv_kernel.cuh"
+#include "gemm_kernel.cuh"
+
+using namespace cb;
+
+namespace {
+
+constexpr size_t SMEM_LIMIT = 227 * 1024;
+constexpr int MAX_DEVICES = 64;
+
+int g_num_sms[MAX_DEVICES];
+int g_cc_major[MAX_DEVICES];
+bool g_dev_known[MAX_DEVICES];
+int g_tune_tiles_per_split = 0;     // 0 = heuristic
+int g_tune_gemv_stages = 0;
+int g_tune_gemm_stages = 0;
+
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int device_info(int* num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return COBALT_ELAUNCH;
+    if (dev < 0 || dev >= MAX_DEVICES) return COBALT_EINVAL;
+    if (!g_dev_known[dev]) {
+        if (cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return COBALT_ELAUNCH;
+        if (cudaDeviceGetAttribute(&g_cc_major[dev], cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return COBALT_ELAUNCH;
+        g_dev_known[dev] = true;
+    }
+    if (g_cc_major[dev] != 10) return COBALT_EARCH;
+    *num_sms = g_num_sms[dev];
+    return COBALT_OK;
+}
+
+int check_mat(const CobaltMat* w) {
+    if (!w || !w->tiles || !w->tile_off) return COBALT_EINVAL;
+    if (w->K <= 0 || w->N <= 0 || w->N % GROUP != 0 || w->group != GROUP) return COBALT_EINVAL;
+    if (w->bits < 2 || w->bits > 4) return COBALT_EINVAL;
+    if (w->n_row_blocks != (w->K + TILE_ROWS - 1) / TILE_ROWS) return COBALT_EINVAL;
+    if (w->n_col_tiles != (w->N / GROUP + TILE_GROUPS - 1) / TILE_GROUPS) return COBALT_EINVAL;
+    if (((uintptr_t)w->tiles & 15) || ((uintptr_t)w->tile_off & 3)) return COBALT_EINVAL;
+    if (w->max_tile_bytes < 320 || (w->max_tile_bytes & 15)) return COBALT_EINVAL;
+    if (w->max_tile_bytes > TILE_ROWS * TILE_GROUPS * 20 + TILE_ROWS * TILE_GROUPS * GROUP * 4 / 8 + 16) return COBALT_EINVAL;
+    return COBALT_OK;
+}
+
+int check_io(const void* x, int64_t ldx, const void* y, int64_t ldy, int M, int K, int N) {
+    if (!x || !y || M <= 0) return COBALT_EINVAL;
+    if (ldx < N || ldy < K) return COBALT_EINVAL;
+    if (((uintptr_t)x & 15) || (ldx & 7)) return COBALT_EINVAL;       // 16-byte vector loads of x
+    if ((uintptr_t)y & 1) return COBALT_EINVAL;
+    return COBALT_OK;
+}
+
+// ----------------------------------------------------------------------------- GEMV configuration
+struct GemvCfg {
+    int splits, tps, stages, mt, grid;
+    uint32_t slot, nib;
+    size_t smem, counters_off, partials_off, total;
+};
+
+uint32_t nibble_bytes(const CobaltMat* w) {
+    if (w->bits == 4) return 0;
+    // upper bound on survivors of one tile from its byte size, 4 bits each, plus read-ahead slack
+    return (uint32_t)round_up((size_t)w->max_tile_bytes * 4 / w->bits + 64, 128);
+}
+
+int gemv_config(const CobaltMat* w, int M, int num_sms, GemvCfg* c) {
+    const int RB = w->n_row_blocks, CT = w->n_col_tiles;
+    c->mt = M > 8 ? 2 : 1;
+    c->slot = (uint32_t)round_up((size_t)w->max_tile_bytes + 32, 128);
+    c->nib = nibble_bytes(w);
+    const size_t fixed = GEMV_LUT_BYTES + GEMV_BAR_BYTES + 64;
+    int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : GEMV_MAX_STAGES;
+    if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
+    while (stages > 1 && fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) --stages;
+    if (fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) return COBALT_EINVAL;
+    c->stages = stages;
+    c->smem = fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib);
+    const long capacity = (long)num_sms * GEMV_WARPS;
+    const long tiles = (long)RB * CT;
+    long tps = g_tune_tiles_per_split > 0 ? g_tune_tiles_per_split : (tiles + capacity / 2) / capacity;
+    if (tps < 1) tps = 1;
+    if (tps > CT) tps = CT;
+    if (tps > 31) tps = 31;
+    c->tps = (int)tps;
+    c->splits = (CT + c->tps - 1) / c->tps;
+    c->grid = (RB * c->splits + GEMV_WARPS - 1) / GEMV_WARPS;
+    c->counters_off = SCRATCH_STATUS_BYTES;
+    c->partials_off = c->counters_off + round_up((size_t)RB * 4, 256);
+    c->total = c->partials_off + (c->splits > 1 ? (size_t)RB * c->splits * 4 * c->mt * 32 * sizeof(float) : 0);
+    return COBALT_OK;
+}
+
+template <int BITS, int MT>
+int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
+    static bool configured[MAX_DEVICES];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(gemv_mma_kernel<BITS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
+            return COBALT_ELAUNCH;
+        configured[dev] = true;
+    }
+    gemv_mma_kernel<BITS, MT><<<c.grid, GEMV_THREADS, c.smem, st>>>(P);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+// ----------------------------------------------------------------------------- GEMM configuration
+struct GemmCfg {
+    int stages;
+    uint32_t slot, nib;
+    size_t smem;
+};
+
+int gemm_config(const CobaltMat* w, GemmCfg* c) {
+    c->slot = (uint32_t)round_up((size_t)w->max_tile_bytes + 32, 128);
+    c->nib = nibble_bytes(w);
+    const size_t ring = (size_t)2 * GEMM_RB * (c->slot + c->nib) + 64;
+    int stages = g_tune_gemm_stages > 0 ? g_tune_gemm_stages : 4;
+    if (stages > 4) stages = 4;
+    while (stages > 2 && (size_t)stages * (GEMM_A_BYTES + GEMM_B_BYTES) + GEMM_LUT_BYTES + GEMM_BAR_BYTES + ring + 1024 > SMEM_LIMIT) --stages;
+    c->smem = (size_t)stages * (GEMM_A_BYTES + GEMM_B_BYTES) + GEMM_LUT_BYTES + GEMM_BAR_BYTES + ring + 1024;
+    if (c->smem > SMEM_LIMIT) return COBALT_EINVAL;
+    c->stages = stages;
+    return COBALT_OK;
+}
+
+template <int BITS>
+int launch_gemm(const GemmParams& P, const GemmCfg& c, dim3 grid, cudaStream_t st) {
+    static bool configured[MAX_DEVICES];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
+            return COBALT_ELAUNCH;
+        configured[dev] = true;
+    }
+    gemm_tcgen05_kernel<BITS><<<grid, GEMM_THREADS, c.smem, st>>>(P);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cobalt_version(void) { return (1 << 16) | 0; }
+
+const char* cobalt_strerror(int status) {
+    switch (status) {
+        case COBALT_OK: return "ok";
+        case COBALT_EINVAL: return "invalid argument (null pointer, shape, alignment or bit width)";
+        case COBALT_ESCRATCH: return "scratch buffer missing, misaligned or too small";
+        case COBALT_ELAUNCH: return "CUDA runtime or launch error";
+        case COBALT_EARCH: return "device is not compute capability 10.x (B200)";
+        case COBALT_ETIMEOUT: return "a bounded device-side wait expired";
+        case COBALT_ETOOBIG: return "size exceeds the stated maximum of this entry point";
+        default: return "unknown status";
+    }
+}
+
+// Tuning hook for benchmarks: key 0 = GEMV tiles per split, 1 = GEMV ring stages, 2 = GEMM operand
+// stages; value 0 restores the heuristic.  Not part of the stable contract.
+int cobalt_set_tuning(int key, int value) {
+    if (value < 0) return COBALT_EINVAL;
+    switch (key) {
+        case 0: g_tune_tiles_per_split = value; return COBALT_OK;
+        case 1: g_tune_gemv_stages = value; return COBALT_OK;
+        case 2: g_tune_gemm_stages = value; return COBALT_OK;
+        default: return COBALT_EINVAL;
+    }
+}
+
+size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M) {
+    int sms = 0;
+    if (check_mat(w) != COBALT_OK || M <= 0 || M > MAX_GEMV_M) return 0;
+    if (device_info(&sms) != COBALT_OK) return 0;
+    GemvCfg c;
+    if (gemv_config(w, M, sms, &c) != COBALT_OK) return 0;
+    return c.total;
+}
+
+int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+                void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (M > MAX_GEMV_M) return COBALT_EINVAL;
+    rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    GemvCfg c;
+    rc = gemv_config(w, M, sms, &c);
+    if (rc) return rc;
+    if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
+    GemvParams P;
+    P.W = make_view(w);
+    P.x = (const uint16_t*)x; P.ldx = ldx;
+    P.y = (uint16_t*)y; P.ldy = ldy;
+    P.bias = (const uint16_t*)bias;
+    P.M = M;
+    P.splits = c.splits; P.tiles_per_split = c.tps; P.stages = c.stages;
+    P.slot_bytes = c.slot; P.nib_bytes = c.nib;
+    P.status = (uint32_t*)scratch;
+    P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
+    P.partials = (float*)((uint8_t*)scratch + c.partials_off);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (c.mt == 1) {
+        switch (w->bits) {
+            case 2: return launch_gemv<2, 1>(P, c, st);
+            case 3: return launch_gemv<3, 1>(P, c, st);
+            default: return launch_gemv<4, 1>(P, c, st);
+        }
+    }
+    switch (w->bits) {
+        case 2: return launch_gemv<2, 2>(P, c, st);
+        case 3: return launch_gemv<3, 2>(P, c, st);
+        default: return launch_gemv<4, 2>(P, c, st);
+    }
+}
+
+int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+                        void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (M > MAX_GEMV_M) return COBALT_EINVAL;
+    rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    MatView V = make_view(w);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M <= 1)
+        gemv_rowwalk_kernel<1><<<V.RB, 64, 0, st>>>(V, (const uint16_t*)x, ldx, (uint16_t*)y, ldy, (const uint16_t*)bias, M);
+    else if (M <= 4)
+        gemv_rowwalk_kernel<4><<<V.RB, 64, 0, st>>>(V, (const uint16_t*)x, ldx, (uint16_t*)y, ldy, (const uint16_t*)bias, M);
+    else
+        gemv_rowwalk_kernel<16><<<V.RB, 64, 0, st>>>(V, (const uint16_t*)x, ldx, (uint16_t*)y, ldy, (const uint16_t*)bias, M);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+size_t cobalt_gemm_scratch_bytes(const CobaltMat* w, int M) {
+    if (check_mat(w) != COBALT_OK || M <= 0) return 0;
+    return SCRATCH_STATUS_BYTES;
+}
+
+int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+                void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < SCRATCH_STATUS_BYTES) return COBALT_ESCRATCH;
+    GemmCfg c;
+    rc = gemm_config(w, &c);
+    if (rc) return rc;
+    GemmParams P;
+    P.W = make_view(w);
+    P.x = (const uint16_t*)x; P.ldx = ldx;
+    P.y = (uint16_t*)y; P.ldy = ldy;
+    P.bias = (const uint16_t*)bias;
+    P.M = M;
+    P.stages = c.stages;
+    P.slot_bytes = c.slot; P.nib_bytes = c.nib;
+    P.status = (uint32_t*)scratch;
+    dim3 grid((unsigned)((w->n_row_blocks + GEMM_RB - 1) / GEMM_RB), (unsigned)((M + GEMM_MAX_NT - 1) / GEMM_MAX_NT));
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (w->bits) {
+        case 2: return launch_gemm<2>(P, c, grid, st);
+        case 3: return launch_gemm<3>(P, c, grid, st);
+        default: return launch_gemm<4>(P, c, grid, st);
+    }
+}
+
+int cobalt_dequant(const CobaltMat* w, void* w_bf16, void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (!w_bf16) return COBALT_EINVAL;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    MatView V = make_view(w);
+    unpack_kernel<<<dim3(V.CT, V.RB), 64, 0, (cudaStream_t)stream>>>(V, nullptr, nullptr, (uint16_t*)w_bf16);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+int cobalt_unpack(const CobaltMat* w, uint8_t* codes, uint8_t* keep, void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (!codes && !keep) return COBALT_EINVAL;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    MatView V = make_view(w);
+    unpack_kernel<<<dim3(V.CT, V.RB), 64, 0, (cudaStream_t)stream>>>(V, codes, keep, nullptr);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M, void* dev_x,
+                       void* dev_y, void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (!x_host || !y_host || !dev_x || !dev_y || M <= 0) return COBALT_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(dev_x, x_host, (size_t)M * w->N * 2, cudaMemcpyHostToDevice, st) != cudaSuccess) return COBALT_ELAUNCH;
+    if (M <= MAX_GEMV_M)
+        rc = cobalt_gemv(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, stream);
+    else
+        rc = cobalt_gemm(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, stream);
+    if (rc) return rc;
+    if (cudaMemcpyAsync(y_host, dev_y, (size_t)M * w->K * 2, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return COBALT_ELAUNCH;
+    return COBALT_OK;
+}
+
+int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out) {
+    if (!scratch || !status_out) return COBALT_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(status_out, scratch, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return COBALT_ELAUNCH;
+    return *status_out == 0 ? COBALT_OK : COBALT_ETIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,264 @@
+// Decode GEMV for M <= 16 tokens.
+//
+// Work item = (row block of 16 rows, range of column tiles), one item per warp.  Each warp
+// pulls its tiles with 1-D bulk async copies into a private shared-memory ring (mbarrier
+// completion), locates every segment's survivor codes with a popcount prefix sum over the
+// warp, expands them to dense bf16 weights in registers (decode_core.cuh) and contracts them
+// against the activations with mma.sync m16n8k16 (A = 16 rows x 16 columns of weights,
+// B = 16 columns x 8 tokens).  Lane (g = lane/4, t = lane%4) owns rows g and g+8 of the row
+// block and group t of the tile; in MMA step s it supplies columns 4s..4s+3 of that group, so
+// the 16 k-slots of one MMA are 4 consecutive columns from each of the tile's 4 groups and the
+// B fragment of the lane is simply 8 contiguous bytes of x.
+//
+// When a row block is split over several warps every warp stores its fp32 fragment to
+// scratch; the last one to arrive (per-row-block counter) adds the fragments in split order,
+// so the result does not depend on timing.
+//
+// Behaviour replaced: cbk::gemv_sparse / gemv_sparse_expand, one warp per row with a 32-lane
+// prefix scan per 1024-column window (src/cobaltkernel/csrc/cobalt_gemv.cuh:216-393).
+#pragma once
+#include "common.cuh"
+
+namespace cb {
+
+constexpr int GEMV_WARPS = 16;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_MAX_STAGES = 4;
+constexpr uint32_t GEMV_LUT_BYTES = LUT_ENTRIES * LUT_COPIES * 8;      // 32 KB
+constexpr uint32_t GEMV_BAR_BYTES = GEMV_WARPS * GEMV_MAX_STAGES * 8;  // 512 B
+
+struct GemvParams {
+    MatView W;
+    const uint16_t* x; int64_t ldx;
+    uint16_t* y; int64_t ldy;
+    const uint16_t* bias;
+    int M;
+    int splits, tiles_per_split, stages;
+    uint32_t slot_bytes, nib_bytes;
+    float* partials; uint32_t* counters; uint32_t* status;
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// bf16( bf16(acc) + bias ): the reference rounds the matmul result first and adds the bias after
+__device__ __forceinline__ uint16_t finish_output(float acc, const uint16_t* bias, int row) {
+    uint16_t r = float_to_bf16(acc);
+    if (bias) r = float_to_bf16(bf16_to_float(r) + bf16_to_float(bias[row]));
+    return r;
+}
+
+// nibble stream window of one 32-column word: 128 bits starting at nibble `nib_off`
+__device__ __forceinline__ void load_window(uint32_t cbase, uint32_t nib_off, uint32_t& w0, uint32_t& w1,
+                                            uint32_t& w2, uint32_t& w3) {
+    const uint32_t bitpos = nib_off * 4u;
+    const uint32_t a = cbase + (bitpos >> 5) * 4u;
+    const uint32_t r0 = lds32(a), r1 = lds32(a + 4), r2 = lds32(a + 8), r3 = lds32(a + 12), r4 = lds32(a + 16);
+    const uint32_t o = bitpos & 31u;
+    w0 = funnel_r(r0, r1, o); w1 = funnel_r(r1, r2, o); w2 = funnel_r(r2, r3, o); w3 = funnel_r(r3, r4, o);
+}
+
+template <int BITS, int MT>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvParams P) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const MatView& W = P.W;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t full = 0xFFFFFFFFu;
+
+    // ---- block set-up: barriers first, so that the first tiles are in flight while the
+    //      expansion table replicas are being written
+    LutEntry* lut_s = reinterpret_cast<LutEntry*>(smem);
+    const uint32_t bar0 = smem_u32(smem + GEMV_LUT_BYTES) + warp * GEMV_MAX_STAGES * 8;
+    if (lane == 0)
+        for (int s = 0; s < P.stages; ++s) mbar_init(bar0 + 8 * s, 1);
+    mbar_fence_init();
+    fence_proxy_async();
+    __syncthreads();
+
+    const int item = blockIdx.x * GEMV_WARPS + warp;
+    const bool has_work = item < W.RB * P.splits;
+    const int rb = has_work ? item / P.splits : 0, sp = has_work ? item % P.splits : 0;
+    const int ct0 = sp * P.tiles_per_split;
+    int ct1 = ct0 + P.tiles_per_split;
+    if (ct1 > W.CT) ct1 = W.CT;
+    const int n = has_work ? ct1 - ct0 : 0;                           // 1..31 tiles
+
+    const uint32_t per_warp = P.stages * P.slot_bytes + P.nib_bytes;
+    const uint32_t ring = smem_u32(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES) + warp * per_warp;
+    const uint32_t nib = ring + P.stages * P.slot_bytes;
+    const LutEntry* lut_lane = lut_s + (lane & (LUT_COPIES - 1));
+
+    // tile offsets of this warp's range, one per lane
+    const uint32_t my_off = (has_work && lane <= n) ? W.tile_off[rb * W.CT + ct0 + lane] : 0u;
+
+    auto issue = [&](int i) {                                          // all lanes call; lane 0 acts
+        const uint32_t o0 = __shfl_sync(full, my_off, i), o1 = __shfl_sync(full, my_off, i + 1);
+        if (lane == 0) {
+            const uint32_t bytes = (o1 - o0) * 16u;
+            const uint32_t bar = bar0 + 8 * (i % P.stages);
+            fence_proxy_async();
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_g2s(ring + (i % P.stages) * P.slot_bytes, W.tiles + (size_t)o0 * 16, bytes, bar);
+        }
+    };
+
+    int issued = n < P.stages ? n : P.stages;
+    for (int i = 0; i < issued; ++i) issue(i);
+
+    for (int i = threadIdx.x; i < LUT_ENTRIES * LUT_COPIES; i += GEMV_THREADS) lut_s[i] = g_lut.e[i / LUT_COPIES];
+    __syncthreads();
+    if (!has_work) return;
+
+    float acc[MT][4];
+#pragma unroll
+    for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+
+    bool healthy = true;
+    for (int i = 0; i < issued; ++i) {
+        const int st = i % P.stages;
+        const bool ok = mbar_wait_bounded(bar0 + 8 * st, (uint32_t)(i / P.stages) & 1u, P.status, DEV_TIMEOUT_TILE);
+        healthy = __all_sync(full, healthy && ok);
+        if (!healthy) continue;                                        // drain what is in flight, decode nothing
+
+        const int ct = ct0 + i;
+        const int w = tile_width(W, ct);
+        const bool active = t < w;
+        const uint32_t slot = ring + st * P.slot_bytes;
+        const int segA = g * w + t, segB = (g + 8) * w + t;
+        uint4 mA = make_uint4(0, 0, 0, 0), mB = make_uint4(0, 0, 0, 0);
+        uint32_t szA = 0, szB = 0;
+        if (active) {
+            mA = lds128(slot + segA * 16);
+            mB = lds128(slot + segB * 16);
+            szA = lds32(slot + TILE_ROWS * w * 16 + segA * 4);
+            szB = lds32(slot + TILE_ROWS * w * 16 + segB * 4);
+        }
+        const uint32_t cntA = __popc(mA.x) + __popc(mA.y) + __popc(mA.z) + __popc(mA.w);
+        const uint32_t cntB = __popc(mB.x) + __popc(mB.y) + __popc(mB.z) + __popc(mB.w);
+        const uint32_t v = cntA | (cntB << 16);
+        uint32_t inc = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(full, inc, d);
+            if (lane >= d) inc += up;
+        }
+        const uint32_t tot = __shfl_sync(full, inc, 31);
+        const uint32_t exc = inc - v;
+        uint32_t offA = exc & 0xFFFFu;                                 // in codes
+        uint32_t offB = (tot & 0xFFFFu) + (exc >> 16);
+
+        uint32_t cbase = slot + TILE_ROWS * w * 20;
+        if (BITS < 4) {                                                // re-pack the tile's codes as nibbles
+            const uint32_t total = (tot & 0xFFFFu) + (tot >> 16);
+            const uint32_t nchunks = (total + 7u) >> 3;
+            for (uint32_t c = lane; c < nchunks; c += 32) {
+                uint32_t outv;
+                if (BITS == 3) {
+                    const uint32_t bo = 3u * c, a = cbase + (bo & ~3u);
+                    outv = spread3(funnel_r(lds32(a), lds32(a + 4), (bo & 3u) * 8u) & 0x00FFFFFFu);
+                } else {
+                    outv = spread2(lds32(cbase + (c >> 1) * 4u) >> (16u * (c & 1u)));
+                }
+                sts32(nib + c * 4u, outv);
+            }
+            __syncwarp();
+            cbase = nib;
+        }
+
+        const SegParams pA = make_seg_params(szA, BITS, W.col_scale != nullptr);
+        const SegParams pB = make_seg_params(szB, BITS, W.col_scale != nullptr);
+        const int col0 = (ct * TILE_GROUPS + t) * GROUP;               // first column of this lane's group
+
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t mAj = mA.x, mBj = mB.x;                     // rotate instead of indexing registers
+            mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
+            mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
+            uint32_t ea[16], eb[16];
+            float cs[32];
+            const float* csp = nullptr;
+            if (W.col_scale != nullptr && active) {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) cs[q] = half_bits_to_float(W.col_scale[col0 + 32 * j + q]);
+                csp = cs;
+            }
+            {
+                uint32_t w0, w1, w2, w3;
+                load_window(cbase, offA, w0, w1, w2, w3);
+                decode32<LUT_COPIES>(mAj, w0, w1, w2, w3, pA, lut_lane, csp, ea);
+                load_window(cbase, offB, w0, w1, w2, w3);
+                decode32<LUT_COPIES>(mBj, w0, w1, w2, w3, pB, lut_lane, csp, eb);
+            }
+            offA += __popc(mAj);
+            offB += __popc(mBj);
+#pragma unroll
+            for (int b = 0; b < MT; ++b) {
+                const int tok = g + 8 * b;
+                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, x2 = x0, x3 = x0;
+                if (active && tok < P.M) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(P.x + (size_t)tok * P.ldx + col0 + 32 * j);
+                    x0 = __ldg(xp); x1 = __ldg(xp + 1); x2 = __ldg(xp + 2); x3 = __ldg(xp + 3);
+                }
+                mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], x0.x, x0.y);
+                mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], x0.z, x0.w);
+                mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], x1.x, x1.y);
+                mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], x1.z, x1.w);
+                mma_bf16_16816(acc[b], ea[8], eb[8], ea[9], eb[9], x2.x, x2.y);
+                mma_bf16_16816(acc[b], ea[10], eb[10], ea[11], eb[11], x2.z, x2.w);
+                mma_bf16_16816(acc[b], ea[12], eb[12], ea[13], eb[13], x3.x, x3.y);
+                mma_bf16_16816(acc[b], ea[14], eb[14], ea[15], eb[15], x3.z, x3.w);
+            }
+        }
+
+        __syncwarp();
+        if (issued < n) { issue(issued); ++issued; }
+    }
+    if (!healthy) return;
+
+    // ---- finish: direct store, or deterministic split reduction by the last arriver
+    const int row0 = rb * TILE_ROWS + g, row1 = row0 + 8;
+    if (P.splits > 1) {
+        float* mine = P.partials + (size_t)item * (4 * MT * 32);
+#pragma unroll
+        for (int b = 0; b < MT; ++b)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
+        __threadfence();
+        __syncwarp();
+        uint32_t old = 0;
+        if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
+        old = __shfl_sync(full, old, 0);
+        if (old != (uint32_t)(P.splits - 1)) return;
+        __threadfence();
+        const float* base = P.partials + (size_t)rb * P.splits * (4 * MT * 32);
+#pragma unroll
+        for (int b = 0; b < MT; ++b)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                float s = 0.0f;
+                for (int k = 0; k < P.splits; ++k) s += __ldcg(base + (size_t)k * (4 * MT * 32) + (b * 4 + r) * 32 + lane);
+                acc[b][r] = s;
+            }
+        if (lane == 0) P.counters[rb] = 0u;
+    }
+#pragma unroll
+    for (int b = 0; b < MT; ++b) {
+        const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
+        if (row0 < W.K) {
+            if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row0] = finish_output(acc[b][0], P.bias, row0);
+            if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row0] = finish_output(acc[b][1], P.bias, row0);
+        }
+        if (row1 < W.K) {
+            if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row1] = finish_output(acc[b][2], P.bias, row1);
+            if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row1] = finish_output(acc[b][3], P.bias, row1);
+        }
+    }
+}
+
+}  // namespace cb

@@ -1,0 +1,237 @@
+"""``CobaltSparseLinear``: drop-in for the reference's sparse-quant linear module.
+
+Same constructor as ``SparseQuantLinear(W_q, scales, zeros, mask, scale2, bias, meta)``
+(benchmarks/benchmark_suite.py:1175-1198, built at src/nosink.py:1353-1356) and the
+``from_linear`` / ``dequantize`` / ``state_dict`` / ``from_state_dict`` / ``extra_repr``
+conventions of ``CPRLinear`` (sinq/cprlinear.py:129-171, 292-330, 357-398, 400-544).
+
+The module keeps only the packed tile image on the device.  ``forward`` calls the CUDA
+library through its C ABI: the decode GEMV for up to 16 tokens, the tcgen05 GEMM above.
+There is no torch fallback: on a non-CUDA tensor ``forward`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .compress import SparseQuantConfig, compress_weight
+from .format import GROUP, TileImage, bytes_to_keep, pack_tiles
+
+GEMV_MAX_TOKENS = 16
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class CobaltSparseLinear(nn.Module):
+    """y = x @ dequant(W).T (+ bias), weights held as bitmask + low-bit survivors."""
+
+    def __init__(self, W_q, scales, zeros, mask, scale2=None, bias=None, meta=None):
+        super().__init__()
+        meta = dict(meta or {})
+        K, N = W_q.shape
+        bits = int(meta.get("nbits", meta.get("bits", 4)))
+        if int(meta.get("group_size", GROUP)) != GROUP:
+            raise ValueError(f"group_size must be {GROUP}")
+        img = pack_tiles(mask, W_q, scales.reshape(K, -1), zeros.reshape(K, -1), bits)
+        self._install(img, scale2, bias, meta)
+
+    # ------------------------------------------------------------------ construction
+    def _install(self, img: TileImage, scale2, bias, meta):
+        self.in_features = img.N
+        self.out_features = img.K
+        self.bits = img.bits
+        self.group_size = GROUP
+        self.meta = dict(meta or {})
+        self.meta.update(nbits=img.bits, group_size=GROUP, shape=(img.K, img.N))
+        self._img_meta = img.meta()
+        self.register_buffer("packed", img.blob)
+        has_scale2 = scale2 is not None and not bool((scale2.float() == 1).all())
+        self.register_buffer("scale2", scale2.reshape(-1).to(torch.float16).to(img.blob.device) if has_scale2 else None)
+        self.bias = nn.Parameter(bias.detach().clone(), requires_grad=False) if bias is not None else None
+        self._scratch = None
+        self._desc = None
+        self._desc_key = None
+
+    @classmethod
+    def _blank(cls):
+        obj = cls.__new__(cls)
+        nn.Module.__init__(obj)
+        return obj
+
+    @classmethod
+    def from_raw(cls, mask_u8, q_u8, scale_f16, zero_f16, col_scale=None, bits: int = 4, bias=None):
+        """Build from the RAW schema of src/cobaltkernel/quantize_cobalt.py:326-329
+        (``mask u8[K, N/8]`` LSB-first, ``q u8[K, N]``, ``scale/zero f16[K, G]``, ``col_scale f16[N]``)."""
+        K, N = q_u8.shape
+        keep = bytes_to_keep(mask_u8, N) if mask_u8.shape[1] * 8 == N and mask_u8.dtype == torch.uint8 and \
+            mask_u8.shape != q_u8.shape else (mask_u8 != 0)
+        obj = cls._blank()
+        obj._install(pack_tiles(keep, q_u8, scale_f16, zero_f16, bits), col_scale, bias,
+                     dict(nbits=bits, group_size=GROUP, shape=(K, N)))
+        return obj
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, act_norms: Optional[torch.Tensor] = None, bits: int = 4,
+                    sparsity: float = 0.5, beta: float = 0.5, group_size: int = GROUP):
+        """Compress an ``nn.Linear`` (mask + RTN run on the linear's device), then pack."""
+        cfg = SparseQuantConfig(bits=bits, sparsity=sparsity, beta=beta, group_size=group_size)
+        W = linear.weight.detach()
+        if act_norms is None:
+            act_norms = torch.ones(W.shape[1], device=W.device)
+        keep, q, scale, zero = compress_weight(W, act_norms.to(W.device), cfg)
+        obj = cls._blank()
+        obj._install(pack_tiles(keep, q, scale, zero, bits), None,
+                     None if linear.bias is None else linear.bias.detach().to(torch.bfloat16),
+                     dict(nbits=bits, group_size=group_size, shape=tuple(W.shape), sparsity=sparsity, beta=beta))
+        return obj
+
+    # ------------------------------------------------------------------ descriptors
+    def _descriptor(self) -> _lib.CobaltMat:
+        key = (self.packed.data_ptr(), None if self.scale2 is None else self.scale2.data_ptr())
+        if self._desc is None or self._desc_key != key:
+            m = self._img_meta
+            d = _lib.CobaltMat()
+            base = self.packed.data_ptr()
+            d.tile_off = base
+            d.tiles = base + m["header_bytes"]
+            d.col_scale = _ptr(self.scale2)
+            d.K, d.N, d.bits, d.group = m["K"], m["N"], m["bits"], GROUP
+            d.n_row_blocks, d.n_col_tiles = m["n_row_blocks"], m["n_col_tiles"]
+            d.max_tile_bytes = m["max_tile_bytes"]
+            d.nnz = m["nnz"]
+            self._desc, self._desc_key = d, key
+        return self._desc
+
+    def _scratch_for(self, M: int) -> torch.Tensor:
+        lib = _lib.load()
+        d = self._descriptor()
+        if M <= GEMV_MAX_TOKENS:
+            need = lib.cobalt_gemv_scratch_bytes(ctypes.byref(d), M)
+        else:
+            need = lib.cobalt_gemm_scratch_bytes(ctypes.byref(d), M)
+        if need == 0:
+            raise _lib.CobaltError("cobalt_*_scratch_bytes", -1, "could not size the scratch buffer")
+        if self._scratch is None or self._scratch.numel() < need or self._scratch.device != self.packed.device:
+            self._scratch = torch.zeros(need + 256, dtype=torch.uint8, device=self.packed.device)
+        return self._scratch
+
+    @staticmethod
+    def _aligned(t: torch.Tensor, a: int = 256) -> int:
+        return (t.data_ptr() + a - 1) // a * a
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("CobaltSparseLinear.forward needs a CUDA tensor; there is no CPU path")
+        if x.dtype != torch.bfloat16:
+            raise TypeError(f"CobaltSparseLinear computes in bfloat16, got {x.dtype}")
+        lib = _lib.load()
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        y = torch.empty(M, self.out_features, dtype=torch.bfloat16, device=x.device)
+        if M == 0:
+            return y.reshape(*lead, self.out_features)
+        d = self._descriptor()
+        scratch = self._scratch_for(M)
+        sp = self._aligned(scratch)
+        sbytes = scratch.numel() - (sp - scratch.data_ptr())
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        bias = None if self.bias is None else self.bias.data.to(torch.bfloat16)
+        if M <= GEMV_MAX_TOKENS:
+            rc = lib.cobalt_gemv(ctypes.byref(d), x2.data_ptr(), x2.stride(0), y.data_ptr(), y.stride(0), _ptr(bias), M,
+                                 sp, sbytes, stream)
+            _lib.check("cobalt_gemv", rc)
+        else:
+            rc = lib.cobalt_gemm(ctypes.byref(d), x2.data_ptr(), x2.stride(0), y.data_ptr(), y.stride(0), _ptr(bias), M,
+                                 sp, sbytes, stream)
+            _lib.check("cobalt_gemm", rc)
+        return y.reshape(*lead, self.out_features)
+
+    # ------------------------------------------------------------------ inspection
+    def dequantize(self) -> torch.Tensor:
+        """Dense bf16 ``[K, N]`` weight, bit-identical to the reference's dequantisation cast to bf16."""
+        lib = _lib.load()
+        W = torch.empty(self.out_features, self.in_features, dtype=torch.bfloat16, device=self.packed.device)
+        rc = lib.cobalt_dequant(ctypes.byref(self._descriptor()), W.data_ptr(),
+                                torch.cuda.current_stream(W.device).cuda_stream)
+        _lib.check("cobalt_dequant", rc)
+        return W
+
+    def unpack(self):
+        """``(codes uint8[K, N], keep bool[K, N])`` recovered from the packed image."""
+        lib = _lib.load()
+        dev = self.packed.device
+        codes = torch.empty(self.out_features, self.in_features, dtype=torch.uint8, device=dev)
+        keep = torch.empty_like(codes)
+        rc = lib.cobalt_unpack(ctypes.byref(self._descriptor()), codes.data_ptr(), keep.data_ptr(),
+                               torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check("cobalt_unpack", rc)
+        return codes, keep.bool()
+
+    def device_status(self) -> int:
+        """Status word of the last kernels that used this module's scratch buffer (0 = healthy)."""
+        if self._scratch is None:
+            return 0
+        out = ctypes.c_uint32(0)
+        _lib.load().cobalt_device_status(self._aligned(self._scratch),
+                                         torch.cuda.current_stream(self.packed.device).cuda_stream, ctypes.byref(out))
+        return int(out.value)
+
+    def compressed_bytes(self) -> int:
+        return TileImage.from_meta(self.packed, self._img_meta).algorithmic_bytes()
+
+    # ------------------------------------------------------------------ (de)serialisation
+    def state_dict(self, *args, **kwargs):
+        """Plain dict of CPU tensors plus ``"meta"`` (layout of sinq/cprlinear.py:400-440)."""
+        sd = {"packed": self.packed.detach().cpu(), "meta": dict(self.meta, image=dict(self._img_meta))}
+        if self.scale2 is not None:
+            sd["scale2"] = self.scale2.detach().cpu()
+        if self.bias is not None:
+            sd["bias"] = self.bias.detach().cpu()
+        return sd
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        meta = dict(state_dict["meta"])
+        img = TileImage.from_meta(state_dict["packed"].to(self.packed.device if hasattr(self, "packed") else "cpu"),
+                                  meta.pop("image"))
+        for name in ("packed", "scale2"):
+            if name in self._buffers:
+                del self._buffers[name]
+        dev = img.blob.device
+        self._install(img, state_dict.get("scale2"), state_dict.get("bias"), meta)
+        if self.scale2 is not None:
+            self.scale2 = self.scale2.to(dev)
+        return self
+
+    @classmethod
+    def from_state_dict(cls, state_dict, device="cuda", compute_dtype=torch.bfloat16):
+        if compute_dtype != torch.bfloat16:
+            raise TypeError("CobaltSparseLinear computes in bfloat16")
+        meta = dict(state_dict["meta"])
+        img = TileImage.from_meta(state_dict["packed"].to(device), meta.pop("image"))
+        obj = cls._blank()
+        s2 = state_dict.get("scale2")
+        b = state_dict.get("bias")
+        obj._install(img, None if s2 is None else s2.to(device), None if b is None else b.to(device), meta)
+        return obj
+
+    def _apply(self, fn, *a, **k):
+        out = super()._apply(fn, *a, **k)
+        self._desc = None
+        self._scratch = None
+        return out
+
+    def extra_repr(self) -> str:
+        m = self._img_meta
+        dens = m["nnz"] / float(m["K"] * m["N"])
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.bits}, "
+                f"group_size={GROUP}, density={dens:.3f}, bias={self.bias is not None}")

@@ -1,0 +1,127 @@
+/*
+ * cobalt_b200.h -- C ABI of libcobalt_b200.so
+ *
+ * Sparse low-bit compressed linear layer for NVIDIA B200 (sm_100a): activations times a
+ * weight stored as a per-row occupancy bitmask, 2/3/4-bit codes for the surviving
+ * positions and one fp16 scale + fp16 zero point per 128-wide group.
+ *
+ * Conventions
+ *   - W is [K, N] = [out_features, in_features]; groups run along N; N % 128 == 0.
+ *   - Every pointer is a DEVICE pointer unless the name says "host".  The caller owns all
+ *     buffers; the library allocates nothing.
+ *   - `stream` is a cudaStream_t passed as void*.  Calls are stream-ordered and never
+ *     synchronise (except cobalt_linear_host() and cobalt_device_status(), which say so).
+ *   - Return value: 0 on success, a negative COBALT_E* code otherwise.  Arguments are
+ *     validated on the host; nothing traps or aborts.
+ *   - Activations and outputs are bf16 (uint16 storage), row-major with a leading
+ *     dimension in elements.
+ *
+ * Tile image (what `tiles` / `tile_off` point at), produced by cobalt_b200/format.py:
+ *   row block rb = 16 rows, column tile ct = up to 4 groups (512 columns); tiles are stored
+ *   row-block-major, tile index = rb * n_col_tiles + ct, each padded to 16 bytes:
+ *     mask   16*w segments x 16 B : segment (r, gi) at index r*w + gi, 4 u32 words,
+ *                                   bit b of word j = column 128*(4*ct+gi) + 32*j + b
+ *     sz     16*w x 4 B           : { fp16 scale, fp16 zero }
+ *     codes  little-endian stream of `bits`-wide survivor codes, segment order, ascending column
+ *   w = min(4, N/128 - 4*ct).  tile_off[i] is the start of tile i in 16-byte units.
+ */
+#ifndef COBALT_B200_H
+#define COBALT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COBALT_OK            0
+#define COBALT_EINVAL       (-1)   /* bad argument (null pointer, shape, alignment, bits) */
+#define COBALT_ESCRATCH     (-2)   /* scratch buffer missing or too small */
+#define COBALT_ELAUNCH      (-3)   /* CUDA launch / runtime error (cudaGetLastError) */
+#define COBALT_EARCH        (-4)   /* device is not compute capability 10.x */
+#define COBALT_ETIMEOUT     (-5)   /* a bounded device-side wait gave up (see cobalt_device_status) */
+#define COBALT_ETOOBIG      (-6)   /* size exceeds a stated maximum of the entry point */
+
+/* Descriptor of one packed matrix.  Replaces the reference's 9 x int64 MatDesc
+ * {data,row_off,scale,zero,col_scale,K,N,G,layout}
+ * (src/cobaltkernel/csrc/megakernel.cuh:21-28, built in src/cobaltkernel/runner.py:318-335). */
+typedef struct CobaltMat {
+    const void*     tiles;          /* first tile, 16-byte aligned */
+    const uint32_t* tile_off;       /* n_row_blocks * n_col_tiles + 1 entries, 16-byte units */
+    const void*     col_scale;      /* optional fp16[N] per-input-column scale (reference `scale2`), or NULL */
+    int32_t K, N;                   /* out_features, in_features */
+    int32_t bits;                   /* 2, 3 or 4 */
+    int32_t group;                  /* 128 */
+    int32_t n_row_blocks;           /* ceil(K / 16) */
+    int32_t n_col_tiles;            /* ceil(N / 512) */
+    uint32_t max_tile_bytes;        /* largest tile of this matrix */
+    uint32_t reserved;
+    int64_t nnz;                    /* number of survivors */
+} CobaltMat;
+
+/* Library / ABI version (major << 16 | minor). */
+int cobalt_version(void);
+
+/* Human-readable text for a status code. */
+const char* cobalt_strerror(int status);
+
+/* Decode GEMV, M <= 16 tokens:  y[m, k] = bf16( sum_j bf16(W[k, j]) * x[m, j] (+ bias[k]) ), fp32 accumulate.
+ * Replaces the reference's warp-per-row bitmap GEMV dispatcher cbk::gemv_rows<M>
+ * (src/cobaltkernel/csrc/cobalt_gemv.cuh:1197-1213; gemv_sparse :216-301, gemv_sparse_expand :311-393)
+ * and, above it, SparseQuantLinear.forward for small batches (benchmarks/benchmark_suite.py:1200-1217).
+ * `scratch` holds split-K partial sums and per-row-block arrival counters; it must be at least
+ * cobalt_gemv_scratch_bytes() bytes, 256-byte aligned and ZERO before its first use (the kernel
+ * leaves the counters zero again).  Calls sharing one scratch buffer must not overlap on the GPU. */
+int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
+                const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
+size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M);
+
+/* Same contract and results as cobalt_gemv() through a plain one-thread-per-segment kernel
+ * (no tensor cores, no bulk copies).  Bring-up and cross-check aid; needs no scratch. */
+int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
+                        const void* bias, int M, void* stream);
+
+/* Prefill GEMM, any M >= 1 (meant for M >= 17): same arithmetic contract as cobalt_gemv().
+ * Weight tiles are dequantised to bf16 in shared memory and multiplied with tcgen05.mma,
+ * accumulators in tensor memory.
+ * Replaces cbk::gemm_tile + gemm_phase (src/cobaltkernel/csrc/cobalt_gemm.cuh:243-609,
+ * src/cobaltkernel/csrc/prefill_kernel.cu:103-150).  `scratch` as for cobalt_gemv(). */
+int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
+                const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
+size_t cobalt_gemm_scratch_bytes(const CobaltMat* w, int M);
+
+/* Dense bf16 weight [K, N] (row-major, ld = N), bit-identical to the reference's
+ * dequantize_sparse_sinq(...).to(bfloat16) (sinq/sparse_quant.py:1635-1681):
+ * bf16_rne( fp32(q - z) * fp32(s) [* fp32(col_scale)] ) * keep.
+ * Replaces cbk::dequant_row (src/cobaltkernel/csrc/cobalt_gemv.cuh:1218-1315). */
+int cobalt_dequant(const CobaltMat* w, void* w_bf16, void* stream);
+
+/* Recover the RAW schema (src/cobaltkernel/quantize_cobalt.py:326-329): codes u8[K, N]
+ * (0 at pruned positions) and keep u8[K, N] in {0, 1}.  Either output may be NULL.
+ * Replaces the host reader dequant_reference (src/cobaltkernel/pack_cobalt.py:277-334). */
+int cobalt_unpack(const CobaltMat* w, uint8_t* codes, uint8_t* keep, void* stream);
+
+/* End-to-end call with HOST activations and outputs: copies x host->device, runs the GEMV
+ * (M <= 16) or GEMM, copies y device->host and synchronises `stream`.  The matrix itself
+ * stays resident on the device.  `x_host` / `y_host` should be pinned for full speed.
+ * `dev_x`, `dev_y`, `scratch` are caller-owned device staging buffers of at least
+ * M*N*2, M*K*2 and max(cobalt_gemv_scratch_bytes, cobalt_gemm_scratch_bytes) bytes.
+ * Mirrors what a caller of SparseQuantLinear.forward pays when its tensors live on the host
+ * (benchmarks/benchmark_suite.py:1200-1217). */
+int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M,
+                       void* dev_x, void* dev_y, void* scratch, size_t scratch_bytes, void* stream);
+
+/* Status word written by device code when a bounded wait gives up (0 = healthy).  Reads the
+ * word at the start of `scratch` region reserved for it; synchronises `stream`. */
+int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out);
+
+/* Benchmark tuning hook (not part of the stable contract): key 0 = GEMV column tiles per work
+ * item, 1 = GEMV ring stages, 2 = GEMM operand stages; value 0 restores the built-in heuristic.
+ * No counterpart in the reference, whose knobs are compile-time macros (src/cobaltkernel/runner.py:52-206). */
+int cobalt_set_tuning(int key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COBALT_B200_H */

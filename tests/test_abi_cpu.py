@@ -1,0 +1,67 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header declares, and the
+lane-level decoder passes its host-side check (compiled with g++ from the same .cuh file)."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from cobalt_b200 import build, _lib
+    build.build()
+    return _lib.load()
+
+
+def test_header_symbols_exported(lib):
+    hdr = open(os.path.join(ROOT, "include", "cobalt_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    names = set(re.findall(r"\b(cobalt_[a-z_0-9]+)\s*\(", hdr))
+    assert {"cobalt_gemv", "cobalt_gemm", "cobalt_dequant", "cobalt_unpack", "cobalt_linear_host"} <= names
+    from cobalt_b200 import _lib
+    assert names == set(_lib.EXPORTS), (names ^ set(_lib.EXPORTS))
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_struct_layout_and_strerror(lib):
+    from cobalt_b200 import _lib
+    assert ctypes.sizeof(_lib.CobaltMat) == 64
+    assert lib.cobalt_version() >> 16 == 1
+    assert lib.cobalt_strerror(0) == b"ok"
+    assert b"invalid" in lib.cobalt_strerror(-1)
+
+
+def test_argument_validation_without_gpu(lib):
+    """Host-side validation rejects bad descriptors before any CUDA call."""
+    from cobalt_b200 import _lib
+    m = _lib.CobaltMat()
+    assert lib.cobalt_gemv(ctypes.byref(m), None, 0, None, 0, None, 1, None, 0, None) == -1
+    assert lib.cobalt_unpack(None, None, None, None) == -1
+    m.tiles, m.tile_off, m.K, m.N, m.bits, m.group = 4096, 4096, 16, 100, 4, 128
+    assert lib.cobalt_dequant(ctypes.byref(m), None, None) == -1      # N not a multiple of 128
+    assert lib.cobalt_set_tuning(9, 1) == -1
+
+
+def test_decoder_core_host_build(tmp_path):
+    exe = tmp_path / "test_decode_core"
+    src = os.path.join(ROOT, "tests", "cpp", "test_decode_core.cpp")
+    subprocess.run(["g++", "-O2", "-std=c++17", "-o", str(exe), src], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and "OK" in out.stdout, out.stdout + out.stderr
+
+
+def test_forward_refuses_cpu_tensor():
+    import torch
+    from cobalt_b200 import CobaltSparseLinear
+    keep = torch.ones(16, 128, dtype=torch.bool)
+    q = torch.zeros(16, 128, dtype=torch.uint8)
+    sc = torch.ones(16, 1).half()
+    mod = CobaltSparseLinear(q, sc, sc, keep, None, None, {"nbits": 4, "group_size": 128})
+    with pytest.raises(RuntimeError):
+        mod(torch.zeros(1, 128, dtype=torch.bfloat16))
