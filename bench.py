@@ -1,0 +1,371 @@
+"""Benchmark of the compressed-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (single GPU): every projection of a Mistral-7B decoder block (q 4096x4096, k/v
+1024x4096, o 4096x4096, gate/up 14336x4096, down 4096x14336), weights N(0, 0.02) compressed
+to 4-bit codes at 50 % sparsity with 128-wide groups, one decode token (M = 1).  A "step" is
+one pass of the decode GEMV over the seven matrices.  Several copies of the block are
+rotated so that every step streams its weights from HBM (the working set is several times
+the 126 MB L2).
+
+  value      GB/s of algorithmic compressed bytes (bitmask + codes + fp16 scale/zero +
+             activations in/out) with all inputs resident in HBM, timed with CUDA events
+             around K steps replayed from a CUDA graph.
+  e2e        the same metric through cobalt_linear_host(): pinned host activations copied
+             in, result copied back, every call.
+  roofline   the GEMV kernel against the measured HBM copy bandwidth.
+  cpu_baseline  the reference path (dense bf16 weight, torch.matmul) on the host cores.
+
+With --gpus N > 1 (launched by torch.distributed.run) the block is tensor-parallel: q/k/v/
+gate/up sharded by output rows, o/down by input columns with one NCCL all-reduce each.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES_7B = [("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4096),
+             ("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336)]
+ROW_PARALLEL = ("o", "down")
+BITS, SPARSITY, BETA = 4, 0.5, 0.5
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------------------- workload construction
+def build_block(device, rank=0, world=1, seed0=1000):
+    """Compress and pack the (shard of the) seven projections of one block on `device`."""
+    from cobalt_b200 import CobaltSparseLinear, SparseQuantConfig, compress_weight
+    from cobalt_b200.format import pack_tiles, slice_cols, slice_rows
+    mods, info = {}, {}
+    cfg = SparseQuantConfig(BITS, SPARSITY, BETA)
+    for idx, (name, K, N) in enumerate(SHAPES_7B):
+        g = torch.Generator(device="cpu").manual_seed(seed0 + idx)
+        W = (torch.randn(K, N, generator=g) * 0.02).half().float().to(device)
+        norm = (torch.randn(N, generator=g).abs() + 0.1).to(device)
+        keep, q, sc, zr = compress_weight(W, norm, cfg)
+        del W
+        if world > 1:
+            if name in ROW_PARALLEL:
+                keep, q, sc, zr = slice_cols(keep, q, sc, zr, rank * N // world, (rank + 1) * N // world)
+            else:
+                keep, q, sc, zr = slice_rows(keep, q, sc, zr, rank * K // world, (rank + 1) * K // world)
+        mod = CobaltSparseLinear.__new__(CobaltSparseLinear)
+        torch.nn.Module.__init__(mod)
+        mod._install(pack_tiles(keep.contiguous(), q.contiguous(), sc.contiguous(), zr.contiguous(), BITS), None, None,
+                     {"nbits": BITS})
+        mods[name] = mod
+        info[name] = dict(K=mod.out_features, N=mod.in_features, bytes=mod.compressed_bytes())
+        del keep, q, sc, zr
+    torch.cuda.empty_cache()
+    return mods, info
+
+
+def clone_block(mods):
+    from cobalt_b200 import CobaltSparseLinear
+    from cobalt_b200.format import TileImage
+    out = {}
+    for name, m in mods.items():
+        c = CobaltSparseLinear.__new__(CobaltSparseLinear)
+        torch.nn.Module.__init__(c)
+        c._install(TileImage.from_meta(m.packed.clone(), m._img_meta), None, None, {"nbits": m.bits})
+        out[name] = c
+    return out
+
+
+def step_bytes(info, M):
+    w = sum(v["bytes"] for v in info.values())
+    act = sum(M * v["N"] * 2 + M * v["K"] * 2 for v in info.values())
+    return w, act
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args):
+    from cobalt_b200 import _lib
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    M = args.tokens
+
+    mods0, info = build_block(dev, rank, world)
+    wbytes, abytes = step_bytes(info, M)
+    copies = max(2, -(-4 * L2_BYTES // max(wbytes, 1)))          # working set >= 4 x L2
+    copies = min(copies, 64)
+    blocks = [mods0] + [clone_block(mods0) for _ in range(copies - 1)]
+    stream = torch.cuda.Stream(dev)
+    xs = {name: (torch.randn(M, v["N"], device=dev) ).to(torch.bfloat16) for name, v in info.items()}
+    ys = {name: torch.empty(M, v["K"], dtype=torch.bfloat16, device=dev) for name, v in info.items()}
+    red = {name: torch.zeros(M, info[name]["K"], dtype=torch.float32, device=dev) for name in ROW_PARALLEL}
+
+    def one_step(blk):
+        for name, _, _ in SHAPES_7B:
+            y = blk[name](xs[name])
+            if world > 1 and name in ROW_PARALLEL:          # partial sums of the row-parallel layers
+                red[name].copy_(y)
+                dist.all_reduce(red[name])
+                ys[name].copy_(red[name])
+
+    with torch.cuda.stream(stream):
+        for b in blocks:                                     # allocate scratch, configure kernels
+            one_step(b)
+        stream.synchronize()
+        graph = None
+        if world == 1:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for b in blocks:
+                    one_step(b)
+
+        def run_steps(n):
+            done = 0
+            while done < n:
+                if graph is not None and n - done >= len(blocks):
+                    graph.replay()
+                    done += len(blocks)
+                else:
+                    one_step(blocks[done % len(blocks)])
+                    done += 1
+
+        run_steps(max(args.warmup, 3))
+        stream.synchronize()
+        if dist is not None:
+            dist.barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        run_steps(args.steps)
+        e1.record(stream)
+        stream.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        # hold the load a little longer so that the clock sampler sees it
+        t_end = time.time() + 1.0
+        while rank == 0 and time.time() < t_end:
+            run_steps(len(blocks))
+            stream.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+        status = max(m.device_status() for b in blocks for m in b.values())
+
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    total_bytes = (wbytes + abytes) * world                  # every rank streams its shard
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer entry point (rank-local; aggregated like `value`)
+    e2e_steps = max(3, min(args.steps, 20))
+    hx = {n: xs[n].cpu().pin_memory() for n in xs}
+    hy = {n: torch.empty(M, info[n]["K"], dtype=torch.bfloat16).pin_memory() for n in xs}
+    scr = {}
+    for name, m in mods0.items():
+        need = lib.cobalt_gemv_scratch_bytes(ctypes.byref(m._descriptor()), M)
+        scr[name] = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+
+    def e2e_step(blk):
+        for name, _, _ in SHAPES_7B:
+            m = blk[name]
+            sp = (scr[name].data_ptr() + 255) // 256 * 256
+            rc = lib.cobalt_linear_host(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
+                                        xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
+                                        stream.cuda_stream)
+            _lib.check("cobalt_linear_host", rc)
+
+    for i in range(3):
+        e2e_step(blocks[i % len(blocks)])
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(blocks[i % len(blocks)])
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = total_bytes / (e2e_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peaks()
+    out = {
+        "metric": "compressed-linear achieved GB/s (7B block decode, compressed bytes)",
+        "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Mistral-7B block projections q/k/v/o/gate/up/down, {BITS}-bit, {int(SPARSITY*100)}% sparse, "
+                               f"g=128, M={M} decode GEMV" + (f", tensor-parallel x{world}" if world > 1 else ""),
+                   "l2": f"{copies} block copies rotated ({copies * wbytes / 1e6:.0f} MB working set > L2)",
+                   "bytes_per_step": int(wbytes + abytes), "peak": peak_kind},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": int(sum(M * v["N"] * 2 for v in info.values())),
+                "d2h_bytes_per_step": int(sum(M * v["K"] * 2 for v in info.values()))},
+        "gpu_launches": int(args.steps * len(SHAPES_7B)),
+        "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(value / world / peak, 4), "traffic": None,
+                     "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": len(SHAPES_7B),
+                     "bytes_per_launch": int((wbytes + abytes) / len(SHAPES_7B))},
+        "device_status": status,
+    }
+    if world == 1:
+        out["cpu_baseline"] = cpu_baseline(info, M, budget_s=15.0)
+    print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- CPU arm (reference path)
+def cpu_baseline(info, M, budget_s=15.0, steps=None, warmup=1):
+    """The reference path on the host cores: SparseQuantLinear keeps a dense bf16 copy of the
+    dequantised weight after its first call and multiplies with torch.matmul
+    (benchmarks/benchmark_suite.py:1200-1217).  The weight values do not influence the time, so a
+    seeded dense bf16 matrix of the right shape stands in for the dequantised one."""
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1)
+    Ws = {n: (torch.randn(v["K"], v["N"], generator=g) * 0.02).to(torch.bfloat16) for n, v in info.items()}
+    xs = {n: torch.randn(M, v["N"], generator=g).to(torch.bfloat16) for n, v in info.items()}
+
+    def step():
+        for n in Ws:
+            torch.matmul(xs[n], Ws[n].t())
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        step()
+        n += 1
+        el = time.perf_counter() - t0
+        if (steps is not None and n >= steps) or (steps is None and (el > budget_s or n >= 50)):
+            break
+    ms = el * 1e3 / n
+    wbytes, abytes = step_bytes(info, M)
+    return {"value": round((wbytes + abytes) / (ms * 1e-3) / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "ms_per_step": round(ms, 3),
+            "sample": f"{n} passes over one block (7 dense bf16 matmuls, cached-weight mode of the reference module), M={M}"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    info = {}
+    for name, K, N in SHAPES_7B:
+        nnz = int(K * N * (1 - SPARSITY))
+        info[name] = dict(K=K, N=N, bytes=K * N // 8 + (BITS * nnz + 7) // 8 + K * (N // 128) * 4)
+    M = args.tokens
+    cb = cpu_baseline(info, M, steps=max(1, args.steps), warmup=max(1, min(args.warmup, 3)))
+    wbytes, abytes = step_bytes(info, M)
+    out = {"impl": "reference", "metric": "compressed-linear achieved GB/s (7B block decode, compressed bytes)",
+           "value": cb["value"], "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": f"Mistral-7B block projections q/k/v/o/gate/up/down, {BITS}-bit, {int(SPARSITY*100)}% sparse, "
+                                  f"g=128, M={M}: reference CPU path (dense bf16 weight + torch.matmul)",
+                      "bytes_per_step": int(wbytes + abytes)},
+           "cpu_baseline": cb,
+           "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=1, help="decode batch M (1..16)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

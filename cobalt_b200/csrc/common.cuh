@@ -86,9 +86,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Wait with an iteration limit: returns false (and records `code`) instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t code) {
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
+    for (uint32_t it = 0; it < (1u << 18); ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (it > 64) __nanosleep(64);
+        if (it > 64) __nanosleep(128);
     }
     if (status) atomicCAS(status, 0u, code);
     return false;

@@ -1,0 +1,303 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle.  Needs a B200.
+
+Bars
+  * unpacked codes, keep mask and dequantised bf16 weights: bit-exact;
+  * layer outputs in bf16: rel-L2 <= 1e-3 and max-abs <= 1e-2 against the oracle's CPU result.
+    bf16 values at |y| >= 2 are 2^-6 = 0.0156 apart, so two correct fp32 accumulations that
+    straddle a rounding boundary differ by more than 1e-2 there.  An element may exceed 1e-2
+    only if it is such a case: the oracle's value and ours must both lie within half a bf16
+    spacing (+0.2 %) of the exact fp64 dot product of the same bf16 weights and activations.
+"""
+import numpy as np
+import pytest
+import torch
+
+from cobalt_b200 import CobaltSparseLinear, SparseQuantConfig, compress_weight
+from oracle import cobalt_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 1e-2
+REL_L2 = 1e-3
+
+
+def bf16_spacing(v: torch.Tensor) -> torch.Tensor:
+    """Distance between neighbouring bf16 values around |v| (normal range)."""
+    e = torch.floor(torch.log2(v.abs().double().clamp(min=1e-30)))
+    return torch.pow(torch.tensor(2.0, dtype=torch.float64), e - 7)
+
+
+def check_output(y: torch.Tensor, y_ref: torch.Tensor, y_exact: torch.Tensor):
+    y, y_ref = y.detach().cpu(), y_ref.detach().cpu()
+    assert y.dtype == torch.bfloat16 and y.shape == y_ref.shape
+    assert torch.isfinite(y.float()).all()
+    d = (y.double() - y_ref.double()).abs()
+    rel = float(d.norm() / y_ref.double().norm().clamp(min=1e-30))
+    assert rel <= REL_L2, f"rel-L2 {rel:.3e}"
+    bad = d > MAX_ABS
+    if bad.any():
+        ex = y_exact.double()[bad]
+        for name, val in (("ours", y.double()[bad]), ("oracle", y_ref.double()[bad])):
+            err = (val - ex).abs()
+            lim = 0.5 * bf16_spacing(val) * 1.002
+            assert bool((err <= lim).all()), f"{name}: {int(bad.sum())} elements off by more than {MAX_ABS} and not a rounding-boundary case"
+    return rel, float(d.max())
+
+
+def exact_fp64(x, Wb):
+    return x.double() @ Wb.double().t()
+
+
+def to_module(keep, q, sc, zr, bits, scale2=None, bias=None):
+    K, N = q.shape
+    G = N // 128
+    dev = "cuda"
+    meta = {"nbits": bits, "group_size": 128, "shape": (K, N)}
+    return CobaltSparseLinear(q.to(dev), sc.view(K, G, 1).to(dev), zr.view(K, G, 1).to(dev), keep.to(dev),
+                              None if scale2 is None else scale2.to(dev), None if bias is None else bias.to(dev), meta)
+
+
+def _bf16(arr):
+    return torch.from_numpy(arr.copy()).view(torch.bfloat16)
+
+
+GOLD = [("c3s70", 3), ("c4s50", 4), ("c2s50", 2), ("c3s60", 3), ("c4s90_b0", 4), ("c4s00", 4)]
+
+
+def _gold(golden, name):
+    return (torch.from_numpy(golden[f"{name}.keep"]), torch.from_numpy(golden[f"{name}.q"]),
+            torch.from_numpy(golden[f"{name}.scale"]), torch.from_numpy(golden[f"{name}.zero"]))
+
+
+# ----------------------------------------------------------------------------- bit-exact parts
+@pytest.mark.parametrize("name,bits", GOLD)
+def test_unpack_and_dequant_bitexact(golden, name, bits):
+    keep, q, sc, zr = _gold(golden, name)
+    mod = to_module(keep, q, sc, zr, bits)
+    codes, k2 = mod.unpack()
+    assert torch.equal(codes.cpu(), q)
+    assert torch.equal(k2.cpu(), keep)
+    W = mod.dequantize().cpu()
+    want = torch.from_numpy(golden[f"{name}.Wdeq_bf16"]).view(torch.bfloat16)
+    assert torch.equal(W.view(torch.int16), want.view(torch.int16))
+    assert bool((W[~keep] == 0).all())
+
+
+def test_dequant_with_column_scale_bitexact(golden):
+    keep, q, sc, zr = _gold(golden, "colscale")
+    cs = torch.from_numpy(golden["colscale.col_scale"])
+    mod = to_module(keep, q, sc, zr, 4, scale2=cs)
+    W = mod.dequantize().cpu()
+    assert torch.equal(W.view(torch.int16), torch.from_numpy(golden["colscale.Wdeq_bf16"]))
+
+
+# ----------------------------------------------------------------------------- GEMV
+@pytest.mark.parametrize("name,bits", GOLD)
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_gemv_golden(golden, name, bits, M):
+    keep, q, sc, zr = _gold(golden, name)
+    mod = to_module(keep, q, sc, zr, bits)
+    x = _bf16(golden[f"{name}.x{M}"])
+    y_ref = _bf16(golden[f"{name}.y{M}"])
+    Wb = torch.from_numpy(golden[f"{name}.Wdeq_bf16"]).view(torch.bfloat16)
+    y = mod(x.cuda())
+    check_output(y, y_ref, exact_fp64(x, Wb))
+    assert mod.device_status() == 0
+
+
+@pytest.mark.parametrize("name,bits", GOLD)
+def test_gemv_rowwalk_golden(golden, name, bits):
+    import ctypes
+    from cobalt_b200 import _lib
+    keep, q, sc, zr = _gold(golden, name)
+    mod = to_module(keep, q, sc, zr, bits)
+    lib = _lib.load()
+    for M in (1, 4, 16):
+        x = _bf16(golden[f"{name}.x{M}"]).cuda()
+        y = torch.empty(M, q.shape[0], dtype=torch.bfloat16, device="cuda")
+        rc = lib.cobalt_gemv_rowwalk(ctypes.byref(mod._descriptor()), x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0),
+                                     None, M, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        Wb = torch.from_numpy(golden[f"{name}.Wdeq_bf16"]).view(torch.bfloat16)
+        check_output(y, _bf16(golden[f"{name}.y{M}"]), exact_fp64(x.cpu(), Wb))
+
+
+def test_gemv_column_scale_and_bias(golden):
+    keep, q, sc, zr = _gold(golden, "colscale")
+    cs = torch.from_numpy(golden["colscale.col_scale"])
+    bias = _bf16(golden["colscale.bias"])
+    x = _bf16(golden["colscale.x4"])
+    mod = to_module(keep, q, sc, zr, 4, scale2=cs, bias=bias)
+    y = mod(x.cuda())
+    Wb = torch.from_numpy(golden["colscale.Wdeq_bf16"]).view(torch.bfloat16)
+    yb = (exact_fp64(x, Wb)).to(torch.bfloat16).double() + bias.double()
+    check_output(y, _bf16(golden["colscale.y4"]), yb)
+
+
+def test_gemv_batch_equals_single_and_is_deterministic():
+    """Token m of a batched call equals the single-token call bit for bit (the reference's
+    M=4 == 4 x M=1 gate, src/cobaltkernel/verify_kernel.py:415-461); two runs are identical."""
+    raw = O.synth_raw(192, 4096, 0.5, 4, seed=192 + 4096)
+    mod = to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)
+    x = O.seeded_activation(16, 4096, 77).cuda()
+    y16 = mod(x)
+    assert torch.equal(y16, mod(x))
+    y4 = mod(x[:4])
+    for m in range(4):
+        y1 = mod(x[m:m + 1])
+        assert torch.equal(y1[0], y4[m])
+        assert torch.equal(y1[0], y16[m])
+
+
+def test_pruned_positions_contribute_exactly_zero():
+    """Huge activations at pruned columns leave the output bit-identical
+    (src/cobaltkernel/test_gemv.py:403-455), also with an off-grid zero point."""
+    K, N, bits = 256, 5376, 4
+    g = torch.Generator().manual_seed(7)
+    pat = torch.rand(N, generator=g) < 0.5
+    keep = pat.view(1, N).expand(K, N).contiguous()
+    q = torch.randint(0, 16, (K, N), generator=g, dtype=torch.uint8) * keep.to(torch.uint8)
+    sc = (torch.rand(K, N // 128, generator=g) * 0.01 + 1e-3).half()
+    for zero in (torch.randint(0, 16, (K, N // 128), generator=g).half(), torch.full((K, N // 128), 52.0).half()):
+        mod = to_module(keep, q, sc, zero, bits)
+        x0 = O.seeded_activation(1, N, 8)
+        xh = x0.clone()
+        xh[0, ~pat] = 1.0e4
+        assert torch.equal(mod(x0.cuda()), mod(xh.cuda()))
+        assert bool((mod.dequantize()[:, (~pat).cuda()] == 0).all())
+
+
+@pytest.mark.parametrize("K,N", [(256, 5376), (128, 21504), (192, 4096), (64, 1024)])
+def test_gemv_reference_test_shapes(K, N):
+    """The shapes and seeds of the reference's GEMV unit test (src/cobaltkernel/test_gemv.py:142-181),
+    4 bit, 50 % sparse, generator pinned by tests/test_oracle_golden.py."""
+    raw = O.synth_raw(K, N, 0.5, 4, seed=K + N)
+    mod = to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)
+    Wb = O.dequantize(raw["q"], raw["scale"], raw["zero"], raw["keep"]).to(torch.bfloat16)
+    assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
+    for M in (1, 2, 4, 8):
+        x = O.seeded_activation(M, N, K + M)
+        check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+
+
+# ----------------------------------------------------------------------------- benchmark configurations
+def _compress_on_gpu(K, N, bits, sparsity, seed):
+    """Seeded weights and norms from the oracle's generator; mask + RTN by the product
+    compressor on the GPU; the same RAW tensors are then given to both sides."""
+    W, norm = O.seeded_matrix(K, N, seed)
+    keep, q, sc, zr = compress_weight(W.cuda(), norm.cuda(), SparseQuantConfig(bits, sparsity, 0.5))
+    return keep, q, sc, zr
+
+
+def test_config1_single_linear():
+    """4096 x 4096, 3 bit, 70 % sparse, x = 1 x 4096: mask and codes from the oracle on the CPU."""
+    W, norm = O.seeded_matrix(4096, 4096, 1)
+    keep, q, sc, zr = O.compress(W, norm, 3, 0.7, 0.5)
+    mod = to_module(keep, q, sc, zr, 3)
+    Wb = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)
+    assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
+    codes, k2 = mod.unpack()
+    assert torch.equal(codes.cpu(), q) and torch.equal(k2.cpu(), keep)
+    x = O.seeded_activation(1, 4096, 3001)
+    check_output(mod(x.cuda()), O.linear_forward(x, q, sc, zr, keep), exact_fp64(x, Wb))
+
+
+@pytest.mark.parametrize("name,K,N", [("q", 4096, 4096), ("kv", 1024, 4096), ("gate_up", 14336, 4096), ("down", 4096, 14336)])
+def test_config2_block_shapes(name, K, N):
+    """Mistral-7B projection shapes, 4 bit, 50 % sparse, M in {1, 4, 16}."""
+    keep, q, sc, zr = _compress_on_gpu(K, N, 4, 0.5, 1000 + K % 97 + N % 89)
+    mod = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": 4})
+    kc, qc, scc, zrc = keep.cpu(), q.cpu(), sc.cpu(), zr.cpu()
+    Wb = O.dequantize(qc, scc, zrc, kc).to(torch.bfloat16)
+    assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
+    for M in (1, 4, 16):
+        x = O.seeded_activation(M, N, 3000 + M)
+        check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+    assert mod.device_status() == 0
+
+
+# ----------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("name,bits", GOLD)
+@pytest.mark.parametrize("M", [17, 100, 128, 300])
+def test_gemm_golden_matrices(golden, name, bits, M):
+    keep, q, sc, zr = _gold(golden, name)
+    mod = to_module(keep, q, sc, zr, bits)
+    Wb = torch.from_numpy(golden[f"{name}.Wdeq_bf16"]).view(torch.bfloat16)
+    x = O.seeded_activation(M, q.shape[1], 500 + M)
+    y = mod(x.cuda())
+    check_output(y, torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+    assert mod.device_status() == 0
+
+
+def test_gemm_column_scale_and_bias(golden):
+    keep, q, sc, zr = _gold(golden, "colscale")
+    cs = torch.from_numpy(golden["colscale.col_scale"])
+    bias = _bf16(golden["colscale.bias"])
+    mod = to_module(keep, q, sc, zr, 4, scale2=cs, bias=bias)
+    x = O.seeded_activation(64, q.shape[1], 11)
+    y_ref = O.linear_forward(x, q, sc, zr, keep, cs, bias)
+    Wb = torch.from_numpy(golden["colscale.Wdeq_bf16"]).view(torch.bfloat16)
+    check_output(mod(x.cuda()), y_ref, exact_fp64(x, Wb).to(torch.bfloat16).double() + bias.double())
+
+
+@pytest.mark.parametrize("bits,sparsity", [(3, 0.7), (2, 0.5)])
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 128), (4096, 4096, 512), (1024, 4096, 2048), (14336, 4096, 128),
+                                    (4096, 14336, 512)])
+def test_config4_prefill_shapes(bits, sparsity, K, N, M):
+    """Prefill sweep shapes on the 7B projections; the oracle matmul runs on the CPU."""
+    keep, q, sc, zr = _compress_on_gpu(K, N, bits, sparsity, 4000 + bits)
+    mod = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": bits})
+    Wb = O.dequantize(q.cpu(), sc.cpu(), zr.cpu(), keep.cpu()).to(torch.bfloat16)
+    x = O.seeded_activation(M, N, 4100 + M)
+    y = mod(x.cuda())
+    check_output(y, torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+    # the first 16 tokens through the GEMV agree with the GEMM (both accumulate the same products in fp32)
+    y16 = mod(x[:16].cuda())
+    d = (y16.float() - y[:16].float()).abs()
+    assert float(d.norm() / y16.float().norm()) <= REL_L2
+    assert mod.device_status() == 0
+
+
+def test_state_dict_roundtrip(golden):
+    keep, q, sc, zr = _gold(golden, "c4s50")
+    mod = to_module(keep, q, sc, zr, 4)
+    sd = mod.state_dict()
+    assert all(not v.is_cuda for v in sd.values() if isinstance(v, torch.Tensor))
+    mod2 = CobaltSparseLinear.from_state_dict(sd, device="cuda")
+    x = _bf16(golden["c4s50.x4"]).cuda()
+    assert torch.equal(mod(x), mod2(x))
+
+
+def test_patch_model_swaps_linears():
+    import torch.nn as nn
+    from cobalt_b200 import patch_model
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = nn.Linear(256, 64, bias=False)
+            self.up_proj = nn.Linear(256, 128, bias=False)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Block(), Block()])
+            self.lm_head = nn.Linear(256, 32, bias=False)
+
+    torch.manual_seed(0)
+    net = Net()
+    ref = {n: m.weight.detach().clone() for n, m in net.named_modules() if isinstance(m, nn.Linear)}
+    patch_model(net, SparseQuantConfig(bits=4, sparsity=0.5))       # compress + pack on the CPU ...
+    net = net.cuda()                                                # ... then move the packed images
+    assert isinstance(net.lm_head, nn.Linear)
+    assert net.cobalt_quantized and sorted(net.linear_tags) == ["q_proj", "up_proj"]
+    for i in range(2):
+        for nme in ("q_proj", "up_proj"):
+            mod = getattr(net.layers[i], nme)
+            assert isinstance(mod, CobaltSparseLinear)
+            W = ref[f"layers.{i}.{nme}"].cpu()
+            keep, q, sc, zr = O.compress(W, torch.ones(W.shape[1]), 4, 0.5, 0.5)
+            Wb = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)
+            assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
+            x = O.seeded_activation(2, 256, 5)
+            check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
