@@ -159,15 +159,21 @@ def run_ours(args):
     lib = _lib.load()
     M = args.tokens
 
+    global SHAPES_7B
+    if args.shapes:
+        want = args.shapes.split(",")
+        SHAPES_7B = [t for t in SHAPES_7B if t[0] in want]
     mods0, info = build_block(dev, rank, world)
     wbytes, abytes = step_bytes(info, M)
     copies = max(2, -(-4 * L2_BYTES // max(wbytes, 1)))          # working set >= 4 x L2
     copies = min(copies, 64)
+    if args.copies > 0:
+        copies = args.copies
     blocks = [mods0] + [clone_block(mods0) for _ in range(copies - 1)]
     stream = torch.cuda.Stream(dev)
     xs = {name: (torch.randn(M, v["N"], device=dev) ).to(torch.bfloat16) for name, v in info.items()}
     ys = {name: torch.empty(M, v["K"], dtype=torch.bfloat16, device=dev) for name, v in info.items()}
-    red = {name: torch.zeros(M, info[name]["K"], dtype=torch.float32, device=dev) for name in ROW_PARALLEL}
+    red = {name: torch.zeros(M, info[name]["K"], dtype=torch.float32, device=dev) for name in ROW_PARALLEL if name in info}
 
     def one_step(blk):
         for name, _, _ in SHAPES_7B:
@@ -182,7 +188,7 @@ def run_ours(args):
             one_step(b)
         stream.synchronize()
         graph = None
-        if world == 1:
+        if world == 1 and not args.profile:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for b in blocks:
@@ -215,8 +221,28 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
+        # per-shape launch time (graph of one launch per copy, replayed)
+        per_shape = {}
+        if world == 1 and not args.profile:
+            for name, _, _ in SHAPES_7B:
+                gsh = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gsh, stream=stream):
+                    for b in blocks:
+                        b[name](xs[name])
+                for _ in range(3):
+                    gsh.replay()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 20
+                a0.record(stream)
+                for _ in range(reps):
+                    gsh.replay()
+                a1.record(stream)
+                stream.synchronize()
+                us = a0.elapsed_time(a1) * 1e3 / (reps * len(blocks))
+                nbytes = info[name]["bytes"] + M * (info[name]["N"] + info[name]["K"]) * 2
+                per_shape[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
         # hold the load a little longer so that the clock sampler sees it
-        t_end = time.time() + 1.0
+        t_end = time.time() + (0.0 if args.profile else 1.0)
         while rank == 0 and time.time() < t_end:
             run_steps(len(blocks))
             stream.synchronize()
@@ -231,6 +257,13 @@ def run_ours(args):
     total_bytes = (wbytes + abytes) * world                  # every rank streams its shard
     value = total_bytes / (ms_step * 1e-3) / 1e9
 
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "value": round(value, 2), "unit": "GB/s", "ms_per_step": round(ms_step, 5),
+                              "shapes": [t[0] for t in SHAPES_7B], "copies": copies}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     # ---- end to end through the host-buffer entry point (rank-local; aggregated like `value`)
     e2e_steps = max(3, min(args.steps, 20))
     hx = {n: xs[n].cpu().pin_memory() for n in xs}
@@ -289,6 +322,7 @@ def run_ours(args):
                      "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": len(SHAPES_7B),
                      "bytes_per_launch": int((wbytes + abytes) / len(SHAPES_7B))},
         "device_status": status,
+        "per_shape": per_shape,
     }
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(info, M, budget_s=15.0)
@@ -360,6 +394,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=1, help="decode batch M (1..16)")
+    ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
+    ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
+    ap.add_argument("--profile", action="store_true",
+                    help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -21,7 +21,7 @@ class CobaltMat(Structure):
         ("K", c_int32), ("N", c_int32),
         ("bits", c_int32), ("group", c_int32),
         ("n_row_blocks", c_int32), ("n_col_tiles", c_int32),
-        ("max_tile_bytes", c_uint32), ("reserved", c_uint32),
+        ("max_tile_bytes", c_uint32), ("max_tile_nnz", c_uint32),
         ("nnz", c_int64),
     ]
 

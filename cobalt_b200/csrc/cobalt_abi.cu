@@ -48,6 +48,8 @@ int check_mat(const CobaltMat* w) {
     if (((uintptr_t)w->tiles & 15) || ((uintptr_t)w->tile_off & 3)) return COBALT_EINVAL;
     if (w->max_tile_bytes < 320 || (w->max_tile_bytes & 15)) return COBALT_EINVAL;
     if (w->max_tile_bytes > TILE_ROWS * TILE_GROUPS * 20 + TILE_ROWS * TILE_GROUPS * GROUP * 4 / 8 + 16) return COBALT_EINVAL;
+    if (w->max_tile_nnz > (uint32_t)(TILE_ROWS * TILE_GROUPS * GROUP)) return COBALT_EINVAL;
+    if ((size_t)w->max_tile_nnz * w->bits / 8 + 320 > (size_t)w->max_tile_bytes + 16) return COBALT_EINVAL;
     return COBALT_OK;
 }
 
@@ -61,15 +63,15 @@ int check_io(const void* x, int64_t ldx, const void* y, int64_t ldy, int M, int 
 
 // ----------------------------------------------------------------------------- GEMV configuration
 struct GemvCfg {
-    int splits, tps, stages, mt, grid;
-    uint32_t slot, nib;
+    int stages, mt, grid;
+    uint32_t slot, nib, total_warps;
     size_t smem, counters_off, partials_off, total;
 };
 
 uint32_t nibble_bytes(const CobaltMat* w) {
     if (w->bits == 4) return 0;
-    // upper bound on survivors of one tile from its byte size, 4 bits each, plus read-ahead slack
-    return (uint32_t)round_up((size_t)w->max_tile_bytes * 4 / w->bits + 64, 128);
+    // survivors of the fullest tile, 4 bits each, plus read-ahead slack
+    return (uint32_t)round_up((size_t)w->max_tile_nnz / 2 + 64, 128);
 }
 
 int gemv_config(const CobaltMat* w, int M, int num_sms, GemvCfg* c) {
@@ -84,18 +86,17 @@ int gemv_config(const CobaltMat* w, int M, int num_sms, GemvCfg* c) {
     if (fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) return COBALT_EINVAL;
     c->stages = stages;
     c->smem = fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib);
-    const long capacity = (long)num_sms * GEMV_WARPS;
+    // persistent grid: one CTA per SM, fewer when there are not enough tiles to go round
     const long tiles = (long)RB * CT;
-    long tps = g_tune_tiles_per_split > 0 ? g_tune_tiles_per_split : (tiles + capacity / 2) / capacity;
-    if (tps < 1) tps = 1;
-    if (tps > CT) tps = CT;
-    if (tps > 31) tps = 31;
-    c->tps = (int)tps;
-    c->splits = (CT + c->tps - 1) / c->tps;
-    c->grid = (RB * c->splits + GEMV_WARPS - 1) / GEMV_WARPS;
+    long grid = g_tune_tiles_per_split > 0 ? g_tune_tiles_per_split : num_sms;     // tuning key 0 overrides the grid size
+    if (grid > tiles) grid = tiles;
+    if (grid < 1) grid = 1;
+    c->grid = (int)grid;
+    c->total_warps = (uint32_t)(grid * GEMV_WARPS);
+    if ((unsigned long long)(tiles + 1) * c->total_warps >= (1ull << 32)) return COBALT_ETOOBIG;   // 32-bit partition arithmetic
     c->counters_off = SCRATCH_STATUS_BYTES;
     c->partials_off = c->counters_off + round_up((size_t)RB * 4, 256);
-    c->total = c->partials_off + (c->splits > 1 ? (size_t)RB * c->splits * 4 * c->mt * 32 * sizeof(float) : 0);
+    c->total = c->partials_off + (size_t)c->total_warps * 2 * 4 * c->mt * 32 * sizeof(float);
     return COBALT_OK;
 }
 
@@ -207,8 +208,10 @@ int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
     P.y = (uint16_t*)y; P.ldy = ldy;
     P.bias = (const uint16_t*)bias;
     P.M = M;
-    P.splits = c.splits; P.tiles_per_split = c.tps; P.stages = c.stages;
+    P.stages = c.stages;
     P.slot_bytes = c.slot; P.nib_bytes = c.nib;
+    P.total_warps = c.total_warps;
+    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k29 = 1u << 29;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);

@@ -58,7 +58,9 @@ CB_HD float u2f(uint32_t u) {
 // byte permute with the semantics of PTX prmt.b32 (default mode), selector nibble bit 3 = replicate sign
 CB_HD uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 #if CB_DEVICE_CODE
-    return __byte_perm(a, b, sel);
+    uint32_t d;                                   // the intrinsic would mask the selector to 3 bits per nibble
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
 #else
     uint64_t src = ((uint64_t)b << 32) | a;
     uint32_t out = 0;
@@ -97,6 +99,11 @@ CB_HD uint32_t funnel_rc(uint32_t lo, uint32_t hi, uint32_t sh) {
 
 // ----------------------------------------------------------------------------- fp16 / bf16 scalars
 CB_HD float half_bits_to_float(uint32_t h) {
+#if CB_DEVICE_CODE
+    float f;
+    asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.f32.f16 %0, t;\n\t}" : "=f"(f) : "r"(h & 0xFFFFu));
+    return f;
+#endif
     h &= 0xFFFFu;
     uint32_t sign = (h & 0x8000u) << 16, e = (h >> 10) & 0x1Fu, m = h & 0x3FFu;
     if (e == 0) {
@@ -280,6 +287,54 @@ CB_HD void decode32(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t 
             if (i < 1) w2 = funnel_rc(w2, w3, amt);
         }
         // words that later steps cannot reach are left stale on purpose
+    }
+}
+
+// ----------------------------------------------------------------------------- 32 positions, fast segments only
+// Same contract as decode32() for segments whose SegParams::fast is set, arranged for the
+// instruction mix of an SM: the ALU pipe (prmt / lop3 / shf) is the scarce one, so right shifts
+// by constants and the "all eight kept" special case are computed with multiplies on the FMA
+// pipe.  `k28`, `k24`, `k29` must hold 1<<28, 1<<24, 1<<29; they are passed in registers so
+// that the multiplies are not turned back into shifts.  `lut(idx)` returns the table entry of
+// mask byte idx.
+CB_HD uint32_t mulhi_u32(uint32_t a, uint32_t b) {
+#if CB_DEVICE_CODE
+    return __umulhi(a, b);
+#else
+    return (uint32_t)(((uint64_t)a * b) >> 32);
+#endif
+}
+
+struct FastConsts { uint32_t k28, k24, k29; };
+
+template <class LutFn>
+CB_HD void decode32_fast(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, const SegParams& p,
+                         const FastConsts& K, LutFn lut, uint32_t out[16]) {
+    uint32_t idx[4], cnt[4];
+    LutEntry e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        idx[i] = prmt(m, 0u, 0x4440u | (uint32_t)i);        // mask byte i, zero-extended
+        e[i] = lut(idx[i]);
+        cnt[i] = (uint32_t)popc(idx[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t full = mulhi_u32(cnt[i], K.k29);      // 1 iff all eight positions are kept
+        const uint32_t andm = full * 0xFF000000u + 0x00FFFFFFu;
+        const uint32_t zsel = p.zb24 - full * p.zb24;
+        const uint32_t hi = (mulhi_u32(w0, K.k28) & andm) | zsel;   // (w0 >> 4) with the zero point in byte 3
+        const uint32_t d0 = prmt(w0, hi, e[i].x), d1 = prmt(w0, hi, e[i].y);
+        out[4 * i + 0] = dq_pair((d0 & 0x000F000Fu) | 0x43004300u, p);
+        out[4 * i + 1] = dq_pair((mulhi_u32(d0, K.k24) & 0x000F000Fu) | 0x43004300u, p);
+        out[4 * i + 2] = dq_pair((d1 & 0x000F000Fu) | 0x43004300u, p);
+        out[4 * i + 3] = dq_pair((mulhi_u32(d1, K.k24) & 0x000F000Fu) | 0x43004300u, p);
+        const uint32_t amt = cnt[i] * 4u;
+        if (i < 3) {
+            w0 = funnel_rc(w0, w1, amt);
+            if (i < 2) w1 = funnel_rc(w1, w2, amt);
+            if (i < 1) w2 = funnel_rc(w2, w3, amt);
+        }
     }
 }
 

@@ -1,18 +1,20 @@
 // Decode GEMV for M <= 16 tokens.
 //
-// Work item = (row block of 16 rows, range of column tiles), one item per warp.  Each warp
-// pulls its tiles with 1-D bulk async copies into a private shared-memory ring (mbarrier
-// completion), locates every segment's survivor codes with a popcount prefix sum over the
-// warp, expands them to dense bf16 weights in registers (decode_core.cuh) and contracts them
-// against the activations with mma.sync m16n8k16 (A = 16 rows x 16 columns of weights,
-// B = 16 columns x 8 tokens).  Lane (g = lane/4, t = lane%4) owns rows g and g+8 of the row
-// block and group t of the tile; in MMA step s it supplies columns 4s..4s+3 of that group, so
-// the 16 k-slots of one MMA are 4 consecutive columns from each of the tile's 4 groups and the
-// B fragment of the lane is simply 8 contiguous bytes of x.
+// Persistent kernel, one CTA per SM.  The tiles of the matrix (row-block-major) are cut into
+// one contiguous range per warp, balanced to +-1 tile over all warps of the grid, so every SM
+// gets the same share whatever the matrix shape.  Each warp pulls its tiles with 1-D bulk async
+// copies into a private shared-memory ring (mbarrier completion), locates every segment's
+// survivor codes with a popcount prefix sum over the warp, expands them to dense bf16 weights
+// in registers (decode_core.cuh) and contracts them against the activations with mma.sync
+// m16n8k16 (A = 16 rows x 16 columns of weights, B = 16 columns x 8 tokens).  Lane
+// (g = lane/4, t = lane%4) owns rows g and g+8 of the row block and group t of the tile; in
+// MMA step s it supplies columns 4s..4s+3 of that group, so the 16 k-slots of one MMA are 4
+// consecutive columns from each of the tile's 4 groups and the B fragment of the lane is
+// simply 8 contiguous bytes of x.
 //
-// When a row block is split over several warps every warp stores its fp32 fragment to
-// scratch; the last one to arrive (per-row-block counter) adds the fragments in split order,
-// so the result does not depend on timing.
+// A row block that is covered by several warps is finished by the last warp to arrive
+// (per-row-block counter): it adds the fp32 fragments of all its parts in range order, so the
+// result does not depend on timing.
 //
 // Behaviour replaced: cbk::gemv_sparse / gemv_sparse_expand, one warp per row with a 32-lane
 // prefix scan per 1024-column window (src/cobaltkernel/csrc/cobalt_gemv.cuh:216-393).
@@ -33,9 +35,13 @@ struct GemvParams {
     uint16_t* y; int64_t ldy;
     const uint16_t* bias;
     int M;
-    int splits, tiles_per_split, stages;
+    int stages;
     uint32_t slot_bytes, nib_bytes;
-    float* partials; uint32_t* counters; uint32_t* status;
+    uint32_t total_warps;                // grid * GEMV_WARPS
+    float* partials;                     // [total_warps][2][4 * MT * 32]
+    uint32_t* counters;                  // [row blocks]
+    uint32_t* status;
+    FastConsts K;
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -53,6 +59,14 @@ __device__ __forceinline__ uint16_t finish_output(float acc, const uint16_t* bia
     return r;
 }
 
+// Read-only 16-byte load kept in program order with the shared-memory loads of the decoder, so
+// that it is issued before the decode of the word it belongs to and its latency hides behind it.
+__device__ __forceinline__ uint4 ldg_nc_early(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 // nibble stream window of one 32-column word: 128 bits starting at nibble `nib_off`
 __device__ __forceinline__ void load_window(uint32_t cbase, uint32_t nib_off, uint32_t& w0, uint32_t& w1,
                                             uint32_t& w2, uint32_t& w3) {
@@ -62,6 +76,10 @@ __device__ __forceinline__ void load_window(uint32_t cbase, uint32_t nib_off, ui
     const uint32_t o = bitpos & 31u;
     w0 = funnel_r(r0, r1, o); w1 = funnel_r(r1, r2, o); w2 = funnel_r(r2, r3, o); w3 = funnel_r(r3, r4, o);
 }
+
+// first tile of warp gw / warp that owns tile tau, for the balanced contiguous partition
+__device__ __forceinline__ uint32_t range_start(uint32_t gw, uint32_t T, uint32_t Wt) { return (uint32_t)(((uint64_t)gw * T) / Wt); }
+__device__ __forceinline__ uint32_t tile_owner(uint32_t tau, uint32_t T, uint32_t Wt) { return ((tau + 1u) * Wt - 1u) / T; }
 
 template <int BITS, int MT>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvParams P) {
@@ -81,24 +99,29 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     fence_proxy_async();
     __syncthreads();
 
-    const int item = blockIdx.x * GEMV_WARPS + warp;
-    const bool has_work = item < W.RB * P.splits;
-    const int rb = has_work ? item / P.splits : 0, sp = has_work ? item % P.splits : 0;
-    const int ct0 = sp * P.tiles_per_split;
-    int ct1 = ct0 + P.tiles_per_split;
-    if (ct1 > W.CT) ct1 = W.CT;
-    const int n = has_work ? ct1 - ct0 : 0;                           // 1..31 tiles
+    const uint32_t T = (uint32_t)W.RB * (uint32_t)W.CT, Wt = P.total_warps;
+    const uint32_t gw = blockIdx.x * GEMV_WARPS + warp;
+    const uint32_t t0 = range_start(gw, T, Wt), t1 = range_start(gw + 1, T, Wt);
+    const int n = (int)(t1 - t0);
 
     const uint32_t per_warp = P.stages * P.slot_bytes + P.nib_bytes;
     const uint32_t ring = smem_u32(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES) + warp * per_warp;
     const uint32_t nib = ring + P.stages * P.slot_bytes;
-    const LutEntry* lut_lane = lut_s + (lane & (LUT_COPIES - 1));
+    const uint32_t lut_lane = smem_u32(smem) + (uint32_t)(lane & (LUT_COPIES - 1)) * 8u;
+    const LutEntry* lut_lane_ptr = lut_s + (lane & (LUT_COPIES - 1));
 
-    // tile offsets of this warp's range, one per lane
-    const uint32_t my_off = (has_work && lane <= n) ? W.tile_off[rb * W.CT + ct0 + lane] : 0u;
+    // offsets of the first 32 tile boundaries of the range, one per lane
+    const uint32_t my_off = (lane <= n) ? W.tile_off[t0 + lane] : 0u;
 
     auto issue = [&](int i) {                                          // all lanes call; lane 0 acts
-        const uint32_t o0 = __shfl_sync(full, my_off, i), o1 = __shfl_sync(full, my_off, i + 1);
+        uint32_t o0, o1;
+        if (i < 31) {
+            o0 = __shfl_sync(full, my_off, i);
+            o1 = __shfl_sync(full, my_off, i + 1);
+        } else {
+            o0 = W.tile_off[t0 + i];
+            o1 = W.tile_off[t0 + i + 1];
+        }
         if (lane == 0) {
             const uint32_t bytes = (o1 - o0) * 16u;
             const uint32_t bar = bar0 + 8 * (i % P.stages);
@@ -113,20 +136,78 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 
     for (int i = threadIdx.x; i < LUT_ENTRIES * LUT_COPIES; i += GEMV_THREADS) lut_s[i] = g_lut.e[i / LUT_COPIES];
     __syncthreads();
-    if (!has_work) return;
+    if (n == 0) return;
 
     float acc[MT][4];
 #pragma unroll
     for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
 
+    // ---- finish one row block: direct store, or deterministic reduction by the last arriver
+    auto flush = [&](int rb) {
+        const uint32_t first = (uint32_t)rb * W.CT, last = first + W.CT - 1;
+        const int row0 = rb * TILE_ROWS + g, row1 = row0 + 8;
+        const bool whole = (t0 <= first) && (t1 > last);
+        if (!whole) {
+            const uint32_t myslot = gw * 2u + (t0 >= first ? 0u : 1u);
+            float* mine = P.partials + (size_t)myslot * (4 * MT * 32);
+#pragma unroll
+            for (int b = 0; b < MT; ++b)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
+            __threadfence();
+            __syncwarp();
+            const uint32_t nparts = (T < Wt) ? (uint32_t)W.CT : tile_owner(last, T, Wt) - tile_owner(first, T, Wt) + 1u;
+            uint32_t old = 0;
+            if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
+            old = __shfl_sync(full, old, 0);
+            if (old != nparts - 1u) return;
+            __threadfence();
+#pragma unroll
+            for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+            uint32_t prev = 0xFFFFFFFFu;
+            for (uint32_t tau = first; tau <= last; ++tau) {           // parts in range order
+                const uint32_t o = tile_owner(tau, T, Wt);
+                if (o == prev) continue;
+                prev = o;
+                const uint32_t slot = o * 2u + (range_start(o, T, Wt) >= first ? 0u : 1u);
+                const float* src = P.partials + (size_t)slot * (4 * MT * 32);
+#pragma unroll
+                for (int b = 0; b < MT; ++b)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[b][r] += __ldcg(src + (b * 4 + r) * 32 + lane);
+            }
+            if (lane == 0) P.counters[rb] = 0u;
+        }
+#pragma unroll
+        for (int b = 0; b < MT; ++b) {
+            const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
+            if (row0 < W.K) {
+                if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row0] = finish_output(acc[b][0], P.bias, row0);
+                if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row0] = finish_output(acc[b][1], P.bias, row0);
+            }
+            if (row1 < W.K) {
+                if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row1] = finish_output(acc[b][2], P.bias, row1);
+                if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row1] = finish_output(acc[b][3], P.bias, row1);
+            }
+        }
+    };
+
     bool healthy = true;
+    int cur_rb = (int)(t0 / (uint32_t)W.CT);
+    int rb = cur_rb, ct = (int)(t0 - (uint32_t)cur_rb * W.CT) - 1;      // advanced at the top of every iteration
     for (int i = 0; i < issued; ++i) {
         const int st = i % P.stages;
         const bool ok = mbar_wait_bounded(bar0 + 8 * st, (uint32_t)(i / P.stages) & 1u, P.status, DEV_TIMEOUT_TILE);
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
-        const int ct = ct0 + i;
+        if (++ct == W.CT) { ct = 0; ++rb; }
+        if (rb != cur_rb) {
+            flush(cur_rb);
+#pragma unroll
+            for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+            cur_rb = rb;
+        }
         const int w = tile_width(W, ct);
         const bool active = t < w;
         const uint32_t slot = ring + st * P.slot_bytes;
@@ -173,46 +254,61 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 
         const SegParams pA = make_seg_params(szA, BITS, W.col_scale != nullptr);
         const SegParams pB = make_seg_params(szB, BITS, W.col_scale != nullptr);
+        const bool all_fast = __all_sync(full, pA.fast && pB.fast);
         const int col0 = (ct * TILE_GROUPS + t) * GROUP;               // first column of this lane's group
+        const uint16_t* xbase = P.x + col0;
 
 #pragma unroll 1
         for (int j = 0; j < 4; ++j) {
             const uint32_t mAj = mA.x, mBj = mB.x;                     // rotate instead of indexing registers
             mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
             mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
-            uint32_t ea[16], eb[16];
-            float cs[32];
-            const float* csp = nullptr;
-            if (W.col_scale != nullptr && active) {
+            // activations of this 32-column word first, so that their latency hides behind the decode
+            uint4 xv[MT][4];
 #pragma unroll
-                for (int q = 0; q < 32; ++q) cs[q] = half_bits_to_float(W.col_scale[col0 + 32 * j + q]);
-                csp = cs;
+            for (int b = 0; b < MT; ++b) {
+                const int tok = g + 8 * b;
+                xv[b][0] = xv[b][1] = xv[b][2] = xv[b][3] = make_uint4(0, 0, 0, 0);
+                if (active && tok < P.M) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(xbase + (size_t)tok * P.ldx + 32 * j);
+                    xv[b][0] = ldg_nc_early(xp); xv[b][1] = ldg_nc_early(xp + 1);
+                    xv[b][2] = ldg_nc_early(xp + 2); xv[b][3] = ldg_nc_early(xp + 3);
+                }
             }
-            {
-                uint32_t w0, w1, w2, w3;
-                load_window(cbase, offA, w0, w1, w2, w3);
-                decode32<LUT_COPIES>(mAj, w0, w1, w2, w3, pA, lut_lane, csp, ea);
-                load_window(cbase, offB, w0, w1, w2, w3);
-                decode32<LUT_COPIES>(mBj, w0, w1, w2, w3, pB, lut_lane, csp, eb);
+            uint32_t ea[16], eb[16];
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            load_window(cbase, offA, a0, a1, a2, a3);
+            load_window(cbase, offB, b0, b1, b2, b3);
+            if (all_fast) {
+                auto lut = [lut_lane](uint32_t idx) {
+                    const uint2 e = lds64(lut_lane + idx * (LUT_COPIES * 8u));
+                    return LutEntry{e.x, e.y};
+                };
+                decode32_fast(mAj, a0, a1, a2, a3, pA, P.K, lut, ea);
+                decode32_fast(mBj, b0, b1, b2, b3, pB, P.K, lut, eb);
+            } else {
+                float cs[32];
+                const float* csp = nullptr;
+                if (W.col_scale != nullptr && active) {
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) cs[q] = half_bits_to_float(W.col_scale[col0 + 32 * j + q]);
+                    csp = cs;
+                }
+                decode32<LUT_COPIES>(mAj, a0, a1, a2, a3, pA, lut_lane_ptr, csp, ea);
+                decode32<LUT_COPIES>(mBj, b0, b1, b2, b3, pB, lut_lane_ptr, csp, eb);
             }
             offA += __popc(mAj);
             offB += __popc(mBj);
 #pragma unroll
             for (int b = 0; b < MT; ++b) {
-                const int tok = g + 8 * b;
-                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, x2 = x0, x3 = x0;
-                if (active && tok < P.M) {
-                    const uint4* xp = reinterpret_cast<const uint4*>(P.x + (size_t)tok * P.ldx + col0 + 32 * j);
-                    x0 = __ldg(xp); x1 = __ldg(xp + 1); x2 = __ldg(xp + 2); x3 = __ldg(xp + 3);
-                }
-                mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], x0.x, x0.y);
-                mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], x0.z, x0.w);
-                mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], x1.x, x1.y);
-                mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], x1.z, x1.w);
-                mma_bf16_16816(acc[b], ea[8], eb[8], ea[9], eb[9], x2.x, x2.y);
-                mma_bf16_16816(acc[b], ea[10], eb[10], ea[11], eb[11], x2.z, x2.w);
-                mma_bf16_16816(acc[b], ea[12], eb[12], ea[13], eb[13], x3.x, x3.y);
-                mma_bf16_16816(acc[b], ea[14], eb[14], ea[15], eb[15], x3.z, x3.w);
+                mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);
+                mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], xv[b][0].z, xv[b][0].w);
+                mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], xv[b][1].x, xv[b][1].y);
+                mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], xv[b][1].z, xv[b][1].w);
+                mma_bf16_16816(acc[b], ea[8], eb[8], ea[9], eb[9], xv[b][2].x, xv[b][2].y);
+                mma_bf16_16816(acc[b], ea[10], eb[10], ea[11], eb[11], xv[b][2].z, xv[b][2].w);
+                mma_bf16_16816(acc[b], ea[12], eb[12], ea[13], eb[13], xv[b][3].x, xv[b][3].y);
+                mma_bf16_16816(acc[b], ea[14], eb[14], ea[15], eb[15], xv[b][3].z, xv[b][3].w);
             }
         }
 
@@ -220,45 +316,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         if (issued < n) { issue(issued); ++issued; }
     }
     if (!healthy) return;
-
-    // ---- finish: direct store, or deterministic split reduction by the last arriver
-    const int row0 = rb * TILE_ROWS + g, row1 = row0 + 8;
-    if (P.splits > 1) {
-        float* mine = P.partials + (size_t)item * (4 * MT * 32);
-#pragma unroll
-        for (int b = 0; b < MT; ++b)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
-        __threadfence();
-        __syncwarp();
-        uint32_t old = 0;
-        if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
-        old = __shfl_sync(full, old, 0);
-        if (old != (uint32_t)(P.splits - 1)) return;
-        __threadfence();
-        const float* base = P.partials + (size_t)rb * P.splits * (4 * MT * 32);
-#pragma unroll
-        for (int b = 0; b < MT; ++b)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                float s = 0.0f;
-                for (int k = 0; k < P.splits; ++k) s += __ldcg(base + (size_t)k * (4 * MT * 32) + (b * 4 + r) * 32 + lane);
-                acc[b][r] = s;
-            }
-        if (lane == 0) P.counters[rb] = 0u;
-    }
-#pragma unroll
-    for (int b = 0; b < MT; ++b) {
-        const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
-        if (row0 < W.K) {
-            if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row0] = finish_output(acc[b][0], P.bias, row0);
-            if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row0] = finish_output(acc[b][1], P.bias, row0);
-        }
-        if (row1 < W.K) {
-            if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row1] = finish_output(acc[b][2], P.bias, row1);
-            if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row1] = finish_output(acc[b][3], P.bias, row1);
-        }
-    }
+    flush(cur_rb);
 }
 
 }  // namespace cb

@@ -46,6 +46,7 @@ class TileImage:
     n_col_tiles: int
     header_bytes: int
     max_tile_bytes: int
+    max_tile_nnz: int = TILE_ROWS * TILE_GROUPS * GROUP
 
     @property
     def n_tiles(self) -> int:
@@ -54,14 +55,15 @@ class TileImage:
     def meta(self) -> dict:
         return dict(K=self.K, N=self.N, bits=self.bits, nnz=self.nnz, n_row_blocks=self.n_row_blocks,
                     n_col_tiles=self.n_col_tiles, header_bytes=self.header_bytes,
-                    max_tile_bytes=self.max_tile_bytes, group_size=GROUP)
+                    max_tile_bytes=self.max_tile_bytes, max_tile_nnz=self.max_tile_nnz, group_size=GROUP)
 
     @staticmethod
     def from_meta(blob: torch.Tensor, meta: dict) -> "TileImage":
         return TileImage(blob=blob, K=int(meta["K"]), N=int(meta["N"]), bits=int(meta["bits"]),
                          nnz=int(meta["nnz"]), n_row_blocks=int(meta["n_row_blocks"]),
                          n_col_tiles=int(meta["n_col_tiles"]), header_bytes=int(meta["header_bytes"]),
-                         max_tile_bytes=int(meta["max_tile_bytes"]))
+                         max_tile_bytes=int(meta["max_tile_bytes"]),
+                         max_tile_nnz=int(meta.get("max_tile_nnz", TILE_ROWS * TILE_GROUPS * GROUP)))
 
     def algorithmic_bytes(self) -> int:
         """Bitmask + codes + fp16 scale/zero, without padding or the offset table."""
@@ -172,7 +174,8 @@ def pack_tiles(keep: torch.Tensor, q: torch.Tensor, scale: torch.Tensor, zero: t
     blob32 = torch.where(blob >= 2 ** 31, blob - 2 ** 32, blob).to(torch.int32)
     blob8 = blob32.view(torch.uint8).clone()
     return TileImage(blob=blob8, K=K, N=N, bits=bits, nnz=nnz, n_row_blocks=RB, n_col_tiles=CT,
-                     header_bytes=header_bytes, max_tile_bytes=int(tb_flat.max()))
+                     header_bytes=header_bytes, max_tile_bytes=int(tb_flat.max()),
+                     max_tile_nnz=int(nnz_tile.max()))
 
 
 def bytes_to_keep(mask_u8: torch.Tensor, N: int) -> torch.Tensor:

@@ -104,6 +104,7 @@ class CobaltSparseLinear(nn.Module):
             d.K, d.N, d.bits, d.group = m["K"], m["N"], m["bits"], GROUP
             d.n_row_blocks, d.n_col_tiles = m["n_row_blocks"], m["n_col_tiles"]
             d.max_tile_bytes = m["max_tile_bytes"]
+            d.max_tile_nnz = m.get("max_tile_nnz", 8192)
             d.nnz = m["nnz"]
             self._desc, self._desc_key = d, key
         return self._desc

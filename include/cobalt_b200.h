@@ -56,7 +56,7 @@ typedef struct CobaltMat {
     int32_t n_row_blocks;           /* ceil(K / 16) */
     int32_t n_col_tiles;            /* ceil(N / 512) */
     uint32_t max_tile_bytes;        /* largest tile of this matrix */
-    uint32_t reserved;
+    uint32_t max_tile_nnz;          /* most survivors in one tile */
     int64_t nnz;                    /* number of survivors */
 } CobaltMat;
 
@@ -116,8 +116,8 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
  * word at the start of `scratch` region reserved for it; synchronises `stream`. */
 int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out);
 
-/* Benchmark tuning hook (not part of the stable contract): key 0 = GEMV column tiles per work
- * item, 1 = GEMV ring stages, 2 = GEMM operand stages; value 0 restores the built-in heuristic.
+/* Benchmark tuning hook (not part of the stable contract): key 0 = GEMV grid size
+ * (CTAs), 1 = GEMV ring stages, 2 = GEMM operand stages; value 0 restores the built-in heuristic.
  * No counterpart in the reference, whose knobs are compile-time macros (src/cobaltkernel/runner.py:52-206). */
 int cobalt_set_tuning(int key, int value);
 

@@ -89,6 +89,16 @@ int main() {
         for (int b = 0; b < 32; ++b) cs[b] = half_bits_to_float(float_to_half_bits(0.5f + (rng() % 1500) / 1000.0f));
         uint32_t out[16];
         decode32<LUT_COPIES>(m, w[0], w[1], w[2], w[3], p, lut.data() + (iter % LUT_COPIES), use_cs ? cs : nullptr, out);
+        if (p.fast) {                                   // the fast variant must agree with the generic one
+            uint32_t out2[16];
+            FastConsts K{1u << 28, 1u << 24, 1u << 29};
+            const LutEntry* lp = lut.data() + (iter % LUT_COPIES);
+            decode32_fast(m, w[0], w[1], w[2], w[3], p, K, [lp](uint32_t i) { return lp[i * LUT_COPIES]; }, out2);
+            for (int k = 0; k < 16; ++k) if (out2[k] != out[k]) {
+                if (fails < 10) printf("decode32_fast mismatch iter=%d k=%d m=%08x got %08x want %08x\n", iter, k, m, out2[k], out[k]);
+                ++fails;
+            }
+        }
         for (int b = 0; b < 32; ++b) {
             uint32_t got = (out[b / 2] >> (16 * (b & 1))) & 0xFFFFu;
             float keepf = (float)((m >> b) & 1);

@@ -141,6 +141,53 @@ def main():
     dig["config1"] = dict(K=K, N=N, bits=3, sparsity=0.7, beta=0.5, seed=1, nnz=int(keep.sum()),
                           keep=sha(keep.bool()), q=sha(q.to(torch.uint8)), scale=sha(sc.half()),
                           zero=sha(zr.half()))
+    # tiny random Mistral-shaped model through the reference's executable spec
+    # (src/cobaltkernel/ref_llama.py): logits of a prefill and greedy continuation
+    import ref_llama as RL
+    mcfg = dict(model_type="mistral", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=320,
+                rms_norm_eps=1e-5, rope_theta=1e6)
+    g = torch.Generator().manual_seed(2024)
+    Wm = {}
+
+    def rnd(*shape, std=0.05):
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+    Wm["model.embed_tokens.weight"] = rnd(320, 256, std=1.0)
+    Wm["lm_head.weight"] = rnd(320, 256)
+    Wm["model.norm.weight"] = (1.0 + 0.1 * torch.randn(256, generator=g)).to(torch.bfloat16)
+    for i in range(2):
+        pfx = f"model.layers.{i}."
+        Wm[pfx + "input_layernorm.weight"] = (1.0 + 0.1 * torch.randn(256, generator=g)).to(torch.bfloat16)
+        Wm[pfx + "post_attention_layernorm.weight"] = (1.0 + 0.1 * torch.randn(256, generator=g)).to(torch.bfloat16)
+        Wm[pfx + "self_attn.q_proj.weight"] = rnd(256, 256)
+        Wm[pfx + "self_attn.k_proj.weight"] = rnd(128, 256)
+        Wm[pfx + "self_attn.v_proj.weight"] = rnd(128, 256)
+        Wm[pfx + "self_attn.o_proj.weight"] = rnd(256, 256)
+        Wm[pfx + "mlp.gate_proj.weight"] = rnd(512, 256)
+        Wm[pfx + "mlp.up_proj.weight"] = rnd(512, 256)
+        Wm[pfx + "mlp.down_proj.weight"] = rnd(256, 512)
+    rcfg = RL.LlamaRefConfig(mcfg)
+    state = {"cfg": rcfg, "W": Wm, "device": "cpu", "dtype": torch.bfloat16,
+             "rope": {lt: RL._inv_freq(rcfg.rope_theta, rcfg.head_dim, "cpu") for lt in set(rcfg.layer_types)}}
+    ids = torch.randint(0, 320, (12,), generator=g)
+    logits, kvs = RL.prefill(state, ids)
+    toks, step_logits = [], []
+    last = logits[0, -1]
+    pos = 12
+    for _ in range(6):
+        t = int(last.float().argmax())
+        toks.append(t)
+        last = RL.forward_step(state, t, pos, kvs)
+        step_logits.append(bf16_bits(last))
+        pos += 1
+    mout = {k: (bf16_bits(v)) for k, v in Wm.items()}
+    mout["__ids"] = ids.numpy()
+    mout["__prefill_logits"] = bf16_bits(logits[0])
+    mout["__tokens"] = np.array(toks)
+    mout["__step_logits"] = np.stack(step_logits)
+    np.savez_compressed(os.path.join(HERE, "golden_model.npz"), **mout)
+    dig["model_cfg"] = mcfg
+
     with open(os.path.join(HERE, "golden_digests.json"), "w") as f:
         json.dump(dig, f, indent=1)
     print("wrote", len(out), "arrays")

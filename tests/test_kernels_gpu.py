@@ -5,8 +5,11 @@ Bars
   * layer outputs in bf16: rel-L2 <= 1e-3 and max-abs <= 1e-2 against the oracle's CPU result.
     bf16 values at |y| >= 2 are 2^-6 = 0.0156 apart, so two correct fp32 accumulations that
     straddle a rounding boundary differ by more than 1e-2 there.  An element may exceed 1e-2
-    only if it is such a case: the oracle's value and ours must both lie within half a bf16
-    spacing (+0.2 %) of the exact fp64 dot product of the same bf16 weights and activations.
+    only if it is such a case: the oracle's value and ours must both lie within 0.52 bf16
+    spacings of the exact fp64 dot product of the same bf16 weights and activations (half a
+    spacing for the final rounding plus 2 % of a spacing, about 8e-5 relative, for the fp32
+    accumulation: the tensor cores truncate when they align addends, which over 14336 columns
+    was measured at up to 5e-5 relative).
 """
 import numpy as np
 import pytest
@@ -39,7 +42,7 @@ def check_output(y: torch.Tensor, y_ref: torch.Tensor, y_exact: torch.Tensor):
         ex = y_exact.double()[bad]
         for name, val in (("ours", y.double()[bad]), ("oracle", y_ref.double()[bad])):
             err = (val - ex).abs()
-            lim = 0.5 * bf16_spacing(val) * 1.002
+            lim = 0.52 * bf16_spacing(val)
             assert bool((err <= lim).all()), f"{name}: {int(bad.sum())} elements off by more than {MAX_ABS} and not a rounding-boundary case"
     return rel, float(d.max())
 
