@@ -158,6 +158,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
     M = args.tokens
+    if args.debug_flags:
+        lib.cobalt_set_tuning(3, args.debug_flags)
 
     global SHAPES_7B
     if args.shapes:
@@ -396,6 +398,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=1, help="decode batch M (1..16)")
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
+    ap.add_argument("--debug-flags", type=int, default=0, help="kernel experiment switches (results become invalid)")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")
     args = ap.parse_args()

@@ -22,6 +22,7 @@ bool g_dev_known[MAX_DEVICES];
 int g_tune_tiles_per_split = 0;     // 0 = heuristic
 int g_tune_gemv_stages = 0;
 int g_tune_gemm_stages = 0;
+int g_debug_flags = 0;
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -148,6 +149,55 @@ int launch_gemm(const GemmParams& P, const GemmCfg& c, dim3 grid, cudaStream_t s
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
+// shared body of cobalt_gemv() and cobalt_gemv_static()
+int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+              void* scratch, size_t scratch_bytes, bool clear_counters, void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (M > MAX_GEMV_M) return COBALT_EINVAL;
+    rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    GemvCfg c;
+    rc = gemv_config(w, M, sms, &c);
+    if (rc) return rc;
+    if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (clear_counters) {
+        // the status word and the per-row-block arrival counters must start at zero; the partial
+        // sums behind them are always written before they are read
+        if (cudaMemsetAsync(scratch, 0, c.partials_off, st) != cudaSuccess) return COBALT_ELAUNCH;
+    }
+    GemvParams P;
+    P.W = make_view(w);
+    P.x = (const uint16_t*)x; P.ldx = ldx;
+    P.y = (uint16_t*)y; P.ldy = ldy;
+    P.bias = (const uint16_t*)bias;
+    P.M = M;
+    P.stages = c.stages;
+    P.slot_bytes = c.slot; P.nib_bytes = c.nib;
+    P.total_warps = c.total_warps;
+    P.debug = (uint32_t)g_debug_flags;
+    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k29 = 1u << 29;
+    P.status = (uint32_t*)scratch;
+    P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
+    P.partials = (float*)((uint8_t*)scratch + c.partials_off);
+    if (c.mt == 1) {
+        switch (w->bits) {
+            case 2: return launch_gemv<2, 1>(P, c, st);
+            case 3: return launch_gemv<3, 1>(P, c, st);
+            default: return launch_gemv<4, 1>(P, c, st);
+        }
+    }
+    switch (w->bits) {
+        case 2: return launch_gemv<2, 2>(P, c, st);
+        case 3: return launch_gemv<3, 2>(P, c, st);
+        default: return launch_gemv<4, 2>(P, c, st);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -175,6 +225,7 @@ int cobalt_set_tuning(int key, int value) {
         case 0: g_tune_tiles_per_split = value; return COBALT_OK;
         case 1: g_tune_gemv_stages = value; return COBALT_OK;
         case 2: g_tune_gemm_stages = value; return COBALT_OK;
+        case 3: g_debug_flags = value; return COBALT_OK;
         default: return COBALT_EINVAL;
     }
 }
@@ -190,44 +241,7 @@ size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M) {
 
 int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
                 void* scratch, size_t scratch_bytes, void* stream) {
-    int rc = check_mat(w);
-    if (rc) return rc;
-    if (M > MAX_GEMV_M) return COBALT_EINVAL;
-    rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
-    if (rc) return rc;
-    int sms = 0;
-    rc = device_info(&sms);
-    if (rc) return rc;
-    GemvCfg c;
-    rc = gemv_config(w, M, sms, &c);
-    if (rc) return rc;
-    if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
-    GemvParams P;
-    P.W = make_view(w);
-    P.x = (const uint16_t*)x; P.ldx = ldx;
-    P.y = (uint16_t*)y; P.ldy = ldy;
-    P.bias = (const uint16_t*)bias;
-    P.M = M;
-    P.stages = c.stages;
-    P.slot_bytes = c.slot; P.nib_bytes = c.nib;
-    P.total_warps = c.total_warps;
-    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k29 = 1u << 29;
-    P.status = (uint32_t*)scratch;
-    P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
-    P.partials = (float*)((uint8_t*)scratch + c.partials_off);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (c.mt == 1) {
-        switch (w->bits) {
-            case 2: return launch_gemv<2, 1>(P, c, st);
-            case 3: return launch_gemv<3, 1>(P, c, st);
-            default: return launch_gemv<4, 1>(P, c, st);
-        }
-    }
-    switch (w->bits) {
-        case 2: return launch_gemv<2, 2>(P, c, st);
-        case 3: return launch_gemv<3, 2>(P, c, st);
-        default: return launch_gemv<4, 2>(P, c, st);
-    }
+    return gemv_impl(w, x, ldx, y, ldy, bias, M, scratch, scratch_bytes, /*clear_counters=*/false, stream);
 }
 
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,

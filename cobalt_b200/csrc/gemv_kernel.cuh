@@ -42,6 +42,7 @@ struct GemvParams {
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
     FastConsts K;
+    uint32_t debug;                      // experiments only: bit0 skip x loads, bit1 skip flush, bit2 skip MMA
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     // offsets of the first 32 tile boundaries of the range, one per lane
     const uint32_t my_off = (lane <= n) ? W.tile_off[t0 + lane] : 0u;
 
-    auto issue = [&](int i) {                                          // all lanes call; lane 0 acts
+    auto issue = [&](int i, int slot_idx) {                            // all lanes call; lane 0 acts
         uint32_t o0, o1;
         if (i < 31) {
             o0 = __shfl_sync(full, my_off, i);
@@ -124,15 +125,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         }
         if (lane == 0) {
             const uint32_t bytes = (o1 - o0) * 16u;
-            const uint32_t bar = bar0 + 8 * (i % P.stages);
+            const uint32_t bar = bar0 + 8 * slot_idx;
             fence_proxy_async();
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_g2s(ring + (i % P.stages) * P.slot_bytes, W.tiles + (size_t)o0 * 16, bytes, bar);
+            bulk_g2s(ring + slot_idx * P.slot_bytes, W.tiles + (size_t)o0 * 16, bytes, bar);
         }
     };
 
     int issued = n < P.stages ? n : P.stages;
-    for (int i = 0; i < issued; ++i) issue(i);
+    for (int i = 0; i < issued; ++i) issue(i, i);
 
     for (int i = threadIdx.x; i < LUT_ENTRIES * LUT_COPIES; i += GEMV_THREADS) lut_s[i] = g_lut.e[i / LUT_COPIES];
     __syncthreads();
@@ -193,17 +194,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     };
 
     bool healthy = true;
+    int st = -1;                                                      // ring slot and phase parity of tile i
+    uint32_t par = 0;
     int cur_rb = (int)(t0 / (uint32_t)W.CT);
     int rb = cur_rb, ct = (int)(t0 - (uint32_t)cur_rb * W.CT) - 1;      // advanced at the top of every iteration
     for (int i = 0; i < issued; ++i) {
-        const int st = i % P.stages;
-        const bool ok = mbar_wait_bounded(bar0 + 8 * st, (uint32_t)(i / P.stages) & 1u, P.status, DEV_TIMEOUT_TILE);
+        if (++st == P.stages) { st = 0; par ^= 1u; }
+        const bool ok = mbar_wait_bounded(bar0 + 8 * st, par, P.status, DEV_TIMEOUT_TILE);
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
         if (++ct == W.CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {
-            flush(cur_rb);
+            if (!(P.debug & 2u)) flush(cur_rb);
 #pragma unroll
             for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
             cur_rb = rb;
@@ -269,7 +272,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             for (int b = 0; b < MT; ++b) {
                 const int tok = g + 8 * b;
                 xv[b][0] = xv[b][1] = xv[b][2] = xv[b][3] = make_uint4(0, 0, 0, 0);
-                if (active && tok < P.M) {
+                if (active && tok < P.M && !(P.debug & 1u)) {
                     const uint4* xp = reinterpret_cast<const uint4*>(xbase + (size_t)tok * P.ldx + 32 * j);
                     xv[b][0] = ldg_nc_early(xp); xv[b][1] = ldg_nc_early(xp + 1);
                     xv[b][2] = ldg_nc_early(xp + 2); xv[b][3] = ldg_nc_early(xp + 3);
@@ -299,6 +302,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             }
             offA += __popc(mAj);
             offB += __popc(mBj);
+            if (P.debug & 4u) { acc[0][0] += __uint_as_float(ea[0] ^ eb[3] ^ ea[7] ^ eb[12] ^ ea[15] ^ eb[9]); continue; }
 #pragma unroll
             for (int b = 0; b < MT; ++b) {
                 mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);
@@ -313,10 +317,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         }
 
         __syncwarp();
-        if (issued < n) { issue(issued); ++issued; }
+        if (issued < n) { issue(issued, st); ++issued; }       // tile i + stages reuses the slot just drained
     }
     if (!healthy) return;
-    flush(cur_rb);
+    if (!(P.debug & 2u)) flush(cur_rb);
 }
 
 }  // namespace cb
