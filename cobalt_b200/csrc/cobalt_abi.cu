@@ -244,6 +244,36 @@ int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
     return gemv_impl(w, x, ldx, y, ldy, bias, M, scratch, scratch_bytes, /*clear_counters=*/false, stream);
 }
 
+// ---- allocation-free variant: scratch lives in a file-scope device array ---------------------
+// One array per GPU that loads the library (held until the process exits).  Host code only ever
+// sees the array's host-side stand-in, so its device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current.
+static __device__ __align__(256) unsigned char g_static_scratch[COBALT_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_ptr[MAX_DEVICES];
+
+int cobalt_gemv_static(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+                       void* stream) {
+    int rc = check_mat(w);
+    if (rc) return rc;
+    if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    GemvCfg c;
+    rc = gemv_config(w, M, sms, &c);
+    if (rc) return rc;
+    if (c.total > (size_t)COBALT_STATIC_SCRATCH_BYTES) return COBALT_ETOOBIG;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return COBALT_ELAUNCH;
+    if (!g_static_scratch_ptr[dev]) {                    // first call on this device: resolve the symbol
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return COBALT_ELAUNCH;
+        g_static_scratch_ptr[dev] = p;
+    }
+    return gemv_impl(w, x, ldx, y, ldy, bias, M, g_static_scratch_ptr[dev], COBALT_STATIC_SCRATCH_BYTES,
+                     /*clear_counters=*/true, stream);
+}
+
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
                         void* stream) {
     int rc = check_mat(w);

@@ -77,6 +77,34 @@ int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
                 const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
 size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M);
 
+/* cobalt_gemv() for callers that must not allocate device memory.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- a plug-in inside a serving
+ * process whose memory pool is frozen after start-up, a real-time loop that cannot afford the
+ * device-wide synchronisation an allocation implies, a host that hands this library raw pointers
+ * from its own arena and forbids any other device allocation, or a process running so close to
+ * the memory limit that an extra allocation may simply fail.  Such callers cannot size and own the scratch buffer that
+ * cobalt_gemv() asks for, so this variant brings its own: a fixed
+ * COBALT_STATIC_SCRATCH_BYTES array that is part of the library image on every GPU that
+ * loads it, from load until the process exits.  Inputs and outputs are still the caller's.
+ *
+ *   - Same arguments (minus scratch), same kernel and bit-identical results as cobalt_gemv().
+ *   - A matrix whose split-K bookkeeping does not fit the array is refused with
+ *     COBALT_ETOOBIG; nothing is launched.  (The need grows with the number of row blocks;
+ *     every 7B- and 27B-class projection, 262144-row heads included, fits.)
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on
+ *     each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) -- make that first call outside any stream capture.
+ *   - All calls on one GPU share the one array, and it keeps what the previous call left.  The
+ *     entry point therefore zeroes the status word and the arrival counters on `stream` before
+ *     every launch (cudaMemsetAsync, not an allocation).  Two calls that overlap on the GPU --
+ *     different streams, or concurrent graph branches -- race on the array and produce wrong
+ *     results; serialise them on one stream.
+ * This entry point has no counterpart in the reference. */
+#define COBALT_STATIC_SCRATCH_BYTES (8u << 20)
+int cobalt_gemv_static(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
+                       const void* bias, int M, void* stream);
+
 /* Same contract and results as cobalt_gemv() through a plain one-thread-per-segment kernel
  * (no tensor cores, no bulk copies).  Bring-up and cross-check aid; needs no scratch. */
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
