@@ -389,6 +389,58 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+# ----------------------------------------------------------------------------- prefill sweep (tensor-bound leg)
+def run_prefill(args):
+    """Prefill GEMM sweep on the 7B projection shapes: M in {128, 512, 2048}, 3-bit/70 % and 2-bit/50 %.
+    Prints one JSON line with TFLOP/s (2*M*K*N per launch) per case against the measured bf16 peak.
+    Every timed launch is preceded by an L2 flush (256 MB written) and timed with its own event pair."""
+    from cobalt_b200 import CobaltSparseLinear, SparseQuantConfig, compress_weight
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = json.load(open(p))["bf16_tflops"] if os.path.exists(p) else 1590.0
+    shapes = [("q", 4096, 4096), ("kv", 1024, 4096), ("gate_up", 14336, 4096), ("down", 4096, 14336)]
+    if args.shapes:
+        shapes = [t for t in shapes if t[0] in args.shapes.split(",")]
+    Ms = [int(m) for m in args.prefill_m.split(",")]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    cases = []
+    for bits, sp in ((3, 0.7), (2, 0.5)):
+        for name, K, N in shapes:
+            g = torch.Generator().manual_seed(4000 + bits)
+            W = (torch.randn(K, N, generator=g) * 0.02).half().float().to(dev)
+            norm = (torch.randn(N, generator=g).abs() + 0.1).to(dev)
+            keep, q, sc, zr = compress_weight(W, norm, SparseQuantConfig(bits, sp, 0.5))
+            mod = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": bits})
+            del W, keep, q, sc, zr
+            for M in Ms:
+                x = torch.randn(M, N, device=dev).to(torch.bfloat16)
+                for _ in range(3):
+                    mod(x)
+                times = []
+                for _ in range(args.steps if args.steps < 50 else 10):
+                    flush.fill_(1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    mod(x)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1))
+                times.sort()
+                ms = times[len(times) // 2]
+                tf = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+                cases.append({"shape": name, "K": K, "N": N, "M": M, "bits": bits, "sparsity": sp, "ms": round(ms, 4),
+                              "tflops": round(tf, 1), "frac": round(tf / peak, 4), "status": mod.device_status()})
+            del mod
+            torch.cuda.empty_cache()
+    best = max(cases, key=lambda c: c["tflops"])
+    print(json.dumps({"metric": "prefill GEMM TFLOP/s (dense-equivalent 2*M*K*N)", "unit": "TFLOP/s", "value": best["tflops"],
+                      "roofline": {"bound": "tensor", "achieved": best["tflops"], "peak": peak, "unit": "TFLOP/s",
+                                   "frac": best["frac"], "kernel": "gemm_tcgen05_kernel"},
+                      "config": {"workload": "prefill sweep on Mistral-7B projection shapes", "l2": "256 MB flush before every timed launch"},
+                      "cases": cases}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,13 +448,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=1, help="decode batch M (1..16)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode = headline 7B block GEMV bench; prefill = tcgen05 GEMM sweep (single GPU)")
+    ap.add_argument("--prefill-m", default="128,512,2048")
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--debug-flags", type=int, default=0, help="kernel experiment switches (results become invalid)")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "prefill":
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

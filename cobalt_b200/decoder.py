@@ -1,0 +1,193 @@
+"""Minimal Mistral/Llama-shaped decoder that calls the compressed linears.
+
+This is the caller side of the hot path (the seven projections of every block), kept in
+plain PyTorch: RMSNorm, RoPE, grouped-query attention over a preallocated KV cache, SwiGLU,
+residual adds, a dense ``lm_head`` (the reference leaves ``lm_head`` uncompressed:
+sinq/patch_model.py:49).  The dtype policy follows the reference's executable spec
+src/cobaltkernel/ref_llama.py:10-16, 82-143: fp32 normalise -> bf16 -> times w; bf16 RoPE
+tables; bf16 score/context matmuls with an fp32 softmax cast back to bf16; bf16 residuals.
+
+One decode step has static shapes (attention runs over the whole cache with a position mask;
+token id and position live in device tensors), so ``generate`` captures it once in a CUDA
+graph and replays it per token with no host round trip.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .compress import SparseQuantConfig, compress_weight
+from .linear import CobaltSparseLinear
+
+PROJ = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+        "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
+
+
+def proj_shapes(cfg: dict) -> Dict[str, tuple]:
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    nh, nkv, I = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"]
+    return {"self_attn.q_proj": (nh * D, H), "self_attn.k_proj": (nkv * D, H), "self_attn.v_proj": (nkv * D, H),
+            "self_attn.o_proj": (H, nh * D), "mlp.gate_proj": (I, H), "mlp.up_proj": (I, H), "mlp.down_proj": (H, I)}
+
+
+def random_raw_layer(cfg: dict, layer: int, qcfg: SparseQuantConfig, device, seed0: int = 1000):
+    """Seeded random weights of one block, compressed: {proj: (keep, q, scale, zero)} on `device`.
+    Weights N(0, 0.02) stored as fp16, activation norms |N(0,1)| + 0.1 (seed ``seed0 + 7*layer + idx``)."""
+    out = {}
+    for idx, (name, (K, N)) in enumerate(proj_shapes(cfg).items()):
+        g = torch.Generator().manual_seed(seed0 + layer * 7 + idx)
+        W = (torch.randn(K, N, generator=g) * 0.02).half().float().to(device)
+        norm = (torch.randn(N, generator=g).abs() + 0.1).to(device)
+        out[name] = compress_weight(W, norm, qcfg)
+    return out
+
+
+def random_dense_params(cfg: dict, device, seed: int = 7):
+    """Embedding, final norm, lm_head and per-layer norm weights (bf16), seeded."""
+    g = torch.Generator().manual_seed(seed)
+    H, V = cfg["hidden_size"], cfg["vocab_size"]
+    P = {"model.embed_tokens.weight": (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16).to(device),
+         "lm_head.weight": (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16).to(device),
+         "model.norm.weight": torch.ones(H, dtype=torch.bfloat16, device=device)}
+    for i in range(cfg["num_hidden_layers"]):
+        P[f"model.layers.{i}.input_layernorm.weight"] = torch.ones(H, dtype=torch.bfloat16, device=device)
+        P[f"model.layers.{i}.post_attention_layernorm.weight"] = torch.ones(H, dtype=torch.bfloat16, device=device)
+    return P
+
+
+def _rms_norm(x, w, eps):
+    h = x.float()
+    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    return w * h.to(x.dtype)
+
+
+def _rotate_half(x):
+    d = x.shape[-1] // 2
+    return torch.cat((-x[..., d:], x[..., :d]), dim=-1)
+
+
+class CobaltDecoder:
+    """Batch-1 decoder over compressed projections.  ``linears[(layer, proj)]`` are
+    ``CobaltSparseLinear`` modules; ``dense`` holds embedding / norms / lm_head."""
+
+    def __init__(self, cfg: dict, linears: Dict[tuple, CobaltSparseLinear], dense: Dict[str, torch.Tensor],
+                 max_ctx: int, device):
+        self.cfg, self.lin, self.P, self.max_ctx, self.dev = cfg, linears, dense, max_ctx, device
+        L, nkv, D = cfg["num_hidden_layers"], cfg["num_key_value_heads"], cfg["head_dim"]
+        self.k_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
+        self.v_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
+        self.inv_freq = 1.0 / (float(cfg["rope_theta"]) ** (torch.arange(0, D, 2, dtype=torch.float32, device=device) / D))
+        self.kv_pos = torch.arange(max_ctx, device=device)
+        self.tok = torch.zeros(1, dtype=torch.long, device=device)        # next token to feed
+        self.pos = torch.zeros(1, dtype=torch.long, device=device)        # its position
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._logits = None
+
+    # ------------------------------------------------------------------ one forward over T tokens
+    def _forward(self, ids: torch.Tensor, positions: torch.Tensor, attend_len: int) -> torch.Tensor:
+        """ids, positions: [T] device tensors.  Keys/values are written at ``positions``; attention
+        looks at cache slots [0, attend_len) under the causal mask ``slot <= position``."""
+        cfg, P = self.cfg, self.P
+        nh, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+        eps, T = cfg["rms_norm_eps"], ids.shape[0]
+        h = P["model.embed_tokens.weight"].index_select(0, ids).unsqueeze(0)          # [1, T, H]
+        freqs = positions.float()[:, None] * self.inv_freq[None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        cos, sin = emb.cos().to(h.dtype), emb.sin().to(h.dtype)
+        allowed = self.kv_pos[None, :attend_len] <= positions[:, None]                 # [T, S]
+        if cfg.get("sliding_window"):
+            allowed = allowed & (self.kv_pos[None, :attend_len] > positions[:, None] - cfg["sliding_window"])
+        for i in range(cfg["num_hidden_layers"]):
+            p = f"model.layers.{i}."
+            x = _rms_norm(h, P[p + "input_layernorm.weight"], eps)
+            q = self.lin[(i, "self_attn.q_proj")](x).view(1, T, nh, D).transpose(1, 2)
+            k = self.lin[(i, "self_attn.k_proj")](x).view(1, T, nkv, D).transpose(1, 2)
+            v = self.lin[(i, "self_attn.v_proj")](x).view(1, T, nkv, D).transpose(1, 2)
+            q = (q * cos[None, None]) + (_rotate_half(q) * sin[None, None])
+            k = (k * cos[None, None]) + (_rotate_half(k) * sin[None, None])
+            self.k_cache[i].index_copy_(1, positions, k[0])
+            self.v_cache[i].index_copy_(1, positions, v[0])
+            Kc = self.k_cache[i][:, :attend_len].unsqueeze(0)                          # [1, nkv, S, D]
+            Vc = self.v_cache[i][:, :attend_len].unsqueeze(0)
+            rep = nh // nkv
+            Kr = Kc[:, :, None].expand(1, nkv, rep, attend_len, D).reshape(1, nh, attend_len, D)
+            Vr = Vc[:, :, None].expand(1, nkv, rep, attend_len, D).reshape(1, nh, attend_len, D)
+            att = torch.matmul(q, Kr.transpose(2, 3)) * (float(D) ** -0.5)
+            att = att.masked_fill(~allowed[None, None], float("-inf"))
+            att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
+            ctx = torch.matmul(att, Vr).transpose(1, 2).reshape(1, T, nh * D)
+            h = h + self.lin[(i, "self_attn.o_proj")](ctx)
+            x = _rms_norm(h, P[p + "post_attention_layernorm.weight"], eps)
+            g = self.lin[(i, "mlp.gate_proj")](x)
+            u = self.lin[(i, "mlp.up_proj")](x)
+            h = h + self.lin[(i, "mlp.down_proj")](F.silu(g) * u)
+        h = _rms_norm(h, P["model.norm.weight"], eps)
+        return F.linear(h, P["lm_head.weight"])                                        # [1, T, V]
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """Run the prompt, fill the cache, return logits [T, V]."""
+        ids = ids.to(self.dev)
+        T = ids.shape[0]
+        logits = self._forward(ids, torch.arange(T, device=self.dev), T)[0]
+        self.pos.fill_(T)
+        return logits
+
+    @torch.no_grad()
+    def step(self) -> torch.Tensor:
+        """One decode step for the token in ``self.tok`` at ``self.pos``; returns logits [V] and
+        advances ``tok`` (greedy) and ``pos`` on the device."""
+        logits = self._forward(self.tok, self.pos, self.max_ctx)[0, 0]
+        self.tok.copy_(torch.argmax(logits.float(), dim=-1, keepdim=True))
+        self.pos.add_(1)
+        return logits
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True, teacher: Optional[torch.Tensor] = None):
+        """Greedy continuation.  Returns (tokens [n_new] on the CPU, logits of every step [n_new, V]).
+        With ``teacher`` (token ids), the fed-back token of step i is ``teacher[i]`` instead of the argmax
+        (teacher-forced run, src/cobaltkernel/verify_kernel.py:288-339)."""
+        logits = self.prefill(prompt)
+        first = torch.argmax(logits[-1].float(), dim=-1, keepdim=True)
+        self.tok.copy_(first if teacher is None else teacher[0:1].to(self.dev))
+        toks = [first.clone()]
+        all_logits = [logits[-1].clone()]
+        if use_graph and self._graph is None:
+            s = torch.cuda.Stream(self.dev)
+            s.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(s):                       # warm-up outside capture (lazy inits, scratch)
+                tok0, pos0 = self.tok.clone(), self.pos.clone()
+                self.step()
+                self.tok.copy_(tok0)
+                self.pos.copy_(pos0)
+            torch.cuda.current_stream(self.dev).wait_stream(s)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._logits = self.step()
+        for i in range(1, n_new):
+            if use_graph:
+                self._graph.replay()
+                lg = self._logits
+            else:
+                lg = self.step()
+            toks.append(torch.argmax(lg.float(), dim=-1, keepdim=True).clone())
+            all_logits.append(lg.clone())
+            if teacher is not None:
+                self.tok.copy_(teacher[i:i + 1].to(self.dev))
+        return torch.cat(toks).cpu(), torch.stack(all_logits)
+
+
+def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, device, keep_raw: bool = False):
+    """Random-init model of the given shape with every projection compressed.  Returns the decoder
+    and, when ``keep_raw``, the RAW tensors per (layer, proj) for an oracle to dequantise."""
+    lin, raws = {}, {}
+    for i in range(cfg["num_hidden_layers"]):
+        layer = random_raw_layer(cfg, i, qcfg, device)
+        for name, (keep, q, sc, zr) in layer.items():
+            lin[(i, name)] = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": qcfg.bits})
+            if keep_raw:
+                raws[(i, name)] = (keep, q, sc, zr)
+    dec = CobaltDecoder(cfg, lin, random_dense_params(cfg, device), max_ctx, device)
+    return (dec, raws) if keep_raw else dec

@@ -132,7 +132,7 @@ def dequantize(q: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, keep: t
     z = zero.float().reshape(K, -1, 1)
     ng = s1.shape[1]
     W = ((Q.view(K, ng, N // ng) - z) * s1).view(K, N)
-    s2 = torch.ones(N) if scale2 is None else scale2.float()
+    s2 = torch.ones(N, device=q.device) if scale2 is None else scale2.float()
     W = W * s2
     W = W * keep.float()
     return W

@@ -18,6 +18,17 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
+# Control switch (src/cobaltkernel/verify_kernel.py:160-169, 262-285 runs the same oracle code under a
+# second, equally legitimate arithmetic to measure what accumulation order alone does to the logits):
+# when set, every linear accumulates in fp32 from upcast operands and rounds once to bf16.
+EXACT_LINEAR = False
+
+
+def _linear(x, w):
+    if EXACT_LINEAR:
+        return torch.matmul(x.float(), w.float().t()).to(x.dtype)
+    return F.linear(x, w)
+
 
 def llama_config(hidden=4096, layers=32, heads=32, kv_heads=8, head_dim=128, inter=14336, vocab=32000,
                  eps=1e-5, theta=1e6, sliding_window=None):
@@ -62,9 +73,9 @@ def _repeat_kv(x, n):
 def _attention(cfg, W, p, h, cos, sin, kv, positions):
     T, D = h.shape[1], cfg["head_dim"]
     nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
-    q = F.linear(h, W[p + "self_attn.q_proj.weight"]).view(1, T, nh, D).transpose(1, 2)
-    k = F.linear(h, W[p + "self_attn.k_proj.weight"]).view(1, T, nkv, D).transpose(1, 2)
-    v = F.linear(h, W[p + "self_attn.v_proj.weight"]).view(1, T, nkv, D).transpose(1, 2)
+    q = _linear(h, W[p + "self_attn.q_proj.weight"]).view(1, T, nh, D).transpose(1, 2)
+    k = _linear(h, W[p + "self_attn.k_proj.weight"]).view(1, T, nkv, D).transpose(1, 2)
+    v = _linear(h, W[p + "self_attn.v_proj.weight"]).view(1, T, nkv, D).transpose(1, 2)
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     kv["k"] = k if kv["k"] is None else torch.cat([kv["k"], k], dim=2)
     kv["v"] = v if kv["v"] is None else torch.cat([kv["v"], v], dim=2)
@@ -78,13 +89,13 @@ def _attention(cfg, W, p, h, cos, sin, kv, positions):
     att = att.masked_fill(~allowed[None, None], float("-inf"))
     att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
     out = torch.matmul(att, _repeat_kv(Vc, nh // nkv)).transpose(1, 2).reshape(1, T, -1)
-    return F.linear(out, W[p + "self_attn.o_proj.weight"])
+    return _linear(out, W[p + "self_attn.o_proj.weight"])
 
 
 def _mlp(W, p, h):
-    g = F.linear(h, W[p + "mlp.gate_proj.weight"])
-    u = F.linear(h, W[p + "mlp.up_proj.weight"])
-    return F.linear(F.silu(g) * u, W[p + "mlp.down_proj.weight"])
+    g = _linear(h, W[p + "mlp.gate_proj.weight"])
+    u = _linear(h, W[p + "mlp.up_proj.weight"])
+    return _linear(F.silu(g) * u, W[p + "mlp.down_proj.weight"])
 
 
 def new_kv(cfg):
@@ -118,6 +129,18 @@ def forward_step(cfg, W, token_id, pos, kv):
     dev = W["lm_head.weight"].device
     ids = torch.tensor([token_id], device=dev, dtype=torch.long)
     return run(cfg, W, ids, torch.tensor([pos], device=dev), kv)[0, 0]
+
+
+def teacher_forced(cfg, W, prompt_ids, tokens):
+    """Logits [len(tokens), V] when the continuation `tokens` is fed back regardless of the argmax:
+    row i is the distribution from which token i is drawn."""
+    logits, kv = prefill(cfg, W, prompt_ids)
+    rows = [logits[0, -1]]
+    pos = prompt_ids.shape[0]
+    for t in tokens[:-1]:
+        rows.append(forward_step(cfg, W, int(t), pos, kv))
+        pos += 1
+    return torch.stack(rows)
 
 
 def greedy(cfg, W, prompt_ids, n_new):
