@@ -180,7 +180,7 @@ int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t l
     P.slot_bytes = c.slot; P.nib_bytes = c.nib;
     P.total_warps = c.total_warps;
     P.debug = (uint32_t)g_debug_flags;
-    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k29 = 1u << 29;
+    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k16 = 1u << 16;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);

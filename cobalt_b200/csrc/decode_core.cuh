@@ -187,8 +187,11 @@ constexpr void build_expand_lut(LutEntry* lut /*[256]*/) {
             if ((mb >> p) & 1) { s[p] = (rank & 1) ? 4u + (uint32_t)(rank >> 1) : (uint32_t)(rank >> 1); ++rank; }
             else s[p] = 7u;
         }
-        lut[mb].x = s[0] | (s[2] << 4) | (s[1] << 8) | (s[3] << 12);
-        lut[mb].y = s[4] | (s[6] << 4) | (s[5] << 8) | (s[7] << 12);
+        // upper halves (ignored by prmt): .x = selector that builds the high view {hi.b0, hi.b1, hi.b2, z or hi.b3},
+        // .y = window advance in bits (4 per survivor)
+        const uint32_t self = (rank == 8) ? 0x3210u : 0x4210u;
+        lut[mb].x = (s[0] | (s[2] << 4) | (s[1] << 8) | (s[3] << 12)) | (self << 16);
+        lut[mb].y = (s[4] | (s[6] << 4) | (s[5] << 8) | (s[7] << 12)) | ((uint32_t)(4 * rank) << 16);
     }
 }
 
@@ -294,7 +297,7 @@ CB_HD void decode32(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t 
 // Same contract as decode32() for segments whose SegParams::fast is set, arranged for the
 // instruction mix of an SM: the ALU pipe (prmt / lop3 / shf) is the scarce one, so right shifts
 // by constants and the "all eight kept" special case are computed with multiplies on the FMA
-// pipe.  `k28`, `k24`, `k29` must hold 1<<28, 1<<24, 1<<29; they are passed in registers so
+// pipe.  `k28`, `k24`, `k16` must hold 1<<28, 1<<24, 1<<16; they are passed in registers so
 // that the multiplies are not turned back into shifts.  `lut(idx)` returns the table entry of
 // mask byte idx.
 CB_HD uint32_t mulhi_u32(uint32_t a, uint32_t b) {
@@ -305,37 +308,38 @@ CB_HD uint32_t mulhi_u32(uint32_t a, uint32_t b) {
 #endif
 }
 
-struct FastConsts { uint32_t k28, k24, k29; };
+struct FastConsts { uint32_t k28, k24, k16; };
 
+// Two mask bytes (16 positions): `m16` holds them in its low 16 bits.  The window words are
+// advanced past the survivors consumed.  out[i] = bf16x2 weights of columns (2i, 2i+1), i < 8.
 template <class LutFn>
-CB_HD void decode32_fast(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, const SegParams& p,
-                         const FastConsts& K, LutFn lut, uint32_t out[16]) {
-    uint32_t idx[4], cnt[4];
-    LutEntry e[4];
+CB_HD void decode16_fast(uint32_t m16, uint32_t& w0, uint32_t& w1, uint32_t& w2, uint32_t& w3, const SegParams& p,
+                         const FastConsts& K, LutFn lut, uint32_t out[8]) {
+    const LutEntry e0 = lut(prmt(m16, 0u, 0x4440u));
+    const LutEntry e1 = lut(prmt(m16, 0u, 0x4441u));
+    const uint32_t zreg = p.zb24 >> 24;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        idx[i] = prmt(m, 0u, 0x4440u | (uint32_t)i);        // mask byte i, zero-extended
-        e[i] = lut(idx[i]);
-        cnt[i] = (uint32_t)popc(idx[i]);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t full = mulhi_u32(cnt[i], K.k29);      // 1 iff all eight positions are kept
-        const uint32_t andm = full * 0xFF000000u + 0x00FFFFFFu;
-        const uint32_t zsel = p.zb24 - full * p.zb24;
-        const uint32_t hi = (mulhi_u32(w0, K.k28) & andm) | zsel;   // (w0 >> 4) with the zero point in byte 3
-        const uint32_t d0 = prmt(w0, hi, e[i].x), d1 = prmt(w0, hi, e[i].y);
+    for (int i = 0; i < 2; ++i) {
+        const LutEntry e = i ? e1 : e0;
+        // high view: (w0 >> 4) with byte 3 replaced by the zero point unless all eight positions are kept
+        const uint32_t hi = prmt(mulhi_u32(w0, K.k28), zreg, mulhi_u32(e.x, K.k16));
+        const uint32_t d0 = prmt(w0, hi, e.x), d1 = prmt(w0, hi, e.y);
         out[4 * i + 0] = dq_pair((d0 & 0x000F000Fu) | 0x43004300u, p);
         out[4 * i + 1] = dq_pair((mulhi_u32(d0, K.k24) & 0x000F000Fu) | 0x43004300u, p);
         out[4 * i + 2] = dq_pair((d1 & 0x000F000Fu) | 0x43004300u, p);
         out[4 * i + 3] = dq_pair((mulhi_u32(d1, K.k24) & 0x000F000Fu) | 0x43004300u, p);
-        const uint32_t amt = cnt[i] * 4u;
-        if (i < 3) {
-            w0 = funnel_rc(w0, w1, amt);
-            if (i < 2) w1 = funnel_rc(w1, w2, amt);
-            if (i < 1) w2 = funnel_rc(w2, w3, amt);
-        }
+        const uint32_t amt = mulhi_u32(e.y, K.k16);
+        w0 = funnel_rc(w0, w1, amt);
+        w1 = funnel_rc(w1, w2, amt);
+        w2 = funnel_rc(w2, w3, amt);
     }
+}
+
+template <class LutFn>
+CB_HD void decode32_fast(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, const SegParams& p,
+                         const FastConsts& K, LutFn lut, uint32_t out[16]) {
+    decode16_fast(m & 0xFFFFu, w0, w1, w2, w3, p, K, lut, out);
+    decode16_fast(m >> 16, w0, w1, w2, w3, p, K, lut, out + 8);
 }
 
 // ----------------------------------------------------------------------------- 2/3-bit -> nibble

@@ -42,7 +42,7 @@ struct GemvParams {
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
     FastConsts K;
-    uint32_t debug;                      // experiments only: bit0 skip x loads, bit1 skip flush, bit2 skip MMA
+    uint32_t debug;                      // experiments only: bit1 skip flush, bit2 skip MMA
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -259,37 +259,54 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         const SegParams pB = make_seg_params(szB, BITS, W.col_scale != nullptr);
         const bool all_fast = __all_sync(full, pA.fast && pB.fast);
         const int col0 = (ct * TILE_GROUPS + t) * GROUP;               // first column of this lane's group
-        const uint16_t* xbase = P.x + col0;
+        // Tokens beyond M read the last real token (their MMA columns are never stored); lanes beyond a
+        // partial tile read column 0 of x, which their all-zero weights cancel.
+        const uint16_t* xrow[MT];
+#pragma unroll
+        for (int b = 0; b < MT; ++b) {
+            int tok = g + 8 * b;
+            if (tok > P.M - 1) tok = P.M - 1;
+            xrow[b] = P.x + (size_t)tok * P.ldx + (active ? col0 : 0);
+        }
+        auto lut = [lut_lane](uint32_t idx) {
+            const uint2 e = lds64(lut_lane + idx * (LUT_COPIES * 8u));
+            return LutEntry{e.x, e.y};
+        };
 
 #pragma unroll 1
         for (int j = 0; j < 4; ++j) {
             const uint32_t mAj = mA.x, mBj = mB.x;                     // rotate instead of indexing registers
             mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
             mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
-            // activations of this 32-column word first, so that their latency hides behind the decode
-            uint4 xv[MT][4];
-#pragma unroll
-            for (int b = 0; b < MT; ++b) {
-                const int tok = g + 8 * b;
-                xv[b][0] = xv[b][1] = xv[b][2] = xv[b][3] = make_uint4(0, 0, 0, 0);
-                if (active && tok < P.M && !(P.debug & 1u)) {
-                    const uint4* xp = reinterpret_cast<const uint4*>(xbase + (size_t)tok * P.ldx + 32 * j);
-                    xv[b][0] = ldg_nc_early(xp); xv[b][1] = ldg_nc_early(xp + 1);
-                    xv[b][2] = ldg_nc_early(xp + 2); xv[b][3] = ldg_nc_early(xp + 3);
-                }
-            }
-            uint32_t ea[16], eb[16];
             uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
             load_window(cbase, offA, a0, a1, a2, a3);
             load_window(cbase, offB, b0, b1, b2, b3);
+            offA += __popc(mAj);
+            offB += __popc(mBj);
             if (all_fast) {
-                auto lut = [lut_lane](uint32_t idx) {
-                    const uint2 e = lds64(lut_lane + idx * (LUT_COPIES * 8u));
-                    return LutEntry{e.x, e.y};
-                };
-                decode32_fast(mAj, a0, a1, a2, a3, pA, P.K, lut, ea);
-                decode32_fast(mBj, b0, b1, b2, b3, pB, P.K, lut, eb);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {                          // 16 columns at a time keeps fewer registers live
+                    uint4 xv[MT][2];
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) {
+                        const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * j + 16 * h);
+                        xv[b][0] = ldg_nc_early(xp);
+                        xv[b][1] = ldg_nc_early(xp + 1);
+                    }
+                    uint32_t ea[8], eb[8];
+                    decode16_fast(h ? (mAj >> 16) : (mAj & 0xFFFFu), a0, a1, a2, a3, pA, P.K, lut, ea);
+                    decode16_fast(h ? (mBj >> 16) : (mBj & 0xFFFFu), b0, b1, b2, b3, pB, P.K, lut, eb);
+                    if (P.debug & 4u) { acc[0][0] += __uint_as_float(ea[0] ^ eb[3] ^ ea[7] ^ eb[5]); continue; }
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) {
+                        mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);
+                        mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], xv[b][0].z, xv[b][0].w);
+                        mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], xv[b][1].x, xv[b][1].y);
+                        mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], xv[b][1].z, xv[b][1].w);
+                    }
+                }
             } else {
+                uint32_t ea[16], eb[16];
                 float cs[32];
                 const float* csp = nullptr;
                 if (W.col_scale != nullptr && active) {
@@ -299,20 +316,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                 }
                 decode32<LUT_COPIES>(mAj, a0, a1, a2, a3, pA, lut_lane_ptr, csp, ea);
                 decode32<LUT_COPIES>(mBj, b0, b1, b2, b3, pB, lut_lane_ptr, csp, eb);
-            }
-            offA += __popc(mAj);
-            offB += __popc(mBj);
-            if (P.debug & 4u) { acc[0][0] += __uint_as_float(ea[0] ^ eb[3] ^ ea[7] ^ eb[12] ^ ea[15] ^ eb[9]); continue; }
 #pragma unroll
-            for (int b = 0; b < MT; ++b) {
-                mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);
-                mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], xv[b][0].z, xv[b][0].w);
-                mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], xv[b][1].x, xv[b][1].y);
-                mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], xv[b][1].z, xv[b][1].w);
-                mma_bf16_16816(acc[b], ea[8], eb[8], ea[9], eb[9], xv[b][2].x, xv[b][2].y);
-                mma_bf16_16816(acc[b], ea[10], eb[10], ea[11], eb[11], xv[b][2].z, xv[b][2].w);
-                mma_bf16_16816(acc[b], ea[12], eb[12], ea[13], eb[13], xv[b][3].x, xv[b][3].y);
-                mma_bf16_16816(acc[b], ea[14], eb[14], ea[15], eb[15], xv[b][3].z, xv[b][3].w);
+                for (int b = 0; b < MT; ++b) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * j);
+                    const uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1), x2 = __ldg(xp + 2), x3 = __ldg(xp + 3);
+                    mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], x0.x, x0.y);
+                    mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], x0.z, x0.w);
+                    mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], x1.x, x1.y);
+                    mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], x1.z, x1.w);
+                    mma_bf16_16816(acc[b], ea[8], eb[8], ea[9], eb[9], x2.x, x2.y);
+                    mma_bf16_16816(acc[b], ea[10], eb[10], ea[11], eb[11], x2.z, x2.w);
+                    mma_bf16_16816(acc[b], ea[12], eb[12], ea[13], eb[13], x3.x, x3.y);
+                    mma_bf16_16816(acc[b], ea[14], eb[14], ea[15], eb[15], x3.z, x3.w);
+                }
             }
         }
 
