@@ -117,35 +117,74 @@ int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
 
 // ----------------------------------------------------------------------------- GEMM configuration
 struct GemmCfg {
-    int stages;
-    uint32_t slot, nib;
-    size_t smem;
+    int splits, tok_per_cta;
+    dim3 grid;
+    size_t counters_off, partials_off, total;
 };
 
-int gemm_config(const CobaltMat* w, GemmCfg* c) {
-    c->slot = (uint32_t)round_up((size_t)w->max_tile_bytes + 32, 128);
-    c->nib = nibble_bytes(w);
-    const size_t ring = (size_t)2 * GEMM_RB * (c->slot + c->nib) + 64;
-    int stages = g_tune_gemm_stages > 0 ? g_tune_gemm_stages : 4;
-    if (stages > 4) stages = 4;
-    while (stages > 2 && (size_t)stages * (GEMM_A_BYTES + GEMM_B_BYTES) + GEMM_LUT_BYTES + GEMM_BAR_BYTES + ring + 1024 > SMEM_LIMIT) --stages;
-    c->smem = (size_t)stages * (GEMM_A_BYTES + GEMM_B_BYTES) + GEMM_LUT_BYTES + GEMM_BAR_BYTES + ring + 1024;
-    if (c->smem > SMEM_LIMIT) return COBALT_EINVAL;
-    c->stages = stages;
+int gemm_config(const CobaltMat* w, int M, int num_sms, GemmCfg* c) {
+    const int row_tiles = (w->n_row_blocks + GEMM_RB - 1) / GEMM_RB;
+    // fewer tokens per CTA when the problem is too small to occupy the SMs with 512-token tiles
+    int tpc = GEMM_TOKENS;
+    while (tpc > 64 && (long)row_tiles * ((M + tpc - 1) / tpc) * 4 < (long)num_sms * 3) tpc /= 2;
+    c->tok_per_cta = tpc;
+    const int tok_tiles = (M + tpc - 1) / tpc;
+    const long units = (long)row_tiles * tok_tiles;
+    long splits = 1;
+    if (g_tune_gemm_stages > 0) splits = g_tune_gemm_stages;                 // tuning key 2 overrides the split-K factor
+    else if (units * 2 < (long)num_sms) splits = num_sms / units;
+    if (splits > 8) splits = 8;
+    if (splits > w->n_col_tiles) splits = w->n_col_tiles;
+    if (splits < 1) splits = 1;
+    c->splits = (int)splits;
+    c->grid = dim3((unsigned)row_tiles, (unsigned)tok_tiles, (unsigned)splits);
+    c->counters_off = SCRATCH_STATUS_BYTES;
+    c->partials_off = c->counters_off + round_up((size_t)units * 4, 256);
+    c->total = c->partials_off + (splits > 1 ? (size_t)units * splits * GEMM_TOKENS * GEMM_ROWS * sizeof(float) : 0);
     return COBALT_OK;
 }
 
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (TensorMapEncodeFn)p;
+    }
+    return fn;
+}
+
+// activations [M, N] bf16, row stride ldx elements: box = 64 columns x 256 tokens, 128-byte swizzle
+int make_x_map(CUtensorMap* map, const void* x, int64_t ldx, int M, int N) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc) return COBALT_ELAUNCH;
+    cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t gstride[1] = {(cuuint64_t)ldx * 2};
+    cuuint32_t box[2] = {(cuuint32_t)GEMM_KS, (cuuint32_t)GEMM_NT};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? COBALT_OK : COBALT_EINVAL;
+}
+
 template <int BITS>
-int launch_gemm(const GemmParams& P, const GemmCfg& c, dim3 grid, cudaStream_t st) {
+int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, cudaStream_t st) {
     static bool configured[MAX_DEVICES];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES) != cudaSuccess)
             return COBALT_ELAUNCH;
         configured[dev] = true;
     }
-    gemm_tcgen05_kernel<BITS><<<grid, GEMM_THREADS, c.smem, st>>>(P);
+    gemm_tcgen05_kernel<BITS><<<c.grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(P, xmap);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
@@ -217,8 +256,8 @@ const char* cobalt_strerror(int status) {
     }
 }
 
-// Tuning hook for benchmarks: key 0 = GEMV tiles per split, 1 = GEMV ring stages, 2 = GEMM operand
-// stages; value 0 restores the heuristic.  Not part of the stable contract.
+// Tuning hook for benchmarks: key 0 = GEMV grid size, 1 = GEMV ring stages, 2 = GEMM split-K factor,
+// 3 = experiment switches; value 0 restores the heuristic.  Not part of the stable contract.
 int cobalt_set_tuning(int key, int value) {
     if (value < 0) return COBALT_EINVAL;
     switch (key) {
@@ -296,8 +335,12 @@ int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y,
 }
 
 size_t cobalt_gemm_scratch_bytes(const CobaltMat* w, int M) {
+    int sms = 0;
     if (check_mat(w) != COBALT_OK || M <= 0) return 0;
-    return SCRATCH_STATUS_BYTES;
+    if (device_info(&sms) != COBALT_OK) return 0;
+    GemmCfg c;
+    if (gemm_config(w, M, sms, &c) != COBALT_OK) return 0;
+    return c.total;
 }
 
 int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
@@ -309,25 +352,29 @@ int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
     int sms = 0;
     rc = device_info(&sms);
     if (rc) return rc;
-    if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < SCRATCH_STATUS_BYTES) return COBALT_ESCRATCH;
     GemmCfg c;
-    rc = gemm_config(w, &c);
+    rc = gemm_config(w, M, sms, &c);
+    if (rc) return rc;
+    if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
+    CUtensorMap xmap;
+    rc = make_x_map(&xmap, x, ldx, M, w->N);
     if (rc) return rc;
     GemmParams P;
     P.W = make_view(w);
-    P.x = (const uint16_t*)x; P.ldx = ldx;
     P.y = (uint16_t*)y; P.ldy = ldy;
     P.bias = (const uint16_t*)bias;
     P.M = M;
-    P.stages = c.stages;
-    P.slot_bytes = c.slot; P.nib_bytes = c.nib;
+    P.splits = c.splits;
+    P.tok_per_cta = c.tok_per_cta;
     P.status = (uint32_t*)scratch;
-    dim3 grid((unsigned)((w->n_row_blocks + GEMM_RB - 1) / GEMM_RB), (unsigned)((M + GEMM_MAX_NT - 1) / GEMM_MAX_NT));
+    P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
+    P.partials = c.splits > 1 ? (float*)((uint8_t*)scratch + c.partials_off) : nullptr;
+    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k16 = 1u << 16;
     cudaStream_t st = (cudaStream_t)stream;
     switch (w->bits) {
-        case 2: return launch_gemm<2>(P, c, grid, st);
-        case 3: return launch_gemm<3>(P, c, grid, st);
-        default: return launch_gemm<4>(P, c, grid, st);
+        case 2: return launch_gemm<2>(P, xmap, c, st);
+        case 3: return launch_gemm<3>(P, xmap, c, st);
+        default: return launch_gemm<4>(P, xmap, c, st);
     }
 }
 
@@ -362,8 +409,10 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
     if (!x_host || !y_host || !dev_x || !dev_y || M <= 0) return COBALT_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
     if (cudaMemcpyAsync(dev_x, x_host, (size_t)M * w->N * 2, cudaMemcpyHostToDevice, st) != cudaSuccess) return COBALT_ELAUNCH;
+    // the two kernels lay out their arrival counters differently: start each call from a clean prefix
+    if (scratch && scratch_bytes >= 65536 && cudaMemsetAsync(scratch, 0, 65536, st) != cudaSuccess) return COBALT_ELAUNCH;
     if (M <= MAX_GEMV_M)
-        rc = cobalt_gemv(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, stream);
+        rc = gemv_impl(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, /*clear_counters=*/true, stream);
     else
         rc = cobalt_gemm(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, stream);
     if (rc) return rc;

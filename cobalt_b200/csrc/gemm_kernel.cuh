@@ -1,56 +1,70 @@
 // Prefill GEMM: Y[m, k] = sum_j bf16(W[k, j]) * X[m, j] with tcgen05.mma, accumulators in
 // tensor memory.
 //
-// One CTA owns 128 weight rows (8 row blocks of the tile image) and up to 256 tokens:
-//   D[128 rows x n tokens] (TMEM, fp32)  +=  A[128 x 64] (bf16, decoded weights)  *  B[n x 64]^T (bf16, x)
-// per 64-column stage, both operands K-major in shared memory with the 128-byte swizzle.
+// One CTA owns 128 weight rows and up to 512 tokens.  Per 64-column stage it forms
+//   D0[128 x n0] += A[128 x 64] * B0[n0 x 64]^T      D1[128 x n1] += A * B1[n1 x 64]^T
+// (n0, n1 <= 256 tokens; bf16 operands, fp32 accumulators in 2 x 256 TMEM columns), so a weight
+// tile is dequantised once per 512 tokens.  Both operands are K-major in shared memory with the
+// 128-byte swizzle.
 //
-//   warps 0-3  decode: thread r owns weight row r.  It expands the row's bitmask + codes for the
-//              64 columns of the stage into 64 bf16 and writes them as eight swizzled 16-byte
-//              chunks.  After the main loop the same warps drain TMEM (warp q reads lanes 32q..)
-//              and store bf16 outputs.
-//   warps 4-7  load the activation stage (16-byte vector loads, swizzled stores) and keep the
-//              compressed-tile ring fed with bulk async copies (8 tiles per 512-column tile).
-//   warp 8     one elected lane issues tcgen05.mma and tcgen05.commit.
+//   warps 0-7  decode: two groups of four warps take alternate stages; thread r of a group owns
+//              weight row r.  It reads the row's bitmask words and code bits straight from the
+//              tile image in global memory (next stage prefetched into registers), expands the 64
+//              columns of the stage to bf16 (decode_core.cuh) and writes eight swizzled 16-byte
+//              chunks into the A stage.  After the main loop the same warps drain TMEM (warp w
+//              reads lanes 32*(w%4).., accumulator w/4) and store the outputs.
+//   warp 8     one elected lane issues the TMA loads of the activation stage (2-D tensor map,
+//              box 64 columns x 256 tokens, 128-byte swizzle, rows beyond M zero-filled).
+//   warp 9     one elected lane issues tcgen05.mma and tcgen05.commit.
 //
-// Generic-proxy writes to operand stages are published with fence.proxy.async before the
-// mbarrier arrive; the MMA thread orders itself with tcgen05.fence::after_thread_sync.  Every
-// wait is bounded: on expiry the kernel records a status code, stops issuing work, lets its
-// outstanding copies land (bounded), frees its tensor memory and returns.
+// Generic-proxy writes to A stages are published with fence.proxy.async before the mbarrier
+// arrive.  Every wait is bounded: on expiry the kernel records a status code, stops issuing
+// work, frees its tensor memory and returns.  With split-K (small grids) every CTA writes its
+// fp32 tile to scratch and the last CTA of a tile adds the splits in order.
 //
 // Behaviour replaced: cbk::gemm_tile (mma.sync m16n8k16, per-fragment bf16x2 dequantisation,
 // src/cobaltkernel/csrc/cobalt_gemm.cuh:243-609) driven by gemm_phase
 // (src/cobaltkernel/csrc/prefill_kernel.cu:103-150).
 #pragma once
+#include <cuda.h>
 #include "common.cuh"
-#include "gemv_kernel.cuh"   // load_window, finish_output
+#include "gemv_kernel.cuh"   // finish_output
 
 namespace cb {
 
 constexpr int GEMM_ROWS = 128;            // UMMA M
-constexpr int GEMM_MAX_NT = 256;          // UMMA N (tokens per CTA)
+constexpr int GEMM_NT = 256;              // UMMA N (tokens per accumulator)
+constexpr int GEMM_ACCS = 2;              // accumulators per CTA -> 512 tokens
+constexpr int GEMM_TOKENS = GEMM_NT * GEMM_ACCS;
 constexpr int GEMM_KS = 64;               // columns per stage = one 128-byte swizzle row of bf16
 constexpr int GEMM_RB = GEMM_ROWS / TILE_ROWS;   // 8 row blocks per CTA
 constexpr int GEMM_LUT_COPIES = 8;
-constexpr int GEMM_THREADS = 288;
+constexpr int GEMM_A_STAGES = 3;
+constexpr int GEMM_B_STAGES = 2;
+constexpr int GEMM_DECODE_THREADS = 256;
+constexpr int GEMM_THREADS = GEMM_DECODE_THREADS + 64;
 constexpr uint32_t GEMM_LUT_BYTES = LUT_ENTRIES * GEMM_LUT_COPIES * 8;   // 16 KB
 constexpr uint32_t GEMM_A_BYTES = GEMM_ROWS * GEMM_KS * 2;               // 16 KB
-constexpr uint32_t GEMM_B_BYTES = GEMM_MAX_NT * GEMM_KS * 2;             // 32 KB
+constexpr uint32_t GEMM_BHALF_BYTES = GEMM_NT * GEMM_KS * 2;             // 32 KB
+constexpr uint32_t GEMM_B_BYTES = GEMM_BHALF_BYTES * GEMM_ACCS;          // 64 KB
 constexpr uint32_t GEMM_BAR_BYTES = 256;
+constexpr uint32_t GEMM_SMEM_BYTES = GEMM_A_STAGES * GEMM_A_BYTES + GEMM_B_STAGES * GEMM_B_BYTES + GEMM_LUT_BYTES +
+                                     GEMM_BAR_BYTES + 1024;
 
 struct GemmParams {
     MatView W;
-    const uint16_t* x; int64_t ldx;
     uint16_t* y; int64_t ldy;
     const uint16_t* bias;
     int M;
-    int stages;                 // operand stages (2..4)
-    uint32_t slot_bytes;        // one compressed tile slot
-    uint32_t nib_bytes;         // per-slot nibble buffer (bits < 4), else 0
+    int tok_per_cta;            // tokens per CTA: 512, or less (multiple of 16) to spread a small problem over more SMs
+    int splits;                 // split-K factor (column tiles are divided among blockIdx.z)
+    float* partials;            // [tile][split][GEMM_TOKENS][GEMM_ROWS] fp32 (splits > 1)
+    uint32_t* counters;         // [tile]
     uint32_t* status;
+    FastConsts K;
 };
 
-// ---- tcgen05 wrappers
+// ---- tcgen05 / TMA wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
@@ -82,6 +96,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 2-D tiled TMA load (no multicast): box of the tensor map at (x = column, y = token) -> shared
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
 
 // K-major, 128-byte swizzle, 8-row groups 1024 B apart; descriptor version 1 (sm_100)
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
@@ -98,84 +117,130 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((GEMM_ROWS >> 4) << 24);
 }
 
+// Nibble window (128 bits, first survivor in bits 0..3 of w0) of the 32-column word whose first
+// survivor has rank `rank` in the tile's code stream `codes` (global memory, 4-byte aligned).
 template <int BITS>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const GemmParams P) {
+__device__ __forceinline__ void fetch_window(const uint32_t* codes, uint32_t rank, uint32_t (&raw)[5]) {
+    const uint32_t bitpos = rank * (uint32_t)BITS;
+    const uint32_t* p = codes + (bitpos >> 5);
+    constexpr int NW = BITS == 4 ? 5 : (BITS == 3 ? 4 : 3);
+#pragma unroll
+    for (int i = 0; i < 5; ++i) raw[i] = i < NW ? __ldg(p + i) : 0u;
+}
+template <int BITS>
+__device__ __forceinline__ void align_window(const uint32_t (&raw)[5], uint32_t rank, uint32_t& w0, uint32_t& w1,
+                                             uint32_t& w2, uint32_t& w3) {
+    const uint32_t o = (rank * (uint32_t)BITS) & 31u;
+    const uint32_t a0 = funnel_r(raw[0], raw[1], o), a1 = funnel_r(raw[1], raw[2], o);
+    const uint32_t a2 = funnel_r(raw[2], raw[3], o), a3 = funnel_r(raw[3], raw[4], o);
+    if (BITS == 4) {
+        w0 = a0; w1 = a1; w2 = a2; w3 = a3;
+    } else if (BITS == 3) {                     // 96 bits = four 24-bit chunks of 8 codes
+        w0 = spread3(a0 & 0x00FFFFFFu);
+        w1 = spread3(funnel_r(a0, a1, 24) & 0x00FFFFFFu);
+        w2 = spread3(funnel_r(a1, a2, 16) & 0x00FFFFFFu);
+        w3 = spread3(a2 >> 8);
+    } else {                                    // 64 bits = four 16-bit chunks of 8 codes
+        w0 = spread2(a0); w1 = spread2(a0 >> 16); w2 = spread2(a1); w3 = spread2(a1 >> 16);
+    }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const GemmParams P,
+                                                                       const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const MatView& W = P.W;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full_mask = 0xFFFFFFFFu;
 
-    // ---- shared memory carve-up (all operand stages 1024-byte aligned)
-    const uint32_t s0 = smem_u32(smem);
-    const uint32_t a_base = s0;                                          // stages x 16 KB
-    const uint32_t b_base = a_base + P.stages * GEMM_A_BYTES;            // stages x 32 KB
-    const uint32_t lut_addr = b_base + P.stages * GEMM_B_BYTES;          // 16 KB
-    const uint32_t bar_base = lut_addr + GEMM_LUT_BYTES;                 // barriers + tmem pointer
-    const uint32_t ring_base = bar_base + GEMM_BAR_BYTES;                // 2 x 8 x (slot + nib)
-    const uint32_t per_slot = P.slot_bytes + P.nib_bytes;
-    // barrier map (8 bytes each): full[4] empty[4] cfull[2] cempty[2] acc  | tmem pointer at +120
-    auto bar_full = [&](int s) { return bar_base + 8u * s; };
-    auto bar_empty = [&](int s) { return bar_base + 32u + 8u * s; };
-    auto bar_cfull = [&](int b) { return bar_base + 64u + 8u * b; };
-    auto bar_cempty = [&](int b) { return bar_base + 80u + 8u * b; };
-    const uint32_t bar_acc = bar_base + 96u;
-    const uint32_t tmem_slot = bar_base + 120u;
+    // ---- shared memory carve-up (operand stages 1024-byte aligned)
+    const uint32_t s_raw = smem_u32(smem);
+    const uint32_t s0 = (s_raw + 1023u) & ~1023u;                         // the allocation carries 1 KB of slack
+    uint8_t* const sm = smem + (s0 - s_raw);
+    const uint32_t a_base = s0;
+    const uint32_t b_base = a_base + GEMM_A_STAGES * GEMM_A_BYTES;
+    const uint32_t lut_addr = b_base + GEMM_B_STAGES * GEMM_B_BYTES;
+    const uint32_t bar_base = lut_addr + GEMM_LUT_BYTES;
+    auto bar_afull = [&](int s) { return bar_base + 8u * s; };             // 3
+    auto bar_aempty = [&](int s) { return bar_base + 24u + 8u * s; };      // 3
+    auto bar_bfull = [&](int s) { return bar_base + 48u + 8u * s; };       // 2
+    auto bar_bempty = [&](int s) { return bar_base + 64u + 8u * s; };      // 2
+    const uint32_t bar_acc = bar_base + 80u;
+    const uint32_t tmem_slot = bar_base + 96u;
 
-    const int row_tile = blockIdx.x;                     // 128 rows
-    const int m0 = blockIdx.y * GEMM_MAX_NT;             // first token
+    const int row_tile = blockIdx.x;
+    const int m0 = blockIdx.y * P.tok_per_cta;
     int n_tok = P.M - m0;
-    if (n_tok > GEMM_MAX_NT) n_tok = GEMM_MAX_NT;
-    const uint32_t n_mma = (uint32_t)((n_tok + 15) & ~15);
+    if (n_tok > P.tok_per_cta) n_tok = P.tok_per_cta;
+    const int n_half0 = n_tok < GEMM_NT ? n_tok : GEMM_NT;
+    const int n_half1 = n_tok - n_half0;
+    const uint32_t n_mma0 = (uint32_t)((n_half0 + 15) & ~15), n_mma1 = (uint32_t)((n_half1 + 15) & ~15);
     const int rb0 = row_tile * GEMM_RB;
     int n_rb = W.RB - rb0;
     if (n_rb > GEMM_RB) n_rb = GEMM_RB;
-    const int total_stages = 2 * W.G;                    // 64-column stages over N
+    // column tiles of this split
+    const int split = blockIdx.z;
+    const int ct_per = (W.CT + P.splits - 1) / P.splits;
+    const int ct_begin = split * ct_per;
+    int ct_end = ct_begin + ct_per;
+    if (ct_end > W.CT) ct_end = W.CT;
+    int my_stages = 0;
+    for (int ct = ct_begin; ct < ct_end; ++ct) my_stages += 2 * tile_width(W, ct);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < P.stages; ++s) { mbar_init(bar_full(s), 256); mbar_init(bar_empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_cfull(b), 1); mbar_init(bar_cempty(b), 128); }
+        for (int s = 0; s < GEMM_A_STAGES; ++s) { mbar_init(bar_afull(s), 128); mbar_init(bar_aempty(s), 1); }
+        for (int s = 0; s < GEMM_B_STAGES; ++s) { mbar_init(bar_bfull(s), 1); mbar_init(bar_bempty(s), 1); }
         mbar_init(bar_acc, 1);
         mbar_fence_init();
         fence_proxy_async();
     }
     {   // expansion table replicas
-        LutEntry* lut_s = reinterpret_cast<LutEntry*>(smem + (lut_addr - s0));
+        LutEntry* lut_s = reinterpret_cast<LutEntry*>(sm + (lut_addr - s0));
         for (int i = threadIdx.x; i < LUT_ENTRIES * GEMM_LUT_COPIES; i += GEMM_THREADS) lut_s[i] = g_lut.e[i / GEMM_LUT_COPIES];
     }
-    if (warp == 8) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+    if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = lds32(tmem_slot);
 
-    if (warp < 4) {
+    if (warp < 8) {
         // =========================================================== decode + epilogue
-        const int r = threadIdx.x;                        // weight row within the CTA tile
+        const int group = warp >> 2;                      // takes stages with (q & 1) == group
+        const int r = threadIdx.x & 127;                  // weight row within the CTA tile
         const int rbl = r >> 4, rr = r & 15;
         const bool have_rb = rbl < n_rb;
-        const LutEntry* lut_lane = reinterpret_cast<const LutEntry*>(smem + (lut_addr - s0)) + (lane & (GEMM_LUT_COPIES - 1));
-        const uint32_t half_mask = (lane < 16) ? 0x0000FFFFu : 0xFFFF0000u;
+        const uint32_t lut_lane = lut_addr + (uint32_t)(lane & (GEMM_LUT_COPIES - 1)) * 8u;
+        const LutEntry* lut_lane_ptr = reinterpret_cast<const LutEntry*>(sm + (lut_addr - s0)) + (lane & (GEMM_LUT_COPIES - 1));
+        auto lut = [lut_lane](uint32_t idx) {
+            const uint2 e = lds64(lut_lane + idx * (GEMM_LUT_COPIES * 8u));
+            return LutEntry{e.x, e.y};
+        };
         bool healthy = true;
-        int q = 0;                                        // global stage counter
-        for (int ct = 0; ct < W.CT && healthy; ++ct) {
-            const int buf = ct & 1;
+        int q = 0;                                        // stage counter of this CTA (both groups count every stage)
+        for (int ct = ct_begin; ct < ct_end && healthy; ++ct) {
             const int w = tile_width(W, ct);
-            healthy = __all_sync(full_mask, mbar_wait_bounded(bar_cfull(buf), (uint32_t)(ct >> 1) & 1u, P.status, DEV_TIMEOUT_STAGE));
-            if (!healthy) break;
-            const uint32_t slot = ring_base + (uint32_t)(buf * GEMM_RB + rbl) * per_slot;
-            // this row's segments and where its codes start
+            // this row's segments, and where its codes start inside the tile
             uint4 mk[TILE_GROUPS];
             uint32_t szv[TILE_GROUPS];
             uint32_t cnt = 0;
+            const uint32_t* codes = nullptr;
+            if (have_rb) {
+                const uint8_t* tile = W.tiles + (size_t)__ldg(W.tile_off + (size_t)(rb0 + rbl) * W.CT + ct) * 16;
+                codes = reinterpret_cast<const uint32_t*>(tile + TILE_ROWS * w * 20);
 #pragma unroll
-            for (int gi = 0; gi < TILE_GROUPS; ++gi) {
-                mk[gi] = make_uint4(0, 0, 0, 0);
-                szv[gi] = 0;
-                if (have_rb && gi < w) {
-                    mk[gi] = lds128(slot + (rr * w + gi) * 16);
-                    szv[gi] = lds32(slot + TILE_ROWS * w * 16 + (rr * w + gi) * 4);
-                    cnt += __popc(mk[gi].x) + __popc(mk[gi].y) + __popc(mk[gi].z) + __popc(mk[gi].w);
+                for (int gi = 0; gi < TILE_GROUPS; ++gi) {
+                    mk[gi] = make_uint4(0, 0, 0, 0);
+                    szv[gi] = 0;
+                    if (gi < w) {
+                        mk[gi] = __ldg(reinterpret_cast<const uint4*>(tile) + rr * w + gi);
+                        szv[gi] = __ldg(reinterpret_cast<const uint32_t*>(tile + TILE_ROWS * w * 16) + rr * w + gi);
+                        cnt += __popc(mk[gi].x) + __popc(mk[gi].y) + __popc(mk[gi].z) + __popc(mk[gi].w);
+                    }
                 }
+            } else {
+#pragma unroll
+                for (int gi = 0; gi < TILE_GROUPS; ++gi) { mk[gi] = make_uint4(0, 0, 0, 0); szv[gi] = 0; }
             }
             uint32_t inc = cnt;
 #pragma unroll
@@ -183,60 +248,50 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
                 const uint32_t up = __shfl_up_sync(full_mask, inc, d, 16);
                 if ((lane & 15) >= d) inc += up;
             }
-            uint32_t off = inc - cnt;                      // first survivor of this row within the tile
-            uint32_t cbase = slot + TILE_ROWS * w * 20;
-            if (BITS < 4) {
-                const uint32_t total = __shfl_sync(full_mask, inc, 15, 16);
-                const uint32_t nchunks = (total + 7u) >> 3;
-                const uint32_t nibb = slot + P.slot_bytes;
-                if (have_rb) {
-                    for (uint32_t c = (uint32_t)(lane & 15); c < nchunks; c += 16) {
-                        uint32_t outv;
-                        if (BITS == 3) {
-                            const uint32_t bo = 3u * c, a = cbase + (bo & ~3u);
-                            outv = spread3(funnel_r(lds32(a), lds32(a + 4), (bo & 3u) * 8u) & 0x00FFFFFFu);
-                        } else {
-                            outv = spread2(lds32(cbase + (c >> 1) * 4u) >> (16u * (c & 1u)));
-                        }
-                        sts32(nibb + c * 4u, outv);
-                    }
-                }
-                __syncwarp(half_mask);
-                cbase = nibb;
-            }
+            uint32_t off = inc - cnt;                      // rank of this row's first survivor within the tile
+
             const int nks = 2 * w;                         // 64-column stages in this column tile
             for (int ks = 0; ks < nks; ++ks, ++q) {
-                const int gi = ks >> 1;
-                uint32_t m0w, m1w;
-                {
-                    const uint4 mm = mk[0];                // rotate so that index 0 is the current group
-                    m0w = (ks & 1) ? mm.z : mm.x;
-                    m1w = (ks & 1) ? mm.w : mm.y;
-                }
-                const SegParams sp = make_seg_params(szv[0], BITS, W.col_scale != nullptr);
-                uint32_t e0[16], e1[16];
-                float cs[32];
-                const float* csp = nullptr;
-                const int col = (ct * TILE_GROUPS + gi) * GROUP + (ks & 1) * 64;
-                uint32_t w0, w1, w2, w3;
-                if (W.col_scale != nullptr) {
-                    for (int i = 0; i < 32; ++i) cs[i] = half_bits_to_float(W.col_scale[col + i]);
-                    csp = cs;
-                }
-                load_window(cbase, off, w0, w1, w2, w3);
-                decode32<GEMM_LUT_COPIES>(m0w, w0, w1, w2, w3, sp, lut_lane, csp, e0);
-                off += __popc(m0w);
-                if (W.col_scale != nullptr)
-                    for (int i = 0; i < 32; ++i) cs[i] = half_bits_to_float(W.col_scale[col + 32 + i]);
-                load_window(cbase, off, w0, w1, w2, w3);
-                decode32<GEMM_LUT_COPIES>(m1w, w0, w1, w2, w3, sp, lut_lane, csp, e1);
-                off += __popc(m1w);
+                const uint32_t m0w = (ks & 1) ? mk[0].z : mk[0].x;
+                const uint32_t m1w = (ks & 1) ? mk[0].w : mk[0].y;
+                const uint32_t sz_cur = szv[0];
+                const uint32_t off0 = off, off1 = off + __popc(m0w);
+                off = off1 + __popc(m1w);
                 if (ks & 1) {                              // group finished: rotate the next one into slot 0
 #pragma unroll
                     for (int k2 = 0; k2 + 1 < TILE_GROUPS; ++k2) { mk[k2] = mk[k2 + 1]; szv[k2] = szv[k2 + 1]; }
                 }
-                const int s = q % P.stages;
-                healthy = __all_sync(full_mask, mbar_wait_bounded(bar_empty(s), (((uint32_t)(q / P.stages)) & 1u) ^ 1u,
+                if ((q & 1) != group) continue;            // the other group's stage
+                uint32_t raw0[5] = {0, 0, 0, 0, 0}, raw1[5] = {0, 0, 0, 0, 0};
+                if (have_rb) {
+                    fetch_window<BITS>(codes, off0, raw0);
+                    fetch_window<BITS>(codes, off1, raw1);
+                }
+                const SegParams sp = make_seg_params(sz_cur, BITS, W.col_scale != nullptr);
+                uint32_t e0[16], e1[16];
+                uint32_t w0, w1, w2, w3;
+                const int col = (ct * TILE_GROUPS + (ks >> 1)) * GROUP + (ks & 1) * 64;
+                if (sp.fast) {
+                    align_window<BITS>(raw0, off0, w0, w1, w2, w3);
+                    decode32_fast(m0w, w0, w1, w2, w3, sp, P.K, lut, e0);
+                    align_window<BITS>(raw1, off1, w0, w1, w2, w3);
+                    decode32_fast(m1w, w0, w1, w2, w3, sp, P.K, lut, e1);
+                } else {
+                    float cs[32];
+                    const float* csp = nullptr;
+                    if (W.col_scale != nullptr) {
+                        for (int i = 0; i < 32; ++i) cs[i] = half_bits_to_float(W.col_scale[col + i]);
+                        csp = cs;
+                    }
+                    align_window<BITS>(raw0, off0, w0, w1, w2, w3);
+                    decode32<GEMM_LUT_COPIES>(m0w, w0, w1, w2, w3, sp, lut_lane_ptr, csp, e0);
+                    if (W.col_scale != nullptr)
+                        for (int i = 0; i < 32; ++i) cs[i] = half_bits_to_float(W.col_scale[col + 32 + i]);
+                    align_window<BITS>(raw1, off1, w0, w1, w2, w3);
+                    decode32<GEMM_LUT_COPIES>(m1w, w0, w1, w2, w3, sp, lut_lane_ptr, csp, e1);
+                }
+                const int s = q % GEMM_A_STAGES;
+                healthy = __all_sync(full_mask, mbar_wait_bounded(bar_aempty(s), (((uint32_t)(q / GEMM_A_STAGES)) & 1u) ^ 1u,
                                                                   P.status, DEV_TIMEOUT_EMPTY));
                 if (!healthy) break;
                 const uint32_t rowaddr = a_base + s * GEMM_A_BYTES + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
@@ -247,112 +302,119 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
                     sts128(rowaddr + (((uint32_t)(c + 4) ^ x7) << 4), e1[4 * c], e1[4 * c + 1], e1[4 * c + 2], e1[4 * c + 3]);
                 }
                 fence_proxy_async();
-                mbar_arrive(bar_full(s));
+                mbar_arrive(bar_afull(s));
             }
-            if (healthy) mbar_arrive(bar_cempty(buf));
         }
-        // ---- epilogue: TMEM lane = weight row
-        if (healthy) healthy = __all_sync(full_mask, mbar_wait_bounded(bar_acc, 0u, P.status, DEV_TIMEOUT_ACC));
+        // ---- epilogue: TMEM lane = weight row; warp w drains accumulator w/4
+        if (healthy && my_stages > 0) healthy = __all_sync(full_mask, mbar_wait_bounded(bar_acc, 0u, P.status, DEV_TIMEOUT_ACC));
         tc_fence_after();
+        const int row = row_tile * GEMM_ROWS + r;
+        const int acc_id = group;
+        const int ntok_acc = acc_id ? n_half1 : n_half0;
+        const uint32_t nmma_acc = acc_id ? n_mma1 : n_mma0;
+        const int tok_base = m0 + acc_id * GEMM_NT;
+        const uint32_t tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        float* part = P.partials ? P.partials + ((size_t)tile_id * P.splits + split) * ((size_t)GEMM_TOKENS * GEMM_ROWS) : nullptr;
         if (healthy) {
-            const int row = row_tile * GEMM_ROWS + r;
-            for (uint32_t c0 = 0; c0 < n_mma; c0 += 32) {
+            for (uint32_t c0 = 0; c0 < nmma_acc; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + c0, v);
-                tmem_ld_wait();
-                if (row < W.K) {
+                if (my_stages > 0) {
+                    tmem_ld32(tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(acc_id * GEMM_NT) + c0, v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+                if (P.splits == 1) {
+                    if (row < W.K) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int tk = (int)c0 + i;
+                            if (tk < ntok_acc) P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(__uint_as_float(v[i]), P.bias, row);
+                        }
+                    }
+                } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int tok = m0 + (int)c0 + i;
-                        if (tok < P.M) P.y[(size_t)tok * P.ldy + row] = finish_output(__uint_as_float(v[i]), P.bias, row);
+                        const int tk = (int)c0 + i;
+                        if (tk < ntok_acc) part[(size_t)(acc_id * GEMM_NT + tk) * GEMM_ROWS + r] = __uint_as_float(v[i]);
                     }
                 }
             }
         }
         tc_fence_before();
-    } else if (warp < 8) {
-        // =========================================================== activation + compressed-tile loader
-        const int li = threadIdx.x - 128;                 // 0..127
-        bool healthy = true;
-        auto issue_ctile = [&](int ct) {                  // one thread: 8 bulk copies for column tile ct
-            const int buf = ct & 1;
-            uint32_t total = 0;
-            uint32_t o0[GEMM_RB], o1[GEMM_RB];
-            for (int b = 0; b < n_rb; ++b) {
-                o0[b] = W.tile_off[(rb0 + b) * W.CT + ct];
-                o1[b] = W.tile_off[(rb0 + b) * W.CT + ct + 1];
-                total += (o1[b] - o0[b]) * 16u;
-            }
-            fence_proxy_async();
-            mbar_arrive_expect_tx(bar_cfull(buf), total);
-            for (int b = 0; b < n_rb; ++b)
-                bulk_g2s(ring_base + (uint32_t)(buf * GEMM_RB + b) * per_slot, W.tiles + (size_t)o0[b] * 16,
-                         (o1[b] - o0[b]) * 16u, bar_cfull(buf));
-        };
-        if (li == 0) { issue_ctile(0); if (W.CT > 1) issue_ctile(1); }
-        int q = 0;
-        const int chunks = (int)n_mma * 8;                // 16-byte chunks per stage
-        for (int ct = 0; ct < W.CT && healthy; ++ct) {
-            const int w = tile_width(W, ct);
-            for (int ks = 0; ks < 2 * w && healthy; ++ks, ++q) {
-                const int col = ct * TILE_GROUPS * GROUP + ks * GEMM_KS;
-                const int s = q % P.stages;
-                uint4 v[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int idx = li + 128 * i;
-                    v[i] = make_uint4(0, 0, 0, 0);
-                    if (idx < chunks) {
-                        const int row = idx >> 3, ch = idx & 7;
-                        if (m0 + row < P.M)
-                            v[i] = __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)(m0 + row) * P.ldx + col + ch * 8));
+        if (P.splits > 1) {
+            // the last split to arrive adds all splits in order and writes the outputs
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");            // the 8 decode warps only
+            if (threadIdx.x == 0) sts32(bar_base + 104u, atomicAdd(&P.counters[tile_id], 1u));
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (lds32(bar_base + 104u) == (uint32_t)(P.splits - 1) && healthy) {
+                __threadfence();
+                const float* base = P.partials + (size_t)tile_id * P.splits * ((size_t)GEMM_TOKENS * GEMM_ROWS);
+                if (row < W.K) {
+                    for (int tk = 0; tk < ntok_acc; ++tk) {
+                        float sum = 0.0f;
+                        for (int k = 0; k < P.splits; ++k)
+                            sum += __ldcg(base + (size_t)k * ((size_t)GEMM_TOKENS * GEMM_ROWS) + (size_t)(acc_id * GEMM_NT + tk) * GEMM_ROWS + r);
+                        P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(sum, P.bias, row);
                     }
                 }
-                healthy = mbar_wait_bounded(bar_empty(s), (((uint32_t)(q / P.stages)) & 1u) ^ 1u, P.status, DEV_TIMEOUT_EMPTY);
-                if (!healthy) break;
-                const uint32_t bs = b_base + s * GEMM_B_BYTES;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int idx = li + 128 * i;
-                    if (idx < chunks) {
-                        const uint32_t row = (uint32_t)idx >> 3, ch = (uint32_t)idx & 7u;
-                        sts128(bs + (row >> 3) * 1024u + (row & 7u) * 128u + ((ch ^ (row & 7u)) << 4), v[i].x, v[i].y, v[i].z, v[i].w);
-                    }
-                }
-                fence_proxy_async();
-                mbar_arrive(bar_full(s));
+                if (threadIdx.x == 0) P.counters[tile_id] = 0u;
             }
-            // refill the compressed ring two column tiles ahead once the decoders released this buffer
-            if (li == 0 && healthy && ct + 2 < W.CT) {
-                healthy = mbar_wait_bounded(bar_cempty(ct & 1), (uint32_t)(ct >> 1) & 1u, P.status, DEV_TIMEOUT_STAGE);
-                if (healthy) issue_ctile(ct + 2);
-            }
-            healthy = __all_sync(full_mask, healthy);
         }
+    } else if (warp == 8) {
+        // =========================================================== activation loader (TMA)
+        if (lane == 0) {
+            bool healthy = true;
+            int q = 0;
+            const uint32_t bytes = (uint32_t)GEMM_BHALF_BYTES * (n_half1 > 0 ? 2u : 1u);
+            for (int ct = ct_begin; ct < ct_end && healthy; ++ct) {
+                const int w = tile_width(W, ct);
+                for (int ks = 0; ks < 2 * w; ++ks, ++q) {
+                    const int s = q % GEMM_B_STAGES;
+                    healthy = mbar_wait_bounded(bar_bempty(s), (((uint32_t)(q / GEMM_B_STAGES)) & 1u) ^ 1u, P.status, DEV_TIMEOUT_EMPTY);
+                    if (!healthy) break;
+                    const int col = ct * TILE_GROUPS * GROUP + ks * GEMM_KS;
+                    mbar_arrive_expect_tx(bar_bfull(s), bytes);
+                    tma_load_2d(b_base + s * GEMM_B_BYTES, &xmap, col, m0, bar_bfull(s));
+                    if (n_half1 > 0) tma_load_2d(b_base + s * GEMM_B_BYTES + GEMM_BHALF_BYTES, &xmap, col, m0 + GEMM_NT, bar_bfull(s));
+                }
+            }
+        }
+        __syncwarp();
     } else {
         // =========================================================== MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(n_mma);
+            const uint32_t idesc0 = umma_idesc(n_mma0), idesc1 = umma_idesc(n_mma1 ? n_mma1 : 16);
             bool healthy = true;
-            for (int q = 0; q < total_stages && healthy; ++q) {
-                const int s = q % P.stages;
-                healthy = mbar_wait_bounded(bar_full(s), ((uint32_t)(q / P.stages)) & 1u, P.status, DEV_TIMEOUT_FULL);
+            for (int q = 0; q < my_stages && healthy; ++q) {
+                const int sa = q % GEMM_A_STAGES, sb = q % GEMM_B_STAGES;
+                healthy = mbar_wait_bounded(bar_afull(sa), ((uint32_t)(q / GEMM_A_STAGES)) & 1u, P.status, DEV_TIMEOUT_FULL);
+                if (healthy) healthy = mbar_wait_bounded(bar_bfull(sb), ((uint32_t)(q / GEMM_B_STAGES)) & 1u, P.status, DEV_TIMEOUT_STAGE);
                 if (!healthy) break;
                 tc_fence_after();
-                const uint64_t ad = umma_smem_desc(a_base + s * GEMM_A_BYTES);
-                const uint64_t bd = umma_smem_desc(b_base + s * GEMM_B_BYTES);
+                const uint64_t ad = umma_smem_desc(a_base + sa * GEMM_A_BYTES);
+                const uint64_t bd0 = umma_smem_desc(b_base + sb * GEMM_B_BYTES);
+                const uint64_t bd1 = umma_smem_desc(b_base + sb * GEMM_B_BYTES + GEMM_BHALF_BYTES);
 #pragma unroll
                 for (int k = 0; k < GEMM_KS / 16; ++k)
-                    umma_bf16(tmem_d, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, (q > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar_empty(s));
+                    umma_bf16(tmem_d, ad + (uint64_t)(2 * k), bd0 + (uint64_t)(2 * k), idesc0, (q > 0 || k > 0) ? 1u : 0u);
+                if (n_mma1) {
+#pragma unroll
+                    for (int k = 0; k < GEMM_KS / 16; ++k)
+                        umma_bf16(tmem_d + GEMM_NT, ad + (uint64_t)(2 * k), bd1 + (uint64_t)(2 * k), idesc1, (q > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_aempty(sa));
+                umma_commit(bar_bempty(sb));
             }
-            if (healthy) umma_commit(bar_acc);
+            if (healthy && my_stages > 0) umma_commit(bar_acc);
         }
         __syncwarp();
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem_d, 256); }
+    if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_d, 512); }
 }
 
 }  // namespace cb

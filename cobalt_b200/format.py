@@ -18,7 +18,7 @@ with a single bulk copy:
                                   order, ascending column, little-endian bits
     padded to a multiple of 16 B
 
-``tile_off`` counts 16-byte units from the first tile.  Rows are padded to a
+``tile_off`` counts 16-byte units from the first tile; 64 zero bytes follow the last tile.  Rows are padded to a
 multiple of 16 with empty (all-pruned) rows.  Everything is torch, so packing
 runs on whatever device the inputs live on.
 """
@@ -32,6 +32,7 @@ GROUP = 128
 TILE_ROWS = 16
 TILE_GROUPS = 4
 HEADER_ALIGN = 256
+TAIL_SLACK = 64          # bytes after the last tile: the decoders read whole words a little past the codes
 
 
 @dataclass
@@ -121,7 +122,7 @@ def pack_tiles(keep: torch.Tensor, q: torch.Tensor, scale: torch.Tensor, zero: t
     total_tiles_bytes = int(tb_flat.sum())
     n_tiles = RB * CT
     header_bytes = _round_up(4 * (n_tiles + 1), HEADER_ALIGN)
-    nwords = (header_bytes + total_tiles_bytes) // 4
+    nwords = (header_bytes + total_tiles_bytes) // 4 + TAIL_SLACK // 4     # readable slack after the last tile
     words = torch.zeros(nwords + 2, dtype=torch.int64, device=dev)
 
     # ---- header

@@ -118,9 +118,16 @@ class CobaltSparseLinear(nn.Module):
             need = lib.cobalt_gemm_scratch_bytes(ctypes.byref(d), M)
         if need == 0:
             raise _lib.CobaltError("cobalt_*_scratch_bytes", -1, "could not size the scratch buffer")
-        if self._scratch is None or self._scratch.numel() < need or self._scratch.device != self.packed.device:
-            self._scratch = torch.zeros(need + 256, dtype=torch.uint8, device=self.packed.device)
-        return self._scratch
+        # one buffer per kernel kind: the two entry points lay their counters out differently and each
+        # relies on finding them zero
+        kind = "gemv" if M <= GEMV_MAX_TOKENS else "gemm"
+        cur = self._scratch.get(kind) if isinstance(self._scratch, dict) else None
+        if cur is None or cur.numel() < need + 256 or cur.device != self.packed.device:
+            if not isinstance(self._scratch, dict):
+                self._scratch = {}
+            cur = torch.zeros(need + 256, dtype=torch.uint8, device=self.packed.device)
+            self._scratch[kind] = cur
+        return cur
 
     @staticmethod
     def _aligned(t: torch.Tensor, a: int = 256) -> int:
@@ -180,12 +187,15 @@ class CobaltSparseLinear(nn.Module):
 
     def device_status(self) -> int:
         """Status word of the last kernels that used this module's scratch buffer (0 = healthy)."""
-        if self._scratch is None:
+        if not self._scratch:
             return 0
-        out = ctypes.c_uint32(0)
-        _lib.load().cobalt_device_status(self._aligned(self._scratch),
-                                         torch.cuda.current_stream(self.packed.device).cuda_stream, ctypes.byref(out))
-        return int(out.value)
+        worst = 0
+        for buf in self._scratch.values():
+            out = ctypes.c_uint32(0)
+            _lib.load().cobalt_device_status(self._aligned(buf), torch.cuda.current_stream(self.packed.device).cuda_stream,
+                                             ctypes.byref(out))
+            worst = max(worst, int(out.value))
+        return worst
 
     def compressed_bytes(self) -> int:
         return TileImage.from_meta(self.packed, self._img_meta).algorithmic_bytes()

@@ -72,7 +72,9 @@ const char* cobalt_strerror(int status);
  * and, above it, SparseQuantLinear.forward for small batches (benchmarks/benchmark_suite.py:1200-1217).
  * `scratch` holds split-K partial sums and per-row-block arrival counters; it must be at least
  * cobalt_gemv_scratch_bytes() bytes, 256-byte aligned and ZERO before its first use (the kernel
- * leaves the counters zero again).  Calls sharing one scratch buffer must not overlap on the GPU. */
+ * leaves the counters zero again).  Calls sharing one scratch buffer must not overlap on the GPU,
+ * and a buffer must not be shared between cobalt_gemv() and cobalt_gemm() without re-zeroing it
+ * (their counters are laid out differently). */
 int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
                 const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
 size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M);
@@ -112,7 +114,8 @@ int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y,
 
 /* Prefill GEMM, any M >= 1 (meant for M >= 17): same arithmetic contract as cobalt_gemv().
  * Weight tiles are dequantised to bf16 in shared memory and multiplied with tcgen05.mma,
- * accumulators in tensor memory.
+ * accumulators in tensor memory; activations arrive through a TMA tensor map.  The tile image
+ * must be followed by at least 64 readable bytes (the packer appends them).
  * Replaces cbk::gemm_tile + gemm_phase (src/cobaltkernel/csrc/cobalt_gemm.cuh:243-609,
  * src/cobaltkernel/csrc/prefill_kernel.cu:103-150).  `scratch` as for cobalt_gemv(). */
 int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
@@ -145,7 +148,7 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
 int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out);
 
 /* Benchmark tuning hook (not part of the stable contract): key 0 = GEMV grid size
- * (CTAs), 1 = GEMV ring stages, 2 = GEMM operand stages; value 0 restores the built-in heuristic.
+ * (CTAs), 1 = GEMV ring stages, 2 = GEMM split-K factor; value 0 restores the built-in heuristic.
  * No counterpart in the reference, whose knobs are compile-time macros (src/cobaltkernel/runner.py:52-206). */
 int cobalt_set_tuning(int key, int value);
 
