@@ -45,6 +45,8 @@ EXPORTS = {
     "cobalt_gemm": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                             c_size_t, c_void_p]),
     "cobalt_gemm_scratch_bytes": (c_size_t, [POINTER(CobaltMat), c_int]),
+    "cobalt_linear_f32": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_size_t,
+                                  c_void_p]),
     "cobalt_dequant": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p]),
     "cobalt_unpack": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p]),
     "cobalt_linear_host": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,

@@ -190,7 +190,7 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
 
 // shared body of cobalt_gemv() and cobalt_gemv_static()
 int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
-              void* scratch, size_t scratch_bytes, bool clear_counters, void* stream) {
+              void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, bool fp32_out = false) {
     int rc = check_mat(w);
     if (rc) return rc;
     if (M > MAX_GEMV_M) return COBALT_EINVAL;
@@ -212,7 +212,8 @@ int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t l
     GemvParams P;
     P.W = make_view(w);
     P.x = (const uint16_t*)x; P.ldx = ldx;
-    P.y = (uint16_t*)y; P.ldy = ldy;
+    P.y = fp32_out ? nullptr : (uint16_t*)y; P.ldy = ldy;
+    P.y32 = fp32_out ? (float*)y : nullptr;
     P.bias = (const uint16_t*)bias;
     P.M = M;
     P.stages = c.stages;
@@ -343,8 +344,8 @@ size_t cobalt_gemm_scratch_bytes(const CobaltMat* w, int M) {
     return c.total;
 }
 
-int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
-                void* scratch, size_t scratch_bytes, void* stream) {
+static int gemm_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+                     void* scratch, size_t scratch_bytes, void* stream, bool fp32_out) {
     int rc = check_mat(w);
     if (rc) return rc;
     rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
@@ -361,7 +362,8 @@ int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
     if (rc) return rc;
     GemmParams P;
     P.W = make_view(w);
-    P.y = (uint16_t*)y; P.ldy = ldy;
+    P.y = fp32_out ? nullptr : (uint16_t*)y; P.ldy = ldy;
+    P.y32 = fp32_out ? (float*)y : nullptr;
     P.bias = (const uint16_t*)bias;
     P.M = M;
     P.splits = c.splits;
@@ -376,6 +378,17 @@ int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
         case 3: return launch_gemm<3>(P, xmap, c, st);
         default: return launch_gemm<4>(P, xmap, c, st);
     }
+}
+
+int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+                void* scratch, size_t scratch_bytes, void* stream) {
+    return gemm_impl(w, x, ldx, y, ldy, bias, M, scratch, scratch_bytes, stream, false);
+}
+
+int cobalt_linear_f32(const CobaltMat* w, const void* x, int64_t ldx, float* y, int64_t ldy, int M, void* scratch,
+                      size_t scratch_bytes, void* stream) {
+    if (M <= MAX_GEMV_M) return gemv_impl(w, x, ldx, y, ldy, nullptr, M, scratch, scratch_bytes, false, stream, true);
+    return gemm_impl(w, x, ldx, y, ldy, nullptr, M, scratch, scratch_bytes, stream, true);
 }
 
 int cobalt_dequant(const CobaltMat* w, void* w_bf16, void* stream) {

@@ -54,6 +54,7 @@ constexpr uint32_t GEMM_SMEM_BYTES = GEMM_A_STAGES * GEMM_A_BYTES + GEMM_B_STAGE
 struct GemmParams {
     MatView W;
     uint16_t* y; int64_t ldy;
+    float* y32;                 // when set, raw fp32 sums go here instead (no bias, no rounding)
     const uint16_t* bias;
     int M;
     int tok_per_cta;            // tokens per CTA: 512, or less (multiple of 16) to spread a small problem over more SMs
@@ -330,7 +331,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int tk = (int)c0 + i;
-                            if (tk < ntok_acc) P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(__uint_as_float(v[i]), P.bias, row);
+                            if (tk < ntok_acc) {
+                                if (P.y32) P.y32[(size_t)(tok_base + tk) * P.ldy + row] = __uint_as_float(v[i]);
+                                else P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(__uint_as_float(v[i]), P.bias, row);
+                            }
                         }
                     }
                 } else {
@@ -357,7 +361,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
                         float sum = 0.0f;
                         for (int k = 0; k < P.splits; ++k)
                             sum += __ldcg(base + (size_t)k * ((size_t)GEMM_TOKENS * GEMM_ROWS) + (size_t)(acc_id * GEMM_NT + tk) * GEMM_ROWS + r);
-                        P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(sum, P.bias, row);
+                        if (P.y32) P.y32[(size_t)(tok_base + tk) * P.ldy + row] = sum;
+                        else P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(sum, P.bias, row);
                     }
                 }
                 if (threadIdx.x == 0) P.counters[tile_id] = 0u;

@@ -33,6 +33,7 @@ struct GemvParams {
     MatView W;
     const uint16_t* x; int64_t ldx;
     uint16_t* y; int64_t ldy;
+    float* y32;                          // when set, raw fp32 sums go here instead (no bias, no rounding)
     const uint16_t* bias;
     int M;
     int stages;
@@ -182,6 +183,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
+            if (P.y32) {
+                if (row0 < W.K) {
+                    if (tok0 < P.M) P.y32[(size_t)tok0 * P.ldy + row0] = acc[b][0];
+                    if (tok1 < P.M) P.y32[(size_t)tok1 * P.ldy + row0] = acc[b][1];
+                }
+                if (row1 < W.K) {
+                    if (tok0 < P.M) P.y32[(size_t)tok0 * P.ldy + row1] = acc[b][2];
+                    if (tok1 < P.M) P.y32[(size_t)tok1 * P.ldy + row1] = acc[b][3];
+                }
+                continue;
+            }
             if (row0 < W.K) {
                 if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row0] = finish_output(acc[b][0], P.bias, row0);
                 if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row0] = finish_output(acc[b][1], P.bias, row0);

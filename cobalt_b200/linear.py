@@ -134,7 +134,9 @@ class CobaltSparseLinear(nn.Module):
         return (t.data_ptr() + a - 1) // a * a
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out_fp32: bool = False) -> torch.Tensor:
+        """``out_fp32`` returns the raw fp32 sums (no bias, no rounding) -- the partial output a row-parallel
+        shard hands to its all-reduce."""
         if not x.is_cuda:
             raise RuntimeError("CobaltSparseLinear.forward needs a CUDA tensor; there is no CPU path")
         if x.dtype != torch.bfloat16:
@@ -145,7 +147,7 @@ class CobaltSparseLinear(nn.Module):
         if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
             x2 = x2.contiguous()
         M = x2.shape[0]
-        y = torch.empty(M, self.out_features, dtype=torch.bfloat16, device=x.device)
+        y = torch.empty(M, self.out_features, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
         if M == 0:
             return y.reshape(*lead, self.out_features)
         d = self._descriptor()
@@ -154,7 +156,11 @@ class CobaltSparseLinear(nn.Module):
         sbytes = scratch.numel() - (sp - scratch.data_ptr())
         stream = torch.cuda.current_stream(x.device).cuda_stream
         bias = None if self.bias is None else self.bias.data.to(torch.bfloat16)
-        if M <= GEMV_MAX_TOKENS:
+        if out_fp32:
+            rc = lib.cobalt_linear_f32(ctypes.byref(d), x2.data_ptr(), x2.stride(0), y.data_ptr(), y.stride(0), M, sp, sbytes,
+                                       stream)
+            _lib.check("cobalt_linear_f32", rc)
+        elif M <= GEMV_MAX_TOKENS:
             rc = lib.cobalt_gemv(ctypes.byref(d), x2.data_ptr(), x2.stride(0), y.data_ptr(), y.stride(0), _ptr(bias), M,
                                  sp, sbytes, stream)
             _lib.check("cobalt_gemv", rc)

@@ -122,6 +122,13 @@ int cobalt_gemm(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
                 const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
 size_t cobalt_gemm_scratch_bytes(const CobaltMat* w, int M);
 
+/* Same product with the raw fp32 sums as output (no bias, no rounding): M <= 16 runs the GEMV,
+ * larger M the GEMM.  For row-parallel tensor-parallel layers, whose partial outputs are added
+ * across GPUs before the single rounding to bf16.  Scratch as for the kernel that runs.
+ * No counterpart in the reference, which has no distributed code. */
+int cobalt_linear_f32(const CobaltMat* w, const void* x, int64_t ldx, float* y, int64_t ldy, int M,
+                      void* scratch, size_t scratch_bytes, void* stream);
+
 /* Dense bf16 weight [K, N] (row-major, ld = N), bit-identical to the reference's
  * dequantize_sparse_sinq(...).to(bfloat16) (sinq/sparse_quant.py:1635-1681):
  * bf16_rne( fp32(q - z) * fp32(s) [* fp32(col_scale)] ) * keep.

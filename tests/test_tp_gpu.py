@@ -1,0 +1,62 @@
+"""Tensor-parallel block on real GPUs (needs >= 2): NCCL ranks as child processes, every shard
+through the CUDA kernels, result against the unsharded CPU oracle."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out):
+    import torch.distributed as dist
+    from cobalt_b200 import CobaltSparseLinear, tp
+    from oracle import cobalt_oracle as O
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        res = {}
+        for M in (1, 8, 64):
+            raw = O.synth_raw(256, 2048, 0.5, 4, seed=31)
+            keep, q, sc, zr = raw["keep"], raw["q"], raw["scale"], raw["zero"]
+            Wb = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)
+            x = O.seeded_activation(M, 2048, 32 + M)
+            full = torch.matmul(x, Wb.t())
+
+            def mod(kind):
+                k, qq, s, z = tp.shard_raw(kind, keep, q, sc, zr, rank, world)
+                return CobaltSparseLinear(qq.cuda(), s.cuda(), z.cuda(), k.cuda(), None, None, {"nbits": 4})
+            col = tp.ColumnParallelLinear(mod("column"), gather_output=True)
+            y_col = col(x.cuda()).cpu()
+            c0, c1 = tp.shard_bounds(2048, rank, world, 128)
+            row = tp.RowParallelLinear(mod("row"))
+            y_row = row(x[:, c0:c1].contiguous().cuda()).cpu()
+            rel_c = float((y_col.double() - full.double()).norm() / full.double().norm())
+            rel_r = float((y_row.double() - full.double()).norm() / full.double().norm())
+            res[M] = (rel_c, rel_r, float((y_row.double() - full.double()).abs().max()))
+        out[rank] = res
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_shards_through_kernels():
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    for rank in range(world):
+        for M, (rel_c, rel_r, maxabs) in out[rank].items():
+            assert rel_c <= 1e-3, f"rank {rank} M={M}: column-parallel rel-L2 {rel_c}"
+            assert rel_r <= 1e-3, f"rank {rank} M={M}: row-parallel rel-L2 {rel_r}"
