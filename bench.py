@@ -11,7 +11,8 @@ the 126 MB L2).
 
   value      GB/s of algorithmic compressed bytes (bitmask + codes + fp16 scale/zero +
              activations in/out) with all inputs resident in HBM, timed with CUDA events
-             around K steps replayed from a CUDA graph.
+             around K steps replayed from a CUDA graph.  q|k|v and gate|up read the same
+             activations and go out as one fused launch each (4 launches per step).
   e2e        the same metric through cobalt_linear_host(): pinned host activations copied
              in, result copied back, every call.
   roofline   the GEMV kernel against the measured HBM copy bandwidth.
@@ -177,25 +178,41 @@ def run_ours(args):
     xs = {name: (torch.randn(M, v["N"], device=dev) ).to(torch.bfloat16) for name, v in info.items()}
     ys = {name: torch.empty(M, v["K"], dtype=torch.bfloat16, device=dev) for name, v in info.items()}
 
-    def one_step(blk):
-        for name, _, _ in SHAPES_7B:
-            if world > 1 and name in ROW_PARALLEL:          # fp32 partial sums, one all-reduce, one rounding
+    from cobalt_b200 import FusedProjections
+    names = [t[0] for t in SHAPES_7B]
+    fuse_groups = [] if args.no_fuse else [g for g in (("q", "k", "v"), ("gate", "up")) if all(n in names for n in g)]
+    fused_of = {n: g for g in fuse_groups for n in g}
+    launches_per_step = len(names) - sum(len(g) - 1 for g in fuse_groups)
+
+    def make_fused(blk):
+        return {g: FusedProjections([blk[n] for n in g]) for g in fuse_groups}
+
+    def one_step(blk, fused):
+        done = set()
+        for name in names:
+            if name in done:
+                continue
+            if name in fused_of:                            # q|k|v and gate|up share their activations: one launch
+                fused[fused_of[name]](xs[name])
+                done.update(fused_of[name])
+            elif world > 1 and name in ROW_PARALLEL:        # fp32 partial sums, one all-reduce, one rounding
                 part = blk[name](xs[name], out_fp32=True)
                 dist.all_reduce(part)
                 ys[name].copy_(part)
             else:
                 blk[name](xs[name])
 
+    fuseds = [make_fused(b) for b in blocks]
     with torch.cuda.stream(stream):
-        for b in blocks:                                     # allocate scratch, configure kernels
-            one_step(b)
+        for b, f in zip(blocks, fuseds):                     # allocate scratch, configure kernels
+            one_step(b, f)
         stream.synchronize()
         graph = None
         if world == 1 and not args.profile:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                for b in blocks:
-                    one_step(b)
+                for b, f in zip(blocks, fuseds):
+                    one_step(b, f)
 
         def run_steps(n):
             done = 0
@@ -204,7 +221,7 @@ def run_ours(args):
                     graph.replay()
                     done += len(blocks)
                 else:
-                    one_step(blocks[done % len(blocks)])
+                    one_step(blocks[done % len(blocks)], fuseds[done % len(blocks)])
                     done += 1
 
         run_steps(max(args.warmup, 3))
@@ -321,11 +338,11 @@ def run_ours(args):
         "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": int(sum(M * v["N"] * 2 for v in info.values())),
                 "d2h_bytes_per_step": int(sum(M * v["K"] * 2 for v in info.values()))},
-        "gpu_launches": int(args.steps * len(SHAPES_7B)),
+        "gpu_launches": int(args.steps * launches_per_step),
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(value / world / peak, 4), "traffic": None,
-                     "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": len(SHAPES_7B),
-                     "bytes_per_launch": int((wbytes + abytes) / len(SHAPES_7B))},
+                     "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": launches_per_step,
+                     "bytes_per_launch": int((wbytes + abytes) / launches_per_step)},
         "device_status": status,
         "per_shape": per_shape,
     }
@@ -446,6 +463,50 @@ def run_prefill(args):
                       "cases": cases}), flush=True)
 
 
+# ----------------------------------------------------------------------------- full decode (7B shape)
+def run_model(args):
+    """Random-init Mistral-7B-shaped decoder, every projection 4-bit / 50 % sparse: the KV cache is pre-filled
+    with 2048 seeded random tokens (one prefill through the tcgen05 GEMM), then 256 greedy tokens are decoded
+    from a CUDA graph.  Prints tokens/s over the replayed decode steps (the prefill is not timed)."""
+    from cobalt_b200 import SparseQuantConfig
+    from cobalt_b200.decoder import build_random_decoder
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = dict(model_type="mistral", hidden_size=4096, num_hidden_layers=args.layers, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rms_norm_eps=1e-5,
+               rope_theta=1e6, sliding_window=None)
+    ctx, n_new = args.context, args.new_tokens
+    dec = build_random_decoder(cfg, SparseQuantConfig(BITS, SPARSITY, BETA), ctx + n_new, dev)
+    g = torch.Generator().manual_seed(2048)
+    prompt = torch.randint(0, cfg["vocab_size"], (ctx,), generator=g)
+    t0 = time.perf_counter()
+    dec.generate(prompt, 4, use_graph=True)                     # prefill + graph capture + a few steps (warm-up)
+    torch.cuda.synchronize()
+    warm_s = time.perf_counter() - t0
+    # timed: replay the captured step n_new times (token and position advance on the device)
+    dec.pos.fill_(ctx)
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(n_new):
+        dec._graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / n_new
+    wbytes = sum(m.compressed_bytes() for m in dec.lin.values())
+    status = max(m.device_status() for m in dec.lin.values())
+    print(json.dumps({"metric": "7B-shape decode tokens/s (batch 1)", "value": round(1e3 / ms, 2), "unit": "tokens/s",
+                      "ms_per_token": round(ms, 4), "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"Mistral-7B shape, {cfg['num_hidden_layers']} layers, {BITS}-bit {int(SPARSITY*100)}% sparse, "
+                                             f"context {ctx}, {n_new} greedy tokens, CUDA graph; dense bf16 lm_head",
+                                 "compressed_bytes_per_token": int(wbytes), "lm_head_bytes": 32000 * 4096 * 2},
+                      "linear_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "clocks": clocks, "device_status": status,
+                      "warmup_s": round(warm_s, 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -453,17 +514,24 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=1, help="decode batch M (1..16)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode = headline 7B block GEMV bench; prefill = tcgen05 GEMM sweep (single GPU)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
+                    help="decode = headline 7B block GEMV bench; prefill = tcgen05 GEMM sweep; model = full 7B-shape "
+                         "greedy decode tokens/s (both single GPU)")
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--prefill-m", default="128,512,2048")
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--debug-flags", type=int, default=0, help="kernel experiment switches (results become invalid)")
+    ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")
     args = ap.parse_args()
     if args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "model":
+        run_model(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -12,9 +12,9 @@ are reached through the C ABI in ``include/cobalt_b200.h``; there is no fallback
 """
 from .compress import SparseQuantConfig, compress_weight, keep_mask, quantize_survivors
 from .format import TileImage, pack_tiles, slice_cols, slice_rows
-from .linear import CobaltSparseLinear
+from .linear import CobaltSparseLinear, FusedProjections
 from .patch import patch_linearlayers, patch_model
 
-__all__ = ["CobaltSparseLinear", "patch_model", "patch_linearlayers", "SparseQuantConfig", "compress_weight",
+__all__ = ["CobaltSparseLinear", "FusedProjections", "patch_model", "patch_linearlayers", "SparseQuantConfig", "compress_weight",
            "keep_mask", "quantize_survivors", "pack_tiles", "TileImage", "slice_rows", "slice_cols"]
 __version__ = "0.1.0"

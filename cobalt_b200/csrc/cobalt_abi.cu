@@ -69,17 +69,21 @@ struct GemvCfg {
     size_t smem, counters_off, partials_off, total;
 };
 
-uint32_t nibble_bytes(const CobaltMat* w) {
-    if (w->bits == 4) return 0;
-    // survivors of the fullest tile, 4 bits each, plus read-ahead slack
-    return (uint32_t)round_up((size_t)w->max_tile_nnz / 2 + 64, 128);
+// geometry shared by the matrices of one (possibly fused) GEMV launch
+struct GemvGeom { int RB, CT, bits; uint32_t max_tile_bytes, max_tile_nnz; };
+
+GemvGeom geom_of(const CobaltMat* w) {
+    GemvGeom g;
+    g.RB = w->n_row_blocks; g.CT = w->n_col_tiles; g.bits = w->bits;
+    g.max_tile_bytes = w->max_tile_bytes; g.max_tile_nnz = w->max_tile_nnz;
+    return g;
 }
 
-int gemv_config(const CobaltMat* w, int M, int num_sms, GemvCfg* c) {
-    const int RB = w->n_row_blocks, CT = w->n_col_tiles;
+int gemv_config(const GemvGeom& g, int M, int num_sms, GemvCfg* c) {
+    const int RB = g.RB, CT = g.CT;
     c->mt = M > 8 ? 2 : 1;
-    c->slot = (uint32_t)round_up((size_t)w->max_tile_bytes + 32, 128);
-    c->nib = nibble_bytes(w);
+    c->slot = (uint32_t)round_up((size_t)g.max_tile_bytes + 32, 128);
+    c->nib = g.bits == 4 ? 0u : (uint32_t)round_up((size_t)g.max_tile_nnz / 2 + 64, 128);
     const size_t fixed = GEMV_LUT_BYTES + GEMV_BAR_BYTES + 64;
     int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : GEMV_MAX_STAGES;
     if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
@@ -111,8 +115,20 @@ int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
             return COBALT_ELAUNCH;
         configured[dev] = true;
     }
-    gemv_mma_kernel<BITS, MT><<<c.grid, GEMV_THREADS, c.smem, st>>>(P);
-    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+    // programmatic stream serialisation: the prologue of this kernel (barrier set-up, table fill, first weight
+    // tiles) may overlap the tail of the previous kernel in the stream; the kernel itself waits before it
+    // touches activations or scratch
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)c.grid);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = c.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<BITS, MT>, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 // ----------------------------------------------------------------------------- GEMM configuration
@@ -188,19 +204,32 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
-// shared body of cobalt_gemv() and cobalt_gemv_static()
-int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
-              void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, bool fp32_out = false) {
-    int rc = check_mat(w);
-    if (rc) return rc;
-    if (M > MAX_GEMV_M) return COBALT_EINVAL;
-    rc = check_io(x, ldx, y, ldy, M, w->K, w->N);
-    if (rc) return rc;
+// shared body of every GEMV entry point: `n` matrices that share x, N and the bit width
+struct GemvOut { void* y; int64_t ldy; const void* bias; };
+
+int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void* x, int64_t ldx, int M, bool fp32_out,
+                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream) {
+    if (n < 1 || n > GEMV_MAX_MATS || !w || !out) return COBALT_EINVAL;
+    if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
+    GemvGeom g = {};
+    for (int i = 0; i < n; ++i) {
+        int rc = check_mat(w[i]);
+        if (rc) return rc;
+        rc = check_io(x, ldx, out[i].y, out[i].ldy, M, w[i]->K, w[i]->N);
+        if (rc) return rc;
+        if (i == 0) g = geom_of(w[0]);
+        else {
+            if (w[i]->N != w[0]->N || w[i]->bits != w[0]->bits || w[i]->col_scale || w[0]->col_scale) return COBALT_EINVAL;
+            g.RB += w[i]->n_row_blocks;
+            if (w[i]->max_tile_bytes > g.max_tile_bytes) g.max_tile_bytes = w[i]->max_tile_bytes;
+            if (w[i]->max_tile_nnz > g.max_tile_nnz) g.max_tile_nnz = w[i]->max_tile_nnz;
+        }
+    }
     int sms = 0;
-    rc = device_info(&sms);
+    int rc = device_info(&sms);
     if (rc) return rc;
     GemvCfg c;
-    rc = gemv_config(w, M, sms, &c);
+    rc = gemv_config(g, M, sms, &c);
     if (rc) return rc;
     if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
     cudaStream_t st = (cudaStream_t)stream;
@@ -209,12 +238,23 @@ int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t l
         // sums behind them are always written before they are read
         if (cudaMemsetAsync(scratch, 0, c.partials_off, st) != cudaSuccess) return COBALT_ELAUNCH;
     }
-    GemvParams P;
-    P.W = make_view(w);
+    GemvParams P = {};
+    P.n_mats = n;
+    int rb = 0;
+    for (int i = 0; i < n; ++i) {
+        P.mat[i].tiles = (const uint8_t*)w[i]->tiles;
+        P.mat[i].tile_off = w[i]->tile_off;
+        P.mat[i].y = fp32_out ? nullptr : (uint16_t*)out[i].y;
+        P.mat[i].y32 = fp32_out ? (float*)out[i].y : nullptr;
+        P.mat[i].bias = (const uint16_t*)out[i].bias;
+        P.mat[i].ldy = out[i].ldy;
+        P.mat[i].K = w[i]->K;
+        P.mat[i].rb_start = rb;
+        rb += w[i]->n_row_blocks;
+    }
+    P.N = w[0]->N; P.G = w[0]->N / GROUP; P.CT = g.CT; P.RB = g.RB;
+    P.col_scale = (const uint16_t*)w[0]->col_scale;
     P.x = (const uint16_t*)x; P.ldx = ldx;
-    P.y = fp32_out ? nullptr : (uint16_t*)y; P.ldy = ldy;
-    P.y32 = fp32_out ? (float*)y : nullptr;
-    P.bias = (const uint16_t*)bias;
     P.M = M;
     P.stages = c.stages;
     P.slot_bytes = c.slot; P.nib_bytes = c.nib;
@@ -225,17 +265,23 @@ int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t l
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);
     if (c.mt == 1) {
-        switch (w->bits) {
+        switch (g.bits) {
             case 2: return launch_gemv<2, 1>(P, c, st);
             case 3: return launch_gemv<3, 1>(P, c, st);
             default: return launch_gemv<4, 1>(P, c, st);
         }
     }
-    switch (w->bits) {
+    switch (g.bits) {
         case 2: return launch_gemv<2, 2>(P, c, st);
         case 3: return launch_gemv<3, 2>(P, c, st);
         default: return launch_gemv<4, 2>(P, c, st);
     }
+}
+
+int gemv_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
+              void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, bool fp32_out = false) {
+    GemvOut o = {y, ldy, bias};
+    return gemv_launch(1, &w, &o, x, ldx, M, fp32_out, scratch, scratch_bytes, clear_counters, stream);
 }
 
 }  // namespace
@@ -275,7 +321,7 @@ size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M) {
     if (check_mat(w) != COBALT_OK || M <= 0 || M > MAX_GEMV_M) return 0;
     if (device_info(&sms) != COBALT_OK) return 0;
     GemvCfg c;
-    if (gemv_config(w, M, sms, &c) != COBALT_OK) return 0;
+    if (gemv_config(geom_of(w), M, sms, &c) != COBALT_OK) return 0;
     return c.total;
 }
 
@@ -300,7 +346,7 @@ int cobalt_gemv_static(const CobaltMat* w, const void* x, int64_t ldx, void* y, 
     rc = device_info(&sms);
     if (rc) return rc;
     GemvCfg c;
-    rc = gemv_config(w, M, sms, &c);
+    rc = gemv_config(geom_of(w), M, sms, &c);
     if (rc) return rc;
     if (c.total > (size_t)COBALT_STATIC_SCRATCH_BYTES) return COBALT_ETOOBIG;
     int dev = 0;
@@ -312,6 +358,33 @@ int cobalt_gemv_static(const CobaltMat* w, const void* x, int64_t ldx, void* y, 
     }
     return gemv_impl(w, x, ldx, y, ldy, bias, M, g_static_scratch_ptr[dev], COBALT_STATIC_SCRATCH_BYTES,
                      /*clear_counters=*/true, stream);
+}
+
+size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, int M) {
+    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || M <= 0 || M > MAX_GEMV_M) return 0;
+    GemvGeom g = {};
+    for (int i = 0; i < n_mats; ++i) {
+        if (check_mat(w[i]) != COBALT_OK) return 0;
+        if (i == 0) g = geom_of(w[0]);
+        else {
+            g.RB += w[i]->n_row_blocks;
+            if (w[i]->max_tile_bytes > g.max_tile_bytes) g.max_tile_bytes = w[i]->max_tile_bytes;
+            if (w[i]->max_tile_nnz > g.max_tile_nnz) g.max_tile_nnz = w[i]->max_tile_nnz;
+        }
+    }
+    int sms = 0;
+    if (device_info(&sms) != COBALT_OK) return 0;
+    GemvCfg c;
+    if (gemv_config(g, M, sms, &c) != COBALT_OK) return 0;
+    return c.total;
+}
+
+int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int64_t ldx, void* const* y, const int64_t* ldy,
+                      const void* const* bias, int M, void* scratch, size_t scratch_bytes, void* stream) {
+    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !y || !ldy) return COBALT_EINVAL;
+    GemvOut o[GEMV_MAX_MATS];
+    for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
+    return gemv_launch(n_mats, w, o, x, ldx, M, false, scratch, scratch_bytes, false, stream);
 }
 
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,

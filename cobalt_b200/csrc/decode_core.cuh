@@ -126,6 +126,9 @@ CB_HD float bf16_bits_to_float(uint32_t b) { return u2f((b & 0xFFFFu) << 16); }
 __device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
     uint32_t d; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
 }
+__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
+    uint32_t d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+}
 __device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
     uint32_t d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
 }
@@ -144,6 +147,11 @@ inline uint32_t bf16_round_double(double v) {            // one RNE rounding of 
 inline uint32_t bf2_sub(uint32_t a, uint32_t b) {
     uint32_t lo = bf16_round_double((double)bf16_bits_to_float(a) - (double)bf16_bits_to_float(b));
     uint32_t hi = bf16_round_double((double)bf16_bits_to_float(a >> 16) - (double)bf16_bits_to_float(b >> 16));
+    return lo | (hi << 16);
+}
+inline uint32_t bf2_add(uint32_t a, uint32_t b) {
+    uint32_t lo = bf16_round_double((double)bf16_bits_to_float(a) + (double)bf16_bits_to_float(b));
+    uint32_t hi = bf16_round_double((double)bf16_bits_to_float(a >> 16) + (double)bf16_bits_to_float(b >> 16));
     return lo | (hi << 16);
 }
 inline uint32_t bf2_mul(uint32_t a, uint32_t b) {
@@ -206,7 +214,7 @@ constexpr LutTable make_expand_lut() {
 struct SegParams {
     float s, z;            // fp32 values of the stored fp16 scale / zero
     uint32_t zb24;         // zero point << 24 (fast path)
-    uint32_t zb2;          // bf16x2 {128+z, 128+z}
+    uint32_t zb2;          // bf16x2 {-(128+z), -(128+z)}: added, so that no per-use negation is needed
     uint32_t shi2, slo2;   // bf16x2 {s_hi, s_hi}, {s_lo, s_lo}
     bool fast;
 };
@@ -222,7 +230,7 @@ CB_HD SegParams make_seg_params(uint32_t sz_bits, int bits, bool has_col_scale) 
     p.fast = z_ok && s_ok && !has_col_scale;
     uint32_t zq = p.fast ? (uint32_t)zi : 0u;
     p.zb24 = zq << 24;
-    uint32_t zb = 0x4300u | zq;
+    uint32_t zb = 0xC300u | zq;                            // sign bit set
     p.zb2 = zb | (zb << 16);
     uint32_t su = f2u(p.s);
     uint32_t hi = su & 0xFFFF0000u;
@@ -235,7 +243,7 @@ CB_HD SegParams make_seg_params(uint32_t sz_bits, int bits, bool has_col_scale) 
 
 // bf16x2 {128+c0, 128+c1} -> bf16x2 weights
 CB_HD uint32_t dq_pair(uint32_t e, const SegParams& p) {
-    uint32_t d = bf2_sub(e, p.zb2);
+    uint32_t d = bf2_add(e, p.zb2);
     uint32_t t = bf2_mul(d, p.slo2);
     return bf2_fma(d, p.shi2, t);
 }

@@ -29,12 +29,26 @@ constexpr int GEMV_MAX_STAGES = 4;
 constexpr uint32_t GEMV_LUT_BYTES = LUT_ENTRIES * LUT_COPIES * 8;      // 32 KB
 constexpr uint32_t GEMV_BAR_BYTES = GEMV_WARPS * GEMV_MAX_STAGES * 8;  // 512 B
 
-struct GemvParams {
-    MatView W;
-    const uint16_t* x; int64_t ldx;
-    uint16_t* y; int64_t ldy;
-    float* y32;                          // when set, raw fp32 sums go here instead (no bias, no rounding)
+constexpr int GEMV_MAX_MATS = 4;
+
+// one matrix of a (possibly fused) launch; all matrices of a launch share x, N and the bit width
+struct GemvMat {
+    const uint8_t* tiles;
+    const uint32_t* tile_off;
+    uint16_t* y;                         // bf16 output [M, K] ...
+    float* y32;                          // ... or, when set, raw fp32 sums (no bias, no rounding)
     const uint16_t* bias;
+    int64_t ldy;
+    int K;
+    int rb_start;                        // first row block of this matrix in the launch's row-block space
+};
+
+struct GemvParams {
+    GemvMat mat[GEMV_MAX_MATS];
+    int n_mats;
+    int N, G, CT, RB;                    // shared geometry; RB = row blocks of all matrices together
+    const uint16_t* col_scale;           // single-matrix launches only
+    const uint16_t* x; int64_t ldx;
     int M;
     int stages;
     uint32_t slot_bytes, nib_bytes;
@@ -86,10 +100,16 @@ __device__ __forceinline__ uint32_t tile_owner(uint32_t tau, uint32_t T, uint32_
 template <int BITS, int MT>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    const MatView& W = P.W;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t full = 0xFFFFFFFFu;
+    auto mat_of = [&](int rbg) {                                       // matrix that owns row block rbg of the launch
+        int m = 0;
+#pragma unroll
+        for (int k = 1; k < GEMV_MAX_MATS; ++k)
+            if (k < P.n_mats && rbg >= P.mat[k].rb_start) m = k;
+        return m;
+    };
 
     // ---- block set-up: barriers first, so that the first tiles are in flight while the
     //      expansion table replicas are being written
@@ -101,7 +121,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     fence_proxy_async();
     __syncthreads();
 
-    const uint32_t T = (uint32_t)W.RB * (uint32_t)W.CT, Wt = P.total_warps;
+    const uint32_t T = (uint32_t)P.RB * (uint32_t)P.CT, Wt = P.total_warps;
     const uint32_t gw = blockIdx.x * GEMV_WARPS + warp;
     const uint32_t t0 = range_start(gw, T, Wt), t1 = range_start(gw + 1, T, Wt);
     const int n = (int)(t1 - t0);
@@ -112,24 +132,34 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     const uint32_t lut_lane = smem_u32(smem) + (uint32_t)(lane & (LUT_COPIES - 1)) * 8u;
     const LutEntry* lut_lane_ptr = lut_s + (lane & (LUT_COPIES - 1));
 
-    // offsets of the first 32 tile boundaries of the range, one per lane
-    const uint32_t my_off = (lane <= n) ? W.tile_off[t0 + lane] : 0u;
+    // address and size of tile t0 + i, looked up by lane i for the first 32 tiles of the range
+    auto tile_src = [&](uint32_t tau, const uint8_t*& src, uint32_t& bytes) {
+        const int rbg = (int)(tau / (uint32_t)P.CT);
+        const GemvMat& mt = P.mat[mat_of(rbg)];
+        const uint32_t local = tau - (uint32_t)mt.rb_start * (uint32_t)P.CT;
+        const uint32_t o0 = mt.tile_off[local], o1 = mt.tile_off[local + 1];
+        src = mt.tiles + (size_t)o0 * 16;
+        bytes = (o1 - o0) * 16u;
+    };
+    const uint8_t* my_src = nullptr;
+    uint32_t my_bytes = 0;
+    if (lane < n) tile_src(t0 + lane, my_src, my_bytes);
 
     auto issue = [&](int i, int slot_idx) {                            // all lanes call; lane 0 acts
-        uint32_t o0, o1;
-        if (i < 31) {
-            o0 = __shfl_sync(full, my_off, i);
-            o1 = __shfl_sync(full, my_off, i + 1);
+        const uint8_t* src;
+        uint32_t bytes;
+        if (i < 32) {
+            const unsigned long long a = __shfl_sync(full, (unsigned long long)my_src, i);
+            src = (const uint8_t*)a;
+            bytes = __shfl_sync(full, my_bytes, i);
         } else {
-            o0 = W.tile_off[t0 + i];
-            o1 = W.tile_off[t0 + i + 1];
+            tile_src(t0 + i, src, bytes);
         }
         if (lane == 0) {
-            const uint32_t bytes = (o1 - o0) * 16u;
             const uint32_t bar = bar0 + 8 * slot_idx;
             fence_proxy_async();
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_g2s(ring + slot_idx * P.slot_bytes, W.tiles + (size_t)o0 * 16, bytes, bar);
+            bulk_g2s(ring + slot_idx * P.slot_bytes, src, bytes, bar);
         }
     };
 
@@ -138,6 +168,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 
     for (int i = threadIdx.x; i < LUT_ENTRIES * LUT_COPIES; i += GEMV_THREADS) lut_s[i] = g_lut.e[i / LUT_COPIES];
     __syncthreads();
+    // Programmatic dependent launch: everything above touched only the weights and this CTA's shared
+    // memory.  From here on the activations and the scratch of the previous kernel in the stream are used.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (n == 0) return;
 
     float acc[MT][4];
@@ -146,8 +180,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 
     // ---- finish one row block: direct store, or deterministic reduction by the last arriver
     auto flush = [&](int rb) {
-        const uint32_t first = (uint32_t)rb * W.CT, last = first + W.CT - 1;
-        const int row0 = rb * TILE_ROWS + g, row1 = row0 + 8;
+        const uint32_t first = (uint32_t)rb * P.CT, last = first + P.CT - 1;
+        const GemvMat& mt = P.mat[mat_of(rb)];
+        const int row0 = (rb - mt.rb_start) * TILE_ROWS + g, row1 = row0 + 8;
         const bool whole = (t0 <= first) && (t1 > last);
         if (!whole) {
             const uint32_t myslot = gw * 2u + (t0 >= first ? 0u : 1u);
@@ -158,7 +193,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                 for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
             __threadfence();
             __syncwarp();
-            const uint32_t nparts = (T < Wt) ? (uint32_t)W.CT : tile_owner(last, T, Wt) - tile_owner(first, T, Wt) + 1u;
+            const uint32_t nparts = (T < Wt) ? (uint32_t)P.CT : tile_owner(last, T, Wt) - tile_owner(first, T, Wt) + 1u;
             uint32_t old = 0;
             if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
             old = __shfl_sync(full, old, 0);
@@ -183,24 +218,24 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
-            if (P.y32) {
-                if (row0 < W.K) {
-                    if (tok0 < P.M) P.y32[(size_t)tok0 * P.ldy + row0] = acc[b][0];
-                    if (tok1 < P.M) P.y32[(size_t)tok1 * P.ldy + row0] = acc[b][1];
+            if (mt.y32) {
+                if (row0 < mt.K) {
+                    if (tok0 < P.M) mt.y32[(size_t)tok0 * mt.ldy + row0] = acc[b][0];
+                    if (tok1 < P.M) mt.y32[(size_t)tok1 * mt.ldy + row0] = acc[b][1];
                 }
-                if (row1 < W.K) {
-                    if (tok0 < P.M) P.y32[(size_t)tok0 * P.ldy + row1] = acc[b][2];
-                    if (tok1 < P.M) P.y32[(size_t)tok1 * P.ldy + row1] = acc[b][3];
+                if (row1 < mt.K) {
+                    if (tok0 < P.M) mt.y32[(size_t)tok0 * mt.ldy + row1] = acc[b][2];
+                    if (tok1 < P.M) mt.y32[(size_t)tok1 * mt.ldy + row1] = acc[b][3];
                 }
                 continue;
             }
-            if (row0 < W.K) {
-                if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row0] = finish_output(acc[b][0], P.bias, row0);
-                if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row0] = finish_output(acc[b][1], P.bias, row0);
+            if (row0 < mt.K) {
+                if (tok0 < P.M) mt.y[(size_t)tok0 * mt.ldy + row0] = finish_output(acc[b][0], mt.bias, row0);
+                if (tok1 < P.M) mt.y[(size_t)tok1 * mt.ldy + row0] = finish_output(acc[b][1], mt.bias, row0);
             }
-            if (row1 < W.K) {
-                if (tok0 < P.M) P.y[(size_t)tok0 * P.ldy + row1] = finish_output(acc[b][2], P.bias, row1);
-                if (tok1 < P.M) P.y[(size_t)tok1 * P.ldy + row1] = finish_output(acc[b][3], P.bias, row1);
+            if (row1 < mt.K) {
+                if (tok0 < P.M) mt.y[(size_t)tok0 * mt.ldy + row1] = finish_output(acc[b][2], mt.bias, row1);
+                if (tok1 < P.M) mt.y[(size_t)tok1 * mt.ldy + row1] = finish_output(acc[b][3], mt.bias, row1);
             }
         }
     };
@@ -208,22 +243,23 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     bool healthy = true;
     int st = -1;                                                      // ring slot and phase parity of tile i
     uint32_t par = 0;
-    int cur_rb = (int)(t0 / (uint32_t)W.CT);
-    int rb = cur_rb, ct = (int)(t0 - (uint32_t)cur_rb * W.CT) - 1;      // advanced at the top of every iteration
+    int cur_rb = (int)(t0 / (uint32_t)P.CT);
+    int rb = cur_rb, ct = (int)(t0 - (uint32_t)cur_rb * P.CT) - 1;      // advanced at the top of every iteration
     for (int i = 0; i < issued; ++i) {
         if (++st == P.stages) { st = 0; par ^= 1u; }
         const bool ok = mbar_wait_bounded(bar0 + 8 * st, par, P.status, DEV_TIMEOUT_TILE);
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
-        if (++ct == W.CT) { ct = 0; ++rb; }
+        if (++ct == P.CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {
             if (!(P.debug & 2u)) flush(cur_rb);
 #pragma unroll
             for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
             cur_rb = rb;
         }
-        const int w = tile_width(W, ct);
+        int w = P.G - TILE_GROUPS * ct;
+        if (w > TILE_GROUPS) w = TILE_GROUPS;
         const bool active = t < w;
         const uint32_t slot = ring + st * P.slot_bytes;
         const int segA = g * w + t, segB = (g + 8) * w + t;
@@ -267,8 +303,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             cbase = nib;
         }
 
-        const SegParams pA = make_seg_params(szA, BITS, W.col_scale != nullptr);
-        const SegParams pB = make_seg_params(szB, BITS, W.col_scale != nullptr);
+        const SegParams pA = make_seg_params(szA, BITS, P.col_scale != nullptr);
+        const SegParams pB = make_seg_params(szB, BITS, P.col_scale != nullptr);
         const bool all_fast = __all_sync(full, pA.fast && pB.fast);
         const int col0 = (ct * TILE_GROUPS + t) * GROUP;               // first column of this lane's group
         // Tokens beyond M read the last real token (their MMA columns are never stored); lanes beyond a
@@ -321,9 +357,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                 uint32_t ea[16], eb[16];
                 float cs[32];
                 const float* csp = nullptr;
-                if (W.col_scale != nullptr && active) {
+                if (P.col_scale != nullptr && active) {
 #pragma unroll
-                    for (int q = 0; q < 32; ++q) cs[q] = half_bits_to_float(W.col_scale[col0 + 32 * j + q]);
+                    for (int q = 0; q < 32; ++q) cs[q] = half_bits_to_float(P.col_scale[col0 + 32 * j + q]);
                     csp = cs;
                 }
                 decode32<LUT_COPIES>(mAj, a0, a1, a2, a3, pA, lut_lane_ptr, csp, ea);

@@ -19,7 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from .compress import SparseQuantConfig, compress_weight
-from .linear import CobaltSparseLinear
+from .linear import CobaltSparseLinear, FusedProjections
 
 PROJ = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
         "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
@@ -82,6 +82,9 @@ class CobaltDecoder:
         self.kv_pos = torch.arange(max_ctx, device=device)
         self.tok = torch.zeros(1, dtype=torch.long, device=device)        # next token to feed
         self.pos = torch.zeros(1, dtype=torch.long, device=device)        # its position
+        self.qkv = [FusedProjections([linears[(i, "self_attn.q_proj")], linears[(i, "self_attn.k_proj")],
+                                      linears[(i, "self_attn.v_proj")]]) for i in range(L)]
+        self.gate_up = [FusedProjections([linears[(i, "mlp.gate_proj")], linears[(i, "mlp.up_proj")]]) for i in range(L)]
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._logits = None
 
@@ -102,9 +105,10 @@ class CobaltDecoder:
         for i in range(cfg["num_hidden_layers"]):
             p = f"model.layers.{i}."
             x = _rms_norm(h, P[p + "input_layernorm.weight"], eps)
-            q = self.lin[(i, "self_attn.q_proj")](x).view(1, T, nh, D).transpose(1, 2)
-            k = self.lin[(i, "self_attn.k_proj")](x).view(1, T, nkv, D).transpose(1, 2)
-            v = self.lin[(i, "self_attn.v_proj")](x).view(1, T, nkv, D).transpose(1, 2)
+            q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
+            q = q.view(1, T, nh, D).transpose(1, 2)
+            k = k.view(1, T, nkv, D).transpose(1, 2)
+            v = v.view(1, T, nkv, D).transpose(1, 2)
             q = (q * cos[None, None]) + (_rotate_half(q) * sin[None, None])
             k = (k * cos[None, None]) + (_rotate_half(k) * sin[None, None])
             self.k_cache[i].index_copy_(1, positions, k[0])
@@ -120,8 +124,7 @@ class CobaltDecoder:
             ctx = torch.matmul(att, Vr).transpose(1, 2).reshape(1, T, nh * D)
             h = h + self.lin[(i, "self_attn.o_proj")](ctx)
             x = _rms_norm(h, P[p + "post_attention_layernorm.weight"], eps)
-            g = self.lin[(i, "mlp.gate_proj")](x)
-            u = self.lin[(i, "mlp.up_proj")](x)
+            g, u = self.gate_up[i](x)
             h = h + self.lin[(i, "mlp.down_proj")](F.silu(g) * u)
         h = _rms_norm(h, P["model.norm.weight"], eps)
         return F.linear(h, P["lm_head.weight"])                                        # [1, T, V]

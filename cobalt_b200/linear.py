@@ -22,6 +22,7 @@ from .compress import SparseQuantConfig, compress_weight
 from .format import GROUP, TileImage, bytes_to_keep, pack_tiles
 
 GEMV_MAX_TOKENS = 16
+FUSED_MAX = 4
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -252,3 +253,54 @@ class CobaltSparseLinear(nn.Module):
         dens = m["nnz"] / float(m["K"] * m["N"])
         return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.bits}, "
                 f"group_size={GROUP}, density={dens:.3f}, bias={self.bias is not None}")
+
+
+class FusedProjections:
+    """Several ``CobaltSparseLinear`` that read the same activations (q|k|v, gate|up), evaluated with one
+    GEMV launch for up to 16 tokens (``cobalt_gemv_fused``) and one call each above that.  The reference
+    reaches the same goal by concatenating the matrices row-wise at pack time (docs/FORMAT.md:126-151)."""
+
+    def __init__(self, mods):
+        mods = list(mods)
+        if not 1 <= len(mods) <= FUSED_MAX:
+            raise ValueError(f"between 1 and {FUSED_MAX} projections can be fused")
+        n0 = mods[0].in_features
+        if any(m.in_features != n0 or m.bits != mods[0].bits or m.scale2 is not None or m.bias is not None for m in mods):
+            raise ValueError("fused projections need equal in_features and bit width, no column scale and no bias")
+        self.mods = mods
+        self._scratch = None
+        self._arrays = None
+
+    def _prepare(self, M, device):
+        lib = _lib.load()
+        n = len(self.mods)
+        descs = (ctypes.POINTER(_lib.CobaltMat) * n)(*[ctypes.pointer(m._descriptor()) for m in self.mods])
+        need = lib.cobalt_gemv_fused_scratch_bytes(n, descs, M)
+        if need == 0:
+            raise _lib.CobaltError("cobalt_gemv_fused_scratch_bytes", -1, "could not size the scratch buffer")
+        if self._scratch is None or self._scratch.numel() < need + 256 or self._scratch.device != device:
+            self._scratch = torch.zeros(need + 256, dtype=torch.uint8, device=device)
+        return descs
+
+    def __call__(self, x: torch.Tensor):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.mods[0].in_features)
+        M = x2.shape[0]
+        if M > GEMV_MAX_TOKENS or M == 0:
+            return [m(x) for m in self.mods]
+        if not x2.is_cuda or x2.dtype != torch.bfloat16:
+            raise TypeError("FusedProjections needs a bf16 CUDA tensor")
+        if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        lib = _lib.load()
+        n = len(self.mods)
+        descs = self._prepare(M, x.device)
+        ys = [torch.empty(M, m.out_features, dtype=torch.bfloat16, device=x.device) for m in self.mods]
+        yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+        ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in ys])
+        sp = (self._scratch.data_ptr() + 255) // 256 * 256
+        rc = lib.cobalt_gemv_fused(n, descs, x2.data_ptr(), x2.stride(0), yp, ld, None, M, sp,
+                                   self._scratch.numel() - (sp - self._scratch.data_ptr()),
+                                   torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check("cobalt_gemv_fused", rc)
+        return [y.reshape(*lead, m.out_features) for y, m in zip(ys, self.mods)]

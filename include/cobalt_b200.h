@@ -79,6 +79,17 @@ int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t
                 const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
 size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M);
 
+/* Up to 4 matrices that read the same activations (q|k|v, gate|up) in ONE launch: the tiles of all
+ * matrices form one work list, so small projections no longer pay a launch each.  All matrices must
+ * have the same in_features and bit width and no column scale.  Results are bit-identical to
+ * separate cobalt_gemv() calls.  y[i], ldy[i], bias[i] belong to matrix i (bias may be NULL).
+ * Replaces the row-concatenated qkv / gate-up matrices of the reference's packer
+ * (docs/FORMAT.md:126-151, src/cobaltkernel/pack_cobalt.py:452-471, 647-660). */
+int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int64_t ldx, void* const* y,
+                      const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
+                      void* stream);
+size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, int M);
+
 /* cobalt_gemv() for callers that must not allocate device memory.
  *
  * Who needs it: code that runs where cudaMalloc is off limits -- a plug-in inside a serving

@@ -304,3 +304,23 @@ def test_patch_model_swaps_linears():
             assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
             x = O.seeded_activation(2, 256, 5)
             check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+
+
+def test_fused_projections_equal_separate_calls():
+    """q|k|v-style fused launch: bit-identical to one cobalt_gemv call per matrix."""
+    from cobalt_b200 import FusedProjections
+    mods = []
+    for i, K in enumerate((512, 128, 128)):
+        raw = O.synth_raw(K, 1536, 0.5, 4, seed=70 + i)
+        mods.append(to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4))
+    fused = FusedProjections(mods)
+    for M in (1, 5, 16):
+        x = O.seeded_activation(M, 1536, 80 + M).cuda()
+        outs = fused(x)
+        for m, y in zip(mods, outs):
+            assert torch.equal(y, m(x))
+    outs = fused(O.seeded_activation(40, 1536, 99).cuda())          # above 16 tokens: one GEMM each
+    assert [o.shape[-1] for o in outs] == [512, 128, 128]
+    with pytest.raises(ValueError):
+        raw = O.synth_raw(64, 1024, 0.5, 4, seed=1)
+        FusedProjections([mods[0], to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
