@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("COBALT_B200_LIB") or os.path.join(HERE, "libcobalt_b200.so")   # override: experiments only
@@ -54,6 +54,10 @@ EXPORTS = {
     "cobalt_unpack": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p]),
     "cobalt_linear_host": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
+    "cobalt_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "cobalt_rope_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_int, c_void_p]),
+    "cobalt_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "cobalt_device_status": (c_int, [c_void_p, c_void_p, POINTER(c_uint32)]),
     "cobalt_set_tuning": (c_int, [c_int, c_int]),
 }

@@ -8,6 +8,7 @@
 #include "walk_kernels.cuh"
 #include "gemv_kernel.cuh"
 #include "gemm_kernel.cuh"
+#include "glue_kernels.cuh"
 
 using namespace cb;
 
@@ -505,6 +506,41 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
     if (cudaMemcpyAsync(y_host, dev_y, (size_t)M * w->K * 2, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
     if (cudaStreamSynchronize(st) != cudaSuccess) return COBALT_ELAUNCH;
     return COBALT_OK;
+}
+
+int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,
+                       void* stream) {
+    if (!h || !w || !y || T <= 0 || H <= 0) return COBALT_EINVAL;
+    int sms = 0;
+    int rc = device_info(&sms);
+    if (rc) return rc;
+    add_rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)h, (const uint16_t*)delta, (const uint16_t*)w,
+                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positions, const float* inv_freq, void* k_cache,
+                   void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, void* stream) {
+    if (!q || !k || !v || !positions || !inv_freq || !k_cache || !v_cache) return COBALT_EINVAL;
+    if (T <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || max_ctx <= 0) return COBALT_EINVAL;
+    int sms = 0;
+    int rc = device_info(&sms);
+    if (rc) return rc;
+    const long long n = (long long)T * (n_heads + 2 * n_kv_heads) * (head_dim / 2);
+    rope_kv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, (const long long*)positions, inv_freq, (uint16_t*)k_cache,
+        (uint16_t*)v_cache, T, n_heads, n_kv_heads, head_dim, max_ctx);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
+int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, void* stream) {
+    if (!gate || !up || !out || n <= 0) return COBALT_EINVAL;
+    int sms = 0;
+    int rc = device_info(&sms);
+    if (rc) return rc;
+    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint16_t*)gate, (const uint16_t*)up,
+                                                                                 (uint16_t*)out, (long long)n);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out) {

@@ -1,9 +1,9 @@
 """Minimal Mistral/Llama-shaped decoder that calls the compressed linears.
 
-This is the caller side of the hot path (the seven projections of every block), kept in
-plain PyTorch: RMSNorm, RoPE, grouped-query attention over a preallocated KV cache, SwiGLU,
-residual adds, a dense ``lm_head`` (the reference leaves ``lm_head`` uncompressed:
-sinq/patch_model.py:49).  The dtype policy follows the reference's executable spec
+This is the caller side of the hot path (the seven projections of every block): residual add +
+RMSNorm, RoPE + KV-cache append and SwiGLU are small fused CUDA kernels of the library;
+grouped-query attention over the preallocated KV cache and the dense ``lm_head`` (the reference
+leaves ``lm_head`` uncompressed: sinq/patch_model.py:49) are PyTorch matmuls.  The dtype policy follows the reference's executable spec
 src/cobaltkernel/ref_llama.py:10-16, 82-143: fp32 normalise -> bf16 -> times w; bf16 RoPE
 tables; bf16 score/context matmuls with an fp32 softmax cast back to bf16; bf16 residuals.
 
@@ -19,6 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from .compress import SparseQuantConfig, compress_weight
+from . import _lib
 from .linear import CobaltSparseLinear, FusedProjections
 
 PROJ = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
@@ -85,8 +86,36 @@ class CobaltDecoder:
         self.qkv = [FusedProjections([linears[(i, "self_attn.q_proj")], linears[(i, "self_attn.k_proj")],
                                       linears[(i, "self_attn.v_proj")]]) for i in range(L)]
         self.gate_up = [FusedProjections([linears[(i, "mlp.gate_proj")], linears[(i, "mlp.up_proj")]]) for i in range(L)]
+        self._lib = _lib.load()
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._logits = None
+
+    # ------------------------------------------------------------------ fused element-wise steps (C ABI)
+    def _add_rmsnorm(self, h, delta, w):
+        """(h + delta, rmsnorm(h + delta) * w); ``delta`` may be None."""
+        T, H = h.shape
+        y = torch.empty_like(h)
+        h_out = torch.empty_like(h) if delta is not None else h
+        rc = self._lib.cobalt_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), w.data_ptr(),
+                                          h_out.data_ptr() if delta is not None else None, y.data_ptr(), T, H,
+                                          float(self.cfg["rms_norm_eps"]), torch.cuda.current_stream(self.dev).cuda_stream)
+        _lib.check("cobalt_add_rmsnorm", rc)
+        return h_out, y
+
+    def _rope_kv(self, q, k, v, positions, layer):
+        cfg = self.cfg
+        rc = self._lib.cobalt_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(), self.inv_freq.data_ptr(),
+                                      self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(), q.shape[0],
+                                      cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], self.max_ctx,
+                                      torch.cuda.current_stream(self.dev).cuda_stream)
+        _lib.check("cobalt_rope_kv", rc)
+
+    def _swiglu(self, g, u):
+        out = torch.empty_like(g)
+        rc = self._lib.cobalt_swiglu(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(),
+                                     torch.cuda.current_stream(self.dev).cuda_stream)
+        _lib.check("cobalt_swiglu", rc)
+        return out
 
     # ------------------------------------------------------------------ one forward over T tokens
     def _forward(self, ids: torch.Tensor, positions: torch.Tensor, attend_len: int) -> torch.Tensor:
@@ -94,40 +123,32 @@ class CobaltDecoder:
         looks at cache slots [0, attend_len) under the causal mask ``slot <= position``."""
         cfg, P = self.cfg, self.P
         nh, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-        eps, T = cfg["rms_norm_eps"], ids.shape[0]
-        h = P["model.embed_tokens.weight"].index_select(0, ids).unsqueeze(0)          # [1, T, H]
-        freqs = positions.float()[:, None] * self.inv_freq[None, :]
-        emb = torch.cat((freqs, freqs), dim=-1)
-        cos, sin = emb.cos().to(h.dtype), emb.sin().to(h.dtype)
-        allowed = self.kv_pos[None, :attend_len] <= positions[:, None]                 # [T, S]
+        T, rep, S = ids.shape[0], nh // nkv, attend_len
+        h = P["model.embed_tokens.weight"].index_select(0, ids)                        # [T, H]
+        allowed = self.kv_pos[None, :S] <= positions[:, None]                          # [T, S]
         if cfg.get("sliding_window"):
-            allowed = allowed & (self.kv_pos[None, :attend_len] > positions[:, None] - cfg["sliding_window"])
+            allowed = allowed & (self.kv_pos[None, :S] > positions[:, None] - cfg["sliding_window"])
+        blocked = ~allowed[None, :, None, :]                                           # [1, T, 1, S]
+        scale = float(D) ** -0.5
+        delta = None
         for i in range(cfg["num_hidden_layers"]):
             p = f"model.layers.{i}."
-            x = _rms_norm(h, P[p + "input_layernorm.weight"], eps)
+            h, x = self._add_rmsnorm(h, delta, P[p + "input_layernorm.weight"])
             q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
-            q = q.view(1, T, nh, D).transpose(1, 2)
-            k = k.view(1, T, nkv, D).transpose(1, 2)
-            v = v.view(1, T, nkv, D).transpose(1, 2)
-            q = (q * cos[None, None]) + (_rotate_half(q) * sin[None, None])
-            k = (k * cos[None, None]) + (_rotate_half(k) * sin[None, None])
-            self.k_cache[i].index_copy_(1, positions, k[0])
-            self.v_cache[i].index_copy_(1, positions, v[0])
-            Kc = self.k_cache[i][:, :attend_len].unsqueeze(0)                          # [1, nkv, S, D]
-            Vc = self.v_cache[i][:, :attend_len].unsqueeze(0)
-            rep = nh // nkv
-            Kr = Kc[:, :, None].expand(1, nkv, rep, attend_len, D).reshape(1, nh, attend_len, D)
-            Vr = Vc[:, :, None].expand(1, nkv, rep, attend_len, D).reshape(1, nh, attend_len, D)
-            att = torch.matmul(q, Kr.transpose(2, 3)) * (float(D) ** -0.5)
-            att = att.masked_fill(~allowed[None, None], float("-inf"))
-            att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
-            ctx = torch.matmul(att, Vr).transpose(1, 2).reshape(1, T, nh * D)
-            h = h + self.lin[(i, "self_attn.o_proj")](ctx)
-            x = _rms_norm(h, P[p + "post_attention_layernorm.weight"], eps)
+            self._rope_kv(q, k, v, positions, i)                                       # q in place, k/v into the caches
+            Kc, Vc = self.k_cache[i][:, :S], self.v_cache[i][:, :S]                    # [nkv, S, D]
+            # grouped-query attention as one batched matmul per KV head (no expanded copies of K/V)
+            qg = q.view(T, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, T * rep, D)
+            att = torch.bmm(qg, Kc.transpose(1, 2)) * scale                            # bf16 scores, scaled in bf16
+            att = att.view(nkv, T, rep, S).masked_fill(blocked, float("-inf"))
+            att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype).view(nkv, T * rep, S)
+            ctx = torch.bmm(att, Vc).view(nkv, T, rep, D).permute(1, 0, 2, 3).reshape(T, nh * D)
+            o = self.lin[(i, "self_attn.o_proj")](ctx)
+            h, x = self._add_rmsnorm(h, o, P[p + "post_attention_layernorm.weight"])
             g, u = self.gate_up[i](x)
-            h = h + self.lin[(i, "mlp.down_proj")](F.silu(g) * u)
-        h = _rms_norm(h, P["model.norm.weight"], eps)
-        return F.linear(h, P["lm_head.weight"])                                        # [1, T, V]
+            delta = self.lin[(i, "mlp.down_proj")](self._swiglu(g, u))
+        h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"])
+        return F.linear(x, P["lm_head.weight"]).unsqueeze(0)                           # [1, T, V]
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
