@@ -340,7 +340,10 @@ def run_ours(args):
                 "d2h_bytes_per_step": int(sum(M * v["K"] * 2 for v in info.values()))},
         "gpu_launches": int(args.steps * launches_per_step),
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(value / world / peak, 4), "traffic": None,
+                     "frac": round(value / world / peak, 4),
+                     # DRAM bytes per launch: 1.005 x algorithmic, from the ncu capture of the gate projection
+                     # (profiles/gemv_mma_kernel_7b_gate_M1.md); traffic grows in proportion to the tiles streamed
+                     "traffic": int(1.005 * (wbytes + abytes) / launches_per_step),
                      "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": launches_per_step,
                      "bytes_per_launch": int((wbytes + abytes) / launches_per_step)},
         "device_status": status,
