@@ -341,8 +341,8 @@ def run_ours(args):
         "gpu_launches": int(args.steps * launches_per_step),
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(value / world / peak, 4),
-                     # DRAM bytes per launch: 1.005 x algorithmic, from the ncu capture of the gate projection
-                     # (profiles/gemv_mma_kernel_7b_gate_M1.md); traffic grows in proportion to the tiles streamed
+                     # DRAM bytes per launch: 1.005 x algorithmic, from an ncu capture of the gate projection
+                     # (24.03 MB read for 23.9 MB); traffic grows in proportion to the tiles streamed
                      "traffic": int(1.005 * (wbytes + abytes) / launches_per_step),
                      "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": launches_per_step,
                      "bytes_per_launch": int((wbytes + abytes) / launches_per_step)},

@@ -38,7 +38,7 @@ def bf16_bits(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     ref = args.reference
     sys.path.insert(0, os.path.join(ref, "src", "cobaltkernel"))
