@@ -64,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -145,6 +145,21 @@ def step_bytes(info, M):
     return w, act
 
 
+def _finish(dist):
+    """Leave a multi-rank run without tearing NCCL down: the process group may hold communicators that a
+    captured CUDA graph still references, and its destructor has been seen to wait forever.  All ranks meet at a
+    barrier (so nobody is killed mid-collective), flush their output and exit the process directly."""
+    if dist is None:
+        return
+    try:
+        dist.barrier()
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 # ----------------------------------------------------------------------------- our arm
 def run_ours(args):
     from cobalt_b200 import _lib
@@ -208,7 +223,8 @@ def run_ours(args):
             one_step(b, f)
         stream.synchronize()
         graph = None
-        if world == 1 and not args.profile:
+        if not args.profile and not args.no_graph:
+            # the all-reduces of the tensor-parallel run are captured with the kernels (NCCL supports capture)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for b, f in zip(blocks, fuseds):
@@ -264,10 +280,15 @@ def run_ours(args):
                 nbytes = info[name]["bytes"] + M * (info[name]["N"] + info[name]["K"]) * 2
                 per_shape[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
         # hold the load a little longer so that the clock sampler sees it
-        t_end = time.time() + (0.0 if (args.profile or world > 1) else 1.0)   # single GPU only: no collectives inside
-        while rank == 0 and time.time() < t_end:
-            run_steps(len(blocks))
-            stream.synchronize()
+        if not args.profile:
+            if world == 1:
+                t_end = time.time() + 1.0
+                while time.time() < t_end:
+                    run_steps(len(blocks))
+                    stream.synchronize()
+            else:                                           # same fixed count on every rank: the steps contain collectives
+                run_steps(max(2000, 10 * args.steps))
+                stream.synchronize()
         clocks = sampler.stop() if rank == 0 else None
         status = max(m.device_status() for b in blocks for m in b.values())
 
@@ -283,8 +304,7 @@ def run_ours(args):
         if rank == 0:
             print(json.dumps({"profile_run": True, "value": round(value, 2), "unit": "GB/s", "ms_per_step": round(ms_step, 5),
                               "shapes": [t[0] for t in SHAPES_7B], "copies": copies}), flush=True)
-        if dist is not None:
-            dist.destroy_process_group()
+        _finish(dist)
         return
     # ---- end to end through the host-buffer entry point (rank-local; aggregated like `value`)
     e2e_steps = max(3, min(args.steps, 20))
@@ -321,8 +341,7 @@ def run_ours(args):
     e2e_val = total_bytes / (e2e_ms * 1e-3) / 1e9
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        _finish(dist)
         return
     peak, peak_kind = measured_peaks()
     out = {
@@ -352,8 +371,7 @@ def run_ours(args):
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(info, M, budget_s=15.0)
     print(json.dumps(out), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    _finish(dist)
 
 
 # ----------------------------------------------------------------------------- CPU arm (reference path)
@@ -527,6 +545,7 @@ def main():
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--debug-flags", type=int, default=0, help="kernel experiment switches (results become invalid)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")

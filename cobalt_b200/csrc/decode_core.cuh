@@ -80,6 +80,16 @@ CB_HD int popc(uint32_t x) {
     int c = 0; while (x) { x &= x - 1; ++c; } return c;
 #endif
 }
+// (a & b) | c in one instruction
+CB_HD uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+#if CB_DEVICE_CODE
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+#else
+    return (a & b) | c;
+#endif
+}
 // low 32 bits of (hi:lo) >> (sh & 31)
 CB_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t sh) {
 #if CB_DEVICE_CODE
@@ -332,10 +342,10 @@ CB_HD void decode16_fast(uint32_t m16, uint32_t& w0, uint32_t& w1, uint32_t& w2,
         // high view: (w0 >> 4) with byte 3 replaced by the zero point unless all eight positions are kept
         const uint32_t hi = prmt(mulhi_u32(w0, K.k28), zreg, mulhi_u32(e.x, K.k16));
         const uint32_t d0 = prmt(w0, hi, e.x), d1 = prmt(w0, hi, e.y);
-        out[4 * i + 0] = dq_pair((d0 & 0x000F000Fu) | 0x43004300u, p);
-        out[4 * i + 1] = dq_pair((mulhi_u32(d0, K.k24) & 0x000F000Fu) | 0x43004300u, p);
-        out[4 * i + 2] = dq_pair((d1 & 0x000F000Fu) | 0x43004300u, p);
-        out[4 * i + 3] = dq_pair((mulhi_u32(d1, K.k24) & 0x000F000Fu) | 0x43004300u, p);
+        out[4 * i + 0] = dq_pair(and_or(d0, 0x000F000Fu, 0x43004300u), p);
+        out[4 * i + 1] = dq_pair(and_or(mulhi_u32(d0, K.k24), 0x000F000Fu, 0x43004300u), p);
+        out[4 * i + 2] = dq_pair(and_or(d1, 0x000F000Fu, 0x43004300u), p);
+        out[4 * i + 3] = dq_pair(and_or(mulhi_u32(d1, K.k24), 0x000F000Fu, 0x43004300u), p);
         const uint32_t amt = mulhi_u32(e.y, K.k16);
         w0 = funnel_rc(w0, w1, amt);
         w1 = funnel_rc(w1, w2, amt);
