@@ -324,3 +324,24 @@ def test_fused_projections_equal_separate_calls():
     with pytest.raises(ValueError):
         raw = O.synth_raw(64, 1024, 0.5, 4, seed=1)
         FusedProjections([mods[0], to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
+
+
+@pytest.mark.parametrize("name,K,N", [("q_shard", 512, 5376), ("kv_shard", 256, 5376), ("o_shard", 5376, 512),
+                                        ("gate_up_shard", 2688, 5376), ("down_shard", 5376, 2688)])
+def test_config5_gemma27b_shard_shapes(name, K, N):
+    """Gemma-3-27B projection shapes as one rank of an 8-way tensor-parallel split sees them (hidden 5376,
+    intermediate 21504, 32 q / 16 kv heads of 128): 3 bit, 60 % sparse.  in_features of 5376, 2688 and 512
+    exercise partial column tiles (2, 1 and 4 groups in the last tile).  Decode batch 1 and 8, prefill 2048."""
+    keep, q, sc, zr = _compress_on_gpu(K, N, 3, 0.6, 5000 + K % 101 + N % 103)
+    mod = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": 3})
+    Wb = O.dequantize(q.cpu(), sc.cpu(), zr.cpu(), keep.cpu()).to(torch.bfloat16)
+    assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
+    for M in (1, 8, 2048):
+        x = O.seeded_activation(M, N, 5100 + M)
+        check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+    # fp32 partial sums of a row-parallel shard: within fp32 accumulation noise of the exact product
+    x = O.seeded_activation(8, N, 5200)
+    part = mod(x.cuda(), out_fp32=True).cpu().double()
+    ex = exact_fp64(x, Wb)
+    assert float((part - ex).norm() / ex.norm()) <= 1e-5
+    assert mod.device_status() == 0
