@@ -175,8 +175,6 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     lib = _lib.load()
     M = args.tokens
-    if args.debug_flags:
-        lib.cobalt_set_tuning(3, args.debug_flags)
 
     global SHAPES_7B
     if args.shapes:
@@ -544,7 +542,6 @@ def main():
     ap.add_argument("--prefill-m", default="128,512,2048")
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
-    ap.add_argument("--debug-flags", type=int, default=0, help="kernel experiment switches (results become invalid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
     ap.add_argument("--profile", action="store_true",

@@ -23,7 +23,6 @@ bool g_dev_known[MAX_DEVICES];
 int g_tune_tiles_per_split = 0;     // 0 = heuristic
 int g_tune_gemv_stages = 0;
 int g_tune_gemm_stages = 0;
-int g_debug_flags = 0;
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -260,7 +259,6 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.stages = c.stages;
     P.slot_bytes = c.slot; P.nib_bytes = c.nib;
     P.total_warps = c.total_warps;
-    P.debug = (uint32_t)g_debug_flags;
     P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k16 = 1u << 16;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
@@ -304,15 +302,14 @@ const char* cobalt_strerror(int status) {
     }
 }
 
-// Tuning hook for benchmarks: key 0 = GEMV grid size, 1 = GEMV ring stages, 2 = GEMM split-K factor,
-// 3 = experiment switches; value 0 restores the heuristic.  Not part of the stable contract.
+// Tuning hook for benchmarks: key 0 = GEMV grid size, 1 = GEMV ring stages, 2 = GEMM split-K factor;
+// value 0 restores the heuristic.  Not part of the stable contract.
 int cobalt_set_tuning(int key, int value) {
     if (value < 0) return COBALT_EINVAL;
     switch (key) {
         case 0: g_tune_tiles_per_split = value; return COBALT_OK;
         case 1: g_tune_gemv_stages = value; return COBALT_OK;
         case 2: g_tune_gemm_stages = value; return COBALT_OK;
-        case 3: g_debug_flags = value; return COBALT_OK;
         default: return COBALT_EINVAL;
     }
 }

@@ -57,7 +57,6 @@ struct GemvParams {
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
     FastConsts K;
-    uint32_t debug;                      // experiments only: bit1 skip flush, bit2 skip MMA
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -121,6 +120,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     fence_proxy_async();
     __syncthreads();
 
+    const int M = P.M, CT = P.CT;
+    const FastConsts KC = P.K;
     const uint32_t T = (uint32_t)P.RB * (uint32_t)P.CT, Wt = P.total_warps;
     const uint32_t gw = blockIdx.x * GEMV_WARPS + warp;
     const uint32_t t0 = range_start(gw, T, Wt), t1 = range_start(gw + 1, T, Wt);
@@ -251,9 +252,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
-        if (++ct == P.CT) { ct = 0; ++rb; }
+        if (++ct == CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {
-            if (!(P.debug & 2u)) flush(cur_rb);
+            flush(cur_rb);
 #pragma unroll
             for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
             cur_rb = rb;
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             int tok = g + 8 * b;
-            if (tok > P.M - 1) tok = P.M - 1;
+            if (tok > M - 1) tok = M - 1;
             xrow[b] = P.x + (size_t)tok * P.ldx + (active ? col0 : 0);
         }
         auto lut = [lut_lane](uint32_t idx) {
@@ -342,9 +343,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                         xv[b][1] = ldg_nc_early(xp + 1);
                     }
                     uint32_t ea[8], eb[8];
-                    decode16_fast(h ? (mAj >> 16) : (mAj & 0xFFFFu), a0, a1, a2, a3, pA, P.K, lut, ea);
-                    decode16_fast(h ? (mBj >> 16) : (mBj & 0xFFFFu), b0, b1, b2, b3, pB, P.K, lut, eb);
-                    if (P.debug & 4u) { acc[0][0] += __uint_as_float(ea[0] ^ eb[3] ^ ea[7] ^ eb[5]); continue; }
+                    decode16_fast(h ? (mAj >> 16) : (mAj & 0xFFFFu), a0, a1, a2, a3, pA, KC, lut, ea);
+                    decode16_fast(h ? (mBj >> 16) : (mBj & 0xFFFFu), b0, b1, b2, b3, pB, KC, lut, eb);
 #pragma unroll
                     for (int b = 0; b < MT; ++b) {
                         mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);
@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         if (issued < n) { issue(issued, st); ++issued; }       // tile i + stages reuses the slot just drained
     }
     if (!healthy) return;
-    if (!(P.debug & 2u)) flush(cur_rb);
+    flush(cur_rb);
 }
 
 }  // namespace cb
