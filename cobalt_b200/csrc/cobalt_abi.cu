@@ -84,16 +84,22 @@ int gemv_config(const GemvGeom& g, int M, int num_sms, GemvCfg* c) {
     c->mt = M > 8 ? 2 : 1;
     c->slot = (uint32_t)round_up((size_t)g.max_tile_bytes + 32, 128);
     c->nib = g.bits == 4 ? 0u : (uint32_t)round_up((size_t)g.max_tile_nnz / 2 + 64, 128);
-    const size_t fixed = GEMV_LUT_BYTES + GEMV_BAR_BYTES + 64;
+    const size_t fixed = GEMV_LUT_BYTES + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES + gemv_red_bytes(c->mt) + 64;
     int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : GEMV_MAX_STAGES;
     if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
     while (stages > 1 && fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) --stages;
     if (fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) return COBALT_EINVAL;
     c->stages = stages;
     c->smem = fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib);
-    // persistent grid: one CTA per SM, fewer when there are not enough tiles to go round
+    // persistent grid: one CTA per SM.  When there is at most one tile per warp, the grid is chosen so that
+    // every CTA holds whole row blocks (their parts then meet in shared memory instead of global scratch).
     const long tiles = (long)RB * CT;
-    long grid = g_tune_tiles_per_split > 0 ? g_tune_tiles_per_split : num_sms;     // tuning key 0 overrides the grid size
+    long grid = num_sms;
+    if (tiles <= (long)num_sms * GEMV_WARPS && CT <= GEMV_WARPS) {
+        for (long r = 8 / CT > 0 ? 8 / CT : 1; r * CT <= GEMV_WARPS; ++r)      // r row blocks per CTA; start with half the warps busy
+            if (RB % r == 0 && RB / r <= num_sms) { grid = RB / r; break; }
+    }
+    if (g_tune_tiles_per_split > 0) grid = g_tune_tiles_per_split;                  // tuning key 0 overrides the grid size
     if (grid > tiles) grid = tiles;
     if (grid < 1) grid = 1;
     c->grid = (int)grid;
@@ -259,7 +265,6 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.stages = c.stages;
     P.slot_bytes = c.slot; P.nib_bytes = c.nib;
     P.total_warps = c.total_warps;
-    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k16 = 1u << 16;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);
@@ -442,7 +447,6 @@ static int gemm_impl(const CobaltMat* w, const void* x, int64_t ldx, void* y, in
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = c.splits > 1 ? (float*)((uint8_t*)scratch + c.partials_off) : nullptr;
-    P.K.k28 = 1u << 28; P.K.k24 = 1u << 24; P.K.k16 = 1u << 16;
     cudaStream_t st = (cudaStream_t)stream;
     switch (w->bits) {
         case 2: return launch_gemm<2>(P, xmap, c, st);

@@ -312,27 +312,18 @@ CB_HD void decode32(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t 
 }
 
 // ----------------------------------------------------------------------------- 32 positions, fast segments only
-// Same contract as decode32() for segments whose SegParams::fast is set, arranged for the
-// instruction mix of an SM: the ALU pipe (prmt / lop3 / shf) is the scarce one, so right shifts
-// by constants and the "all eight kept" special case are computed with multiplies on the FMA
-// pipe.  `k28`, `k24`, `k16` must hold 1<<28, 1<<24, 1<<16; they are passed in registers so
-// that the multiplies are not turned back into shifts.  `lut(idx)` returns the table entry of
-// mask byte idx.
-CB_HD uint32_t mulhi_u32(uint32_t a, uint32_t b) {
-#if CB_DEVICE_CODE
-    return __umulhi(a, b);
-#else
-    return (uint32_t)(((uint64_t)a * b) >> 32);
-#endif
-}
-
-struct FastConsts { uint32_t k28, k24, k16; };
+// Same contract as decode32() for segments whose SegParams::fast is set, with the special cases
+// folded into the table: the upper half of entry .x is the selector that builds the high view
+// (byte 3 = zero point unless all eight positions are kept), the upper half of .y the window
+// advance in bits.  `lut(idx)` returns the table entry of mask byte idx.
+// (Right shifts stay on the integer pipe: a multiply-high costs four issue cycles on the pipe
+// that also executes the bf16x2 arithmetic, a shift two on a pipe of its own.)
 
 // Two mask bytes (16 positions): `m16` holds them in its low 16 bits.  The window words are
 // advanced past the survivors consumed.  out[i] = bf16x2 weights of columns (2i, 2i+1), i < 8.
 template <class LutFn>
 CB_HD void decode16_fast(uint32_t m16, uint32_t& w0, uint32_t& w1, uint32_t& w2, uint32_t& w3, const SegParams& p,
-                         const FastConsts& K, LutFn lut, uint32_t out[8]) {
+                         LutFn lut, uint32_t out[8]) {
     const LutEntry e0 = lut(prmt(m16, 0u, 0x4440u));
     const LutEntry e1 = lut(prmt(m16, 0u, 0x4441u));
     const uint32_t zreg = p.zb24 >> 24;
@@ -340,13 +331,13 @@ CB_HD void decode16_fast(uint32_t m16, uint32_t& w0, uint32_t& w1, uint32_t& w2,
     for (int i = 0; i < 2; ++i) {
         const LutEntry e = i ? e1 : e0;
         // high view: (w0 >> 4) with byte 3 replaced by the zero point unless all eight positions are kept
-        const uint32_t hi = prmt(mulhi_u32(w0, K.k28), zreg, mulhi_u32(e.x, K.k16));
+        const uint32_t hi = prmt(w0 >> 4, zreg, e.x >> 16);
         const uint32_t d0 = prmt(w0, hi, e.x), d1 = prmt(w0, hi, e.y);
         out[4 * i + 0] = dq_pair(and_or(d0, 0x000F000Fu, 0x43004300u), p);
-        out[4 * i + 1] = dq_pair(and_or(mulhi_u32(d0, K.k24), 0x000F000Fu, 0x43004300u), p);
+        out[4 * i + 1] = dq_pair(and_or(d0 >> 8, 0x000F000Fu, 0x43004300u), p);
         out[4 * i + 2] = dq_pair(and_or(d1, 0x000F000Fu, 0x43004300u), p);
-        out[4 * i + 3] = dq_pair(and_or(mulhi_u32(d1, K.k24), 0x000F000Fu, 0x43004300u), p);
-        const uint32_t amt = mulhi_u32(e.y, K.k16);
+        out[4 * i + 3] = dq_pair(and_or(d1 >> 8, 0x000F000Fu, 0x43004300u), p);
+        const uint32_t amt = e.y >> 16;
         w0 = funnel_rc(w0, w1, amt);
         w1 = funnel_rc(w1, w2, amt);
         w2 = funnel_rc(w2, w3, amt);
@@ -355,9 +346,9 @@ CB_HD void decode16_fast(uint32_t m16, uint32_t& w0, uint32_t& w1, uint32_t& w2,
 
 template <class LutFn>
 CB_HD void decode32_fast(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, const SegParams& p,
-                         const FastConsts& K, LutFn lut, uint32_t out[16]) {
-    decode16_fast(m & 0xFFFFu, w0, w1, w2, w3, p, K, lut, out);
-    decode16_fast(m >> 16, w0, w1, w2, w3, p, K, lut, out + 8);
+                         LutFn lut, uint32_t out[16]) {
+    decode16_fast(m & 0xFFFFu, w0, w1, w2, w3, p, lut, out);
+    decode16_fast(m >> 16, w0, w1, w2, w3, p, lut, out + 8);
 }
 
 // ----------------------------------------------------------------------------- 2/3-bit -> nibble

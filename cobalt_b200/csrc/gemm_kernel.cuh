@@ -62,7 +62,6 @@ struct GemmParams {
     float* partials;            // [tile][split][GEMM_TOKENS][GEMM_ROWS] fp32 (splits > 1)
     uint32_t* counters;         // [tile]
     uint32_t* status;
-    FastConsts K;
 };
 
 // ---- tcgen05 / TMA wrappers
@@ -274,9 +273,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
                 const int col = (ct * TILE_GROUPS + (ks >> 1)) * GROUP + (ks & 1) * 64;
                 if (sp.fast) {
                     align_window<BITS>(raw0, off0, w0, w1, w2, w3);
-                    decode32_fast(m0w, w0, w1, w2, w3, sp, P.K, lut, e0);
+                    decode32_fast(m0w, w0, w1, w2, w3, sp, lut, e0);
                     align_window<BITS>(raw1, off1, w0, w1, w2, w3);
-                    decode32_fast(m1w, w0, w1, w2, w3, sp, P.K, lut, e1);
+                    decode32_fast(m1w, w0, w1, w2, w3, sp, lut, e1);
                 } else {
                     float cs[32];
                     const float* csp = nullptr;

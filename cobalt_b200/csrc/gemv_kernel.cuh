@@ -12,9 +12,13 @@
 // consecutive columns from each of the tile's 4 groups and the B fragment of the lane is
 // simply 8 contiguous bytes of x.
 //
-// A row block that is covered by several warps is finished by the last warp to arrive
-// (per-row-block counter): it adds the fp32 fragments of all its parts in range order, so the
-// result does not depend on timing.
+// A row block that is covered by several warps is finished in two deterministic stages.  The
+// parts held by one CTA meet in shared memory: the last of its warps to arrive adds the fp32
+// fragments in range order.  If the block straddles CTAs, that subtotal goes to global scratch and
+// the last CTA to arrive adds the subtotals in CTA order (fence + atomic + L2 round trips,
+// microseconds).  Warps whose range ends in a block that continues into the next CTA walk their
+// range backwards, so that this slow exchange happens at the start of both neighbours' work
+// instead of at the very end of the kernel.
 //
 // Behaviour replaced: cbk::gemv_sparse / gemv_sparse_expand, one warp per row with a 32-lane
 // prefix scan per 1024-column window (src/cobaltkernel/csrc/cobalt_gemv.cuh:216-393).
@@ -28,6 +32,9 @@ constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 4;
 constexpr uint32_t GEMV_LUT_BYTES = LUT_ENTRIES * LUT_COPIES * 8;      // 32 KB
 constexpr uint32_t GEMV_BAR_BYTES = GEMV_WARPS * GEMV_MAX_STAGES * 8;  // 512 B
+constexpr uint32_t GEMV_REDCNT_BYTES = 128;                            // in-CTA arrival counters: one per first owner + one
+// in-CTA reduction fragments: [warp][head|tail][4 * MT * 32] floats
+constexpr uint32_t gemv_red_bytes(int mt) { return GEMV_WARPS * 2 * 4 * mt * 32 * 4; }
 
 constexpr int GEMV_MAX_MATS = 4;
 
@@ -56,7 +63,6 @@ struct GemvParams {
     float* partials;                     // [total_warps][2][4 * MT * 32]
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
-    FastConsts K;
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -116,24 +122,32 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     const uint32_t bar0 = smem_u32(smem + GEMV_LUT_BYTES) + warp * GEMV_MAX_STAGES * 8;
     if (lane == 0)
         for (int s = 0; s < P.stages; ++s) mbar_init(bar0 + 8 * s, 1);
+    constexpr int FR = 4 * MT * 32;                                    // floats of one accumulator fragment set
+    uint32_t* red_cnt = reinterpret_cast<uint32_t*>(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES);
+    float* red = reinterpret_cast<float*>(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES);
+    if (threadIdx.x <= GEMV_WARPS) red_cnt[threadIdx.x] = 0u;
     mbar_fence_init();
     fence_proxy_async();
     __syncthreads();
 
     const int M = P.M, CT = P.CT;
-    const FastConsts KC = P.K;
     const uint32_t T = (uint32_t)P.RB * (uint32_t)P.CT, Wt = P.total_warps;
     const uint32_t gw = blockIdx.x * GEMV_WARPS + warp;
     const uint32_t t0 = range_start(gw, T, Wt), t1 = range_start(gw + 1, T, Wt);
     const int n = (int)(t1 - t0);
 
     const uint32_t per_warp = P.stages * P.slot_bytes + P.nib_bytes;
-    const uint32_t ring = smem_u32(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES) + warp * per_warp;
+    const uint32_t ring = smem_u32(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES + gemv_red_bytes(MT)) + warp * per_warp;
+    const uint32_t cta_t0 = range_start(blockIdx.x * GEMV_WARPS, T, Wt), cta_t1 = range_start((blockIdx.x + 1) * GEMV_WARPS, T, Wt);
+    // A warp whose range ends in the row block that continues into the next CTA walks backwards: that block's
+    // exchange through global scratch then starts early in both CTAs instead of ending the kernel.
+    const bool rev = n > 0 && ((t1 - 1u) / (uint32_t)P.CT + 1u) * (uint32_t)P.CT > cta_t1;
+    auto tile_at = [&](int i) { return rev ? t1 - 1u - (uint32_t)i : t0 + (uint32_t)i; };
     const uint32_t nib = ring + P.stages * P.slot_bytes;
     const uint32_t lut_lane = smem_u32(smem) + (uint32_t)(lane & (LUT_COPIES - 1)) * 8u;
     const LutEntry* lut_lane_ptr = lut_s + (lane & (LUT_COPIES - 1));
 
-    // address and size of tile t0 + i, looked up by lane i for the first 32 tiles of the range
+    // address and size of the i-th tile of the walk, looked up by lane i for the first 32 tiles
     auto tile_src = [&](uint32_t tau, const uint8_t*& src, uint32_t& bytes) {
         const int rbg = (int)(tau / (uint32_t)P.CT);
         const GemvMat& mt = P.mat[mat_of(rbg)];
@@ -144,7 +158,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     };
     const uint8_t* my_src = nullptr;
     uint32_t my_bytes = 0;
-    if (lane < n) tile_src(t0 + lane, my_src, my_bytes);
+    if (lane < n) tile_src(tile_at(lane), my_src, my_bytes);
 
     auto issue = [&](int i, int slot_idx) {                            // all lanes call; lane 0 acts
         const uint8_t* src;
@@ -154,7 +168,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             src = (const uint8_t*)a;
             bytes = __shfl_sync(full, my_bytes, i);
         } else {
-            tile_src(t0 + i, src, bytes);
+            tile_src(tile_at(i), src, bytes);
         }
         if (lane == 0) {
             const uint32_t bar = bar0 + 8 * slot_idx;
@@ -186,35 +200,76 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         const int row0 = (rb - mt.rb_start) * TILE_ROWS + g, row1 = row0 + 8;
         const bool whole = (t0 <= first) && (t1 > last);
         if (!whole) {
-            const uint32_t myslot = gw * 2u + (t0 >= first ? 0u : 1u);
-            float* mine = P.partials + (size_t)myslot * (4 * MT * 32);
-#pragma unroll
-            for (int b = 0; b < MT; ++b)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
-            __threadfence();
-            __syncwarp();
-            const uint32_t nparts = (T < Wt) ? (uint32_t)P.CT : tile_owner(last, T, Wt) - tile_owner(first, T, Wt) + 1u;
-            uint32_t old = 0;
-            if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
-            old = __shfl_sync(full, old, 0);
-            if (old != nparts - 1u) return;
-            __threadfence();
-#pragma unroll
-            for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
-            uint32_t prev = 0xFFFFFFFFu;
-            for (uint32_t tau = first; tau <= last; ++tau) {           // parts in range order
-                const uint32_t o = tile_owner(tau, T, Wt);
-                if (o == prev) continue;
-                prev = o;
-                const uint32_t slot = o * 2u + (range_start(o, T, Wt) >= first ? 0u : 1u);
-                const float* src = P.partials + (size_t)slot * (4 * MT * 32);
+            // ---- stage 1, shared memory: the parts held by this CTA's warps, added in range order by the last of them
+            const uint32_t o_first = tile_owner(first, T, Wt), o_last = tile_owner(last, T, Wt);
+            const uint32_t cta_lo = blockIdx.x * GEMV_WARPS;
+            const uint32_t lo_t = first > cta_t0 ? first : cta_t0, hi_t = last < cta_t1 - 1u ? last : cta_t1 - 1u;   // tiles of the block in this CTA
+            const uint32_t o_lo = o_first > cta_lo ? o_first : cta_lo;
+            const uint32_t o_hi = o_last < cta_lo + GEMV_WARPS - 1u ? o_last : cta_lo + GEMV_WARPS - 1u;
+            const uint32_t nlocal = (T < Wt) ? hi_t - lo_t + 1u : o_hi - o_lo + 1u;      // at most one tile per warp when T < Wt
+            if (nlocal > 1u) {
+                float* mine = red + (warp * 2 + (t0 >= first ? 0 : 1)) * FR;
 #pragma unroll
                 for (int b = 0; b < MT; ++b)
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) acc[b][r] += __ldcg(src + (b * 4 + r) * 32 + lane);
+                    for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
+                __threadfence_block();
+                __syncwarp();
+                // counter: keyed by the first owner inside the CTA; the block that began in an earlier CTA has its own
+                const uint32_t key = o_first < cta_lo ? (uint32_t)GEMV_WARPS : o_first - cta_lo;
+                uint32_t old = 0;
+                if (lane == 0) old = atomicAdd(&red_cnt[key], 1u);
+                old = __shfl_sync(full, old, 0);
+                if (old != nlocal - 1u) return;
+                __threadfence_block();
+#pragma unroll
+                for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+                if (T < Wt) {                                          // one tile per owner, owners not consecutive
+                    for (uint32_t tau = lo_t; tau <= hi_t; ++tau) {
+                        const volatile float* src = red + (tile_owner(tau, T, Wt) - cta_lo) * 2u * FR;
+#pragma unroll
+                        for (int b = 0; b < MT; ++b)
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
+                    }
+                } else {                                               // consecutive owners; only the block's first owner can hold it as a tail
+                    for (uint32_t o = o_lo; o <= o_hi; ++o) {
+                        const uint32_t tail = (o == o_first && range_start(o, T, Wt) < first) ? 1u : 0u;
+                        const volatile float* src = red + ((o - cta_lo) * 2u + tail) * FR;
+#pragma unroll
+                        for (int b = 0; b < MT; ++b)
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
+                    }
+                }
             }
-            if (lane == 0) P.counters[rb] = 0u;
+            // ---- stage 2, global scratch: one subtotal per CTA, added in CTA order by the last CTA to arrive
+            const uint32_t c_first = o_first / GEMV_WARPS, c_last = o_last / GEMV_WARPS;
+            if (c_first != c_last) {
+                float* mine = P.partials + (size_t)(blockIdx.x * 2u + (cta_t0 >= first ? 0u : 1u)) * FR;
+#pragma unroll
+                for (int b = 0; b < MT; ++b)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
+                fence_acq_rel_gpu();
+                __syncwarp();
+                uint32_t old = 0;
+                if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
+                old = __shfl_sync(full, old, 0);
+                if (old != c_last - c_first) return;
+                fence_acq_rel_gpu();
+#pragma unroll
+                for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+                for (uint32_t c = c_first; c <= c_last; ++c) {         // only the first CTA can hold the block as a tail
+                    const uint32_t tail = (c == c_first && range_start(c * GEMV_WARPS, T, Wt) < first) ? 1u : 0u;
+                    const float* src = P.partials + (size_t)(c * 2u + tail) * FR;
+#pragma unroll
+                    for (int b = 0; b < MT; ++b)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) acc[b][r] += __ldcg(src + (b * 4 + r) * 32 + lane);
+                }
+                if (lane == 0) P.counters[rb] = 0u;
+            }
         }
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
@@ -244,15 +299,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     bool healthy = true;
     int st = -1;                                                      // ring slot and phase parity of tile i
     uint32_t par = 0;
-    int cur_rb = (int)(t0 / (uint32_t)P.CT);
-    int rb = cur_rb, ct = (int)(t0 - (uint32_t)cur_rb * P.CT) - 1;      // advanced at the top of every iteration
+    const uint32_t tau0 = rev ? t1 - 1u : t0;                           // first tile of the walk
+    int cur_rb = (int)(tau0 / (uint32_t)P.CT);
+    int rb = cur_rb, ct = (int)(tau0 - (uint32_t)cur_rb * P.CT) + (rev ? 1 : -1);   // stepped at the top of every iteration
     for (int i = 0; i < issued; ++i) {
         if (++st == P.stages) { st = 0; par ^= 1u; }
         const bool ok = mbar_wait_bounded(bar0 + 8 * st, par, P.status, DEV_TIMEOUT_TILE);
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
-        if (++ct == CT) { ct = 0; ++rb; }
+        if (rev) { if (--ct < 0) { ct = CT - 1; --rb; } }
+        else if (++ct == CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {
             flush(cur_rb);
 #pragma unroll
@@ -343,8 +400,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                         xv[b][1] = ldg_nc_early(xp + 1);
                     }
                     uint32_t ea[8], eb[8];
-                    decode16_fast(h ? (mAj >> 16) : (mAj & 0xFFFFu), a0, a1, a2, a3, pA, KC, lut, ea);
-                    decode16_fast(h ? (mBj >> 16) : (mBj & 0xFFFFu), b0, b1, b2, b3, pB, KC, lut, eb);
+                    decode16_fast(h ? (mAj >> 16) : (mAj & 0xFFFFu), a0, a1, a2, a3, pA, lut, ea);
+                    decode16_fast(h ? (mBj >> 16) : (mBj & 0xFFFFu), b0, b1, b2, b3, pB, lut, eb);
 #pragma unroll
                     for (int b = 0; b < MT; ++b) {
                         mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);

@@ -91,9 +91,8 @@ int main() {
         decode32<LUT_COPIES>(m, w[0], w[1], w[2], w[3], p, lut.data() + (iter % LUT_COPIES), use_cs ? cs : nullptr, out);
         if (p.fast) {                                   // the fast variant must agree with the generic one
             uint32_t out2[16];
-            FastConsts K{1u << 28, 1u << 24, 1u << 16};
             const LutEntry* lp = lut.data() + (iter % LUT_COPIES);
-            decode32_fast(m, w[0], w[1], w[2], w[3], p, K, [lp](uint32_t i) { return lp[i * LUT_COPIES]; }, out2);
+            decode32_fast(m, w[0], w[1], w[2], w[3], p, [lp](uint32_t i) { return lp[i * LUT_COPIES]; }, out2);
             for (int k = 0; k < 16; ++k) if (out2[k] != out[k]) {
                 if (fails < 10) printf("decode32_fast mismatch iter=%d k=%d m=%08x got %08x want %08x\n", iter, k, m, out2[k], out[k]);
                 ++fails;
