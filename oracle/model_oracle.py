@@ -1,5 +1,5 @@
-"""Executable specification of the decoder that calls the compressed linears
-(Mistral / Llama family), restated from the reference.
+"""Executable specification of the decoders that call the compressed linears
+(Mistral / Llama family and Gemma-3 text), restated from the reference.
 
 TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).
 
@@ -8,6 +8,12 @@ Follows src/cobaltkernel/ref_llama.py:82-195 and the dtype policy stated at its 
 RoPE tables are computed in fp32 and cast to bf16; attention scores and the context
 product are bf16 matmuls with an fp32 softmax cast back to bf16; SwiGLU and the
 residual adds are bf16; no embedding scale; untied ``lm_head``.
+
+Gemma-3 follows src/cobaltkernel/ref_gemma3.py:138-294: RMSNorm multiplies by ``(1 + w)`` in fp32 and
+casts once; q and k get a per-head RMSNorm before RoPE; every branch is normalised again before it
+is added to the residual (four norms per layer); the MLP is GeGLU with the tanh GELU; embeddings are
+scaled by ``bf16(sqrt(hidden))``; sliding-window and full-attention layers alternate and use
+different RoPE bases; the attention scale is ``query_pre_attn_scalar ** -0.5``; the head is tied.
 
 Weights are a plain dict ``{hf_parameter_name: tensor}``; every linear weight is the
 dense dequantised ``[out, in]`` matrix in bf16, which is what the reference's module
@@ -36,6 +42,47 @@ def llama_config(hidden=4096, layers=32, heads=32, kv_heads=8, head_dim=128, int
     return dict(model_type="mistral", hidden_size=hidden, num_hidden_layers=layers, num_attention_heads=heads,
                 num_key_value_heads=kv_heads, head_dim=head_dim, intermediate_size=inter, vocab_size=vocab,
                 rms_norm_eps=eps, rope_theta=theta, sliding_window=sliding_window)
+
+
+def gemma3_config(hidden=5376, layers=62, heads=32, kv_heads=16, head_dim=128, inter=21504, vocab=262144, eps=1e-6,
+                  sliding_window=1024, pattern=6, query_pre_attn_scalar=168, rope_theta=1e6, rope_local_base_freq=1e4,
+                  rope_scaling=None):
+    """Config fields read by src/cobaltkernel/ref_gemma3.py:40-87 (old dialect).  Defaults: Gemma-3-27B text."""
+    return dict(model_type="gemma3_text", hidden_size=hidden, num_hidden_layers=layers, num_attention_heads=heads,
+                num_key_value_heads=kv_heads, head_dim=head_dim, intermediate_size=inter, vocab_size=vocab,
+                rms_norm_eps=eps, sliding_window=sliding_window, sliding_window_pattern=pattern,
+                query_pre_attn_scalar=query_pre_attn_scalar, rope_theta=rope_theta,
+                rope_local_base_freq=rope_local_base_freq, rope_scaling=rope_scaling, tie_word_embeddings=True)
+
+
+def gemma3_layer_types(cfg):
+    """src/cobaltkernel/ref_gemma3.py:57-67: every `pattern`-th layer attends globally."""
+    if cfg.get("layer_types"):
+        return list(cfg["layer_types"])
+    pat = cfg.get("sliding_window_pattern", 6)
+    return ["sliding_attention" if (i + 1) % pat else "full_attention" for i in range(cfg["num_hidden_layers"])]
+
+
+def gemma3_inv_freq(cfg, layer_type, device):
+    """src/cobaltkernel/ref_gemma3.py:70-101: local base for sliding layers; global base, optionally with linear scaling."""
+    D = cfg["head_dim"]
+    if layer_type == "sliding_attention":
+        return inv_freq(float(cfg.get("rope_local_base_freq", 1e4)), D, device)
+    inv = inv_freq(float(cfg.get("rope_theta", 1e6)), D, device)
+    sc = cfg.get("rope_scaling")
+    if sc:
+        kind = sc.get("rope_type", sc.get("type", "default"))
+        if kind == "linear":
+            inv = inv / float(sc["factor"])
+        elif kind != "default":
+            raise NotImplementedError(kind)
+    return inv
+
+
+def gemma_rms_norm(x, w, eps):
+    h = x.float()
+    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    return (h * (1.0 + w.float())).to(x.dtype)
 
 
 def inv_freq(theta, head_dim, device):
@@ -102,9 +149,57 @@ def new_kv(cfg):
     return [{"k": None, "v": None} for _ in range(cfg["num_hidden_layers"])]
 
 
+def _gemma3_attention(cfg, W, p, h, cos, sin, kv, positions, sliding):
+    T, D = h.shape[1], cfg["head_dim"]
+    nh, nkv, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["rms_norm_eps"]
+    q = _linear(h, W[p + "self_attn.q_proj.weight"]).view(1, T, nh, D).transpose(1, 2)
+    k = _linear(h, W[p + "self_attn.k_proj.weight"]).view(1, T, nkv, D).transpose(1, 2)
+    v = _linear(h, W[p + "self_attn.v_proj.weight"]).view(1, T, nkv, D).transpose(1, 2)
+    q = gemma_rms_norm(q, W[p + "self_attn.q_norm.weight"], eps)
+    k = gemma_rms_norm(k, W[p + "self_attn.k_norm.weight"], eps)
+    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    kv["k"] = k if kv["k"] is None else torch.cat([kv["k"], k], dim=2)
+    kv["v"] = v if kv["v"] is None else torch.cat([kv["v"], v], dim=2)
+    Kc, Vc = kv["k"], kv["v"]
+    S = Kc.shape[2]
+    att = torch.matmul(q, _repeat_kv(Kc, nh // nkv).transpose(2, 3)) * (float(cfg["query_pre_attn_scalar"]) ** -0.5)
+    kv_pos = torch.arange(S, device=q.device)
+    allowed = kv_pos[None, :] <= positions[:, None]
+    if sliding:
+        allowed &= kv_pos[None, :] > positions[:, None] - cfg["sliding_window"]
+    att = att.masked_fill(~allowed[None, None], float("-inf"))
+    att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
+    out = torch.matmul(att, _repeat_kv(Vc, nh // nkv)).transpose(1, 2).reshape(1, T, -1)
+    return _linear(out, W[p + "self_attn.o_proj.weight"])
+
+
+def _run_gemma3(cfg, W, ids, positions, kv):
+    eps = cfg["rms_norm_eps"]
+    e = W["model.embed_tokens.weight"][ids]
+    scale = torch.tensor(float(cfg["hidden_size"]) ** 0.5, dtype=e.dtype, device=e.device)      # rounded to bf16 first
+    h = (e * scale).unsqueeze(0)
+    types = gemma3_layer_types(cfg)
+    tables = {lt: rope_tables(gemma3_inv_freq(cfg, lt, h.device), positions, h.dtype) for lt in set(types)}
+    for i, lt in enumerate(types):
+        p = f"model.layers.{i}."
+        cos, sin = tables[lt]
+        x = gemma_rms_norm(h, W[p + "input_layernorm.weight"], eps)
+        x = _gemma3_attention(cfg, W, p, x, cos, sin, kv[i], positions, lt == "sliding_attention")
+        h = h + gemma_rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
+        x = gemma_rms_norm(h, W[p + "pre_feedforward_layernorm.weight"], eps)
+        g = _linear(x, W[p + "mlp.gate_proj.weight"])
+        u = _linear(x, W[p + "mlp.up_proj.weight"])
+        x = _linear(F.gelu(g, approximate="tanh") * u, W[p + "mlp.down_proj.weight"])
+        h = h + gemma_rms_norm(x, W[p + "post_feedforward_layernorm.weight"], eps)
+    h = gemma_rms_norm(h, W["model.norm.weight"], eps)
+    return F.linear(h, W["model.embed_tokens.weight"])                                          # tied head
+
+
 @torch.no_grad()
 def run(cfg, W, ids, positions, kv):
     """Logits ``[1, T, vocab]`` for tokens ``ids`` at ``positions``; ``kv`` is extended in place."""
+    if cfg.get("model_type") == "gemma3_text":
+        return _run_gemma3(cfg, W, ids, positions, kv)
     h = W["model.embed_tokens.weight"][ids].unsqueeze(0)
     inv = inv_freq(float(cfg["rope_theta"]), cfg["head_dim"], h.device)
     cos, sin = rope_tables(inv, positions, h.dtype)
@@ -126,7 +221,7 @@ def prefill(cfg, W, ids):
 
 
 def forward_step(cfg, W, token_id, pos, kv):
-    dev = W["lm_head.weight"].device
+    dev = W["model.embed_tokens.weight"].device
     ids = torch.tensor([token_id], device=dev, dtype=torch.long)
     return run(cfg, W, ids, torch.tensor([pos], device=dev), kv)[0, 0]
 

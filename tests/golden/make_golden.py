@@ -188,6 +188,52 @@ def main():
     np.savez_compressed(os.path.join(HERE, "golden_model.npz"), **mout)
     dig["model_cfg"] = mcfg
 
+    # tiny random Gemma-3-shaped model through src/cobaltkernel/ref_gemma3.py: sliding and full layers, linear RoPE
+    # scaling on the global base, a window short enough to cut the context
+    import ref_gemma3 as RG
+    gcfg = dict(model_type="gemma3_text", hidden_size=256, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=320, rms_norm_eps=1e-6,
+                sliding_window=8, sliding_window_pattern=2, query_pre_attn_scalar=96, rope_theta=1e6,
+                rope_local_base_freq=1e4, rope_scaling={"rope_type": "linear", "factor": 8.0}, tie_word_embeddings=True)
+    g = torch.Generator().manual_seed(2025)
+    Wg = {"model.embed_tokens.weight": rnd(320, 256, std=0.05), "model.norm.weight": rnd(256, std=0.1)}
+    for i in range(3):
+        pfx = f"model.layers.{i}."
+        for nm in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+            Wg[pfx + nm + ".weight"] = rnd(256, std=0.1)
+        Wg[pfx + "self_attn.q_norm.weight"] = rnd(64, std=0.1)
+        Wg[pfx + "self_attn.k_norm.weight"] = rnd(64, std=0.1)
+        Wg[pfx + "self_attn.q_proj.weight"] = rnd(256, 256)
+        Wg[pfx + "self_attn.k_proj.weight"] = rnd(128, 256)
+        Wg[pfx + "self_attn.v_proj.weight"] = rnd(128, 256)
+        Wg[pfx + "self_attn.o_proj.weight"] = rnd(256, 256)
+        Wg[pfx + "mlp.gate_proj.weight"] = rnd(512, 256)
+        Wg[pfx + "mlp.up_proj.weight"] = rnd(512, 256)
+        Wg[pfx + "mlp.down_proj.weight"] = rnd(256, 512)
+    gc = RG.Gemma3RefConfig(gcfg)
+    Wfull = dict(Wg)
+    Wfull["lm_head.weight"] = Wfull["model.embed_tokens.weight"]
+    gstate = {"cfg": gc, "W": Wfull, "device": "cpu", "dtype": torch.bfloat16,
+              "rope": {lt: RG._inv_freq(gc.rope_parameters[lt], gc.head_dim, "cpu") for lt in set(gc.layer_types)}}
+    gids = torch.randint(0, 320, (12,), generator=g)
+    glogits, gkv = RG.prefill(gstate, gids)
+    gtoks, gsteps = [], []
+    last = glogits[0, -1]
+    pos = 12
+    for _ in range(6):
+        t = int(last.float().argmax())
+        gtoks.append(t)
+        last = RG.forward_step(gstate, t, pos, gkv)
+        gsteps.append(bf16_bits(last))
+        pos += 1
+    gout = {k: bf16_bits(v) for k, v in Wg.items()}
+    gout["__ids"] = gids.numpy()
+    gout["__prefill_logits"] = bf16_bits(glogits[0])
+    gout["__tokens"] = np.array(gtoks)
+    gout["__step_logits"] = np.stack(gsteps)
+    np.savez_compressed(os.path.join(HERE, "golden_model_gemma3.npz"), **gout)
+    dig["gemma3_cfg"] = gcfg
+
     with open(os.path.join(HERE, "golden_digests.json"), "w") as f:
         json.dump(dig, f, indent=1)
     print("wrote", len(out), "arrays")
