@@ -14,7 +14,8 @@ from .compress import SparseQuantConfig, compress_weight, keep_mask, quantize_su
 from .format import TileImage, pack_tiles, slice_cols, slice_rows
 from .linear import CobaltSparseLinear, FusedProjections
 from .patch import patch_linearlayers, patch_model
+from .artifact import import_raw_layer, load_artifact, save_artifact, verify_artifact
 
-__all__ = ["CobaltSparseLinear", "FusedProjections", "patch_model", "patch_linearlayers", "SparseQuantConfig", "compress_weight",
+__all__ = ["import_raw_layer", "load_artifact", "save_artifact", "verify_artifact", "CobaltSparseLinear", "FusedProjections", "patch_model", "patch_linearlayers", "SparseQuantConfig", "compress_weight",
            "keep_mask", "quantize_survivors", "pack_tiles", "TileImage", "slice_rows", "slice_cols"]
 __version__ = "0.1.0"

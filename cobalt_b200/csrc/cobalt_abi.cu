@@ -510,13 +510,13 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
 }
 
 int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,
-                       void* stream) {
-    if (!h || !w || !y || T <= 0 || H <= 0) return COBALT_EINVAL;
+                       int flavor, void* stream) {
+    if (!h || !w || !y || T <= 0 || H <= 0 || flavor < 0 || flavor > 1) return COBALT_EINVAL;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
     add_rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)h, (const uint16_t*)delta, (const uint16_t*)w,
-                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps);
+                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps, flavor);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
@@ -534,13 +534,13 @@ int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positio
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
-int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, void* stream) {
-    if (!gate || !up || !out || n <= 0) return COBALT_EINVAL;
+int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream) {
+    if (!gate || !up || !out || n <= 0 || act < 0 || act > 1) return COBALT_EINVAL;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
     swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint16_t*)gate, (const uint16_t*)up,
-                                                                                 (uint16_t*)out, (long long)n);
+                                                                                 (uint16_t*)out, (long long)n, act);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 

@@ -1,8 +1,8 @@
 // Small fused kernels around the compressed linears of a decoder block: residual add + RMSNorm,
-// RoPE + KV-cache append, SwiGLU.  They follow the dtype policy of the reference's executable
-// spec (src/cobaltkernel/ref_llama.py:82-97, 139-143): every intermediate that the spec holds in a
-// bf16 tensor is rounded to bf16 here as well, so that results agree with the spec up to the
-// summation order of the mean.
+// RoPE + KV-cache append, SwiGLU / GeGLU.  They follow the dtype policy of the reference's
+// executable specs (src/cobaltkernel/ref_llama.py:82-97, 139-143; src/cobaltkernel/ref_gemma3.py:138-143, 173-174,
+// 225-228): every intermediate that the spec holds in a bf16 tensor is rounded to bf16 here as
+// well, so that results agree with the spec up to the summation order of the mean.
 #pragma once
 #include "common.cuh"
 
@@ -10,10 +10,12 @@ namespace cb {
 
 __device__ __forceinline__ float bf16_round(float f) { return bf16_to_float(float_to_bf16(f)); }
 
-// h_out = bf16(h + delta) (delta may be null), y = w * bf16( h_out * rsqrt(mean(h_out^2) + eps) )
-// one block per token; H % 2 == 0
+// h_out = bf16(h + delta) (delta may be null);
+// flavor 0 (Llama):  y = w * bf16( h_out * rsqrt(mean(h_out^2) + eps) )
+// flavor 1 (Gemma):  y = bf16( h_out * rsqrt(mean(h_out^2) + eps) * (1 + w) ), all in fp32 before the one rounding
+// one block per row
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, const uint16_t* delta, const uint16_t* w,
-                                                          uint16_t* h_out, uint16_t* y, int H, float eps) {
+                                                          uint16_t* h_out, uint16_t* y, int H, float eps, int flavor) {
     __shared__ float red[8];
     const size_t base = (size_t)blockIdx.x * H;
     float ss = 0.0f;
@@ -34,8 +36,12 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, con
     for (int i = threadIdx.x; i < H; i += 256) {
         float v = bf16_to_float(h[base + i]);
         if (delta) v = bf16_round(v + bf16_to_float(delta[base + i]));
-        const float n = bf16_round(v * r);
-        y[base + i] = float_to_bf16(bf16_to_float(w[i]) * n);
+        if (flavor == 0) {
+            const float n = bf16_round(v * r);
+            y[base + i] = float_to_bf16(bf16_to_float(w[i]) * n);
+        } else {
+            y[base + i] = float_to_bf16(__fmul_rn(__fmul_rn(v, r), __fadd_rn(1.0f, bf16_to_float(w[i]))));
+        }
     }
 }
 
@@ -72,13 +78,20 @@ __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v
     }
 }
 
-// out = bf16( bf16(silu(g)) * u )
-__global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* out, long long n) {
+// out = bf16( bf16(act(g)) * u ); act 0 = SiLU, act 1 = GELU with the tanh approximation
+__global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* out, long long n, int act) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = bf16_to_float(g[i]);
-    const float s = bf16_round(x / (1.0f + expf(-x)));
-    out[i] = float_to_bf16(s * bf16_to_float(u[i]));
+    float a;
+    if (act == 0) {
+        a = x / (1.0f + expf(-x));
+    } else {
+        const float kBeta = 0.7978845608028654f, kKappa = 0.044715f;   // sqrt(2/pi)
+        const float inner = kBeta * (x + kKappa * (x * x * x));
+        a = 0.5f * x * (1.0f + tanhf(inner));
+    }
+    out[i] = float_to_bf16(bf16_round(a) * bf16_to_float(u[i]));
 }
 
 }  // namespace cb

@@ -1,4 +1,4 @@
-"""Minimal Mistral/Llama-shaped decoder that calls the compressed linears.
+"""Minimal decoder (Mistral/Llama family and Gemma-3 text) that calls the compressed linears.
 
 This is the caller side of the hot path (the seven projections of every block): residual add +
 RMSNorm, RoPE + KV-cache append and SwiGLU are small fused CUDA kernels of the library;
@@ -6,6 +6,11 @@ grouped-query attention over the preallocated KV cache and the dense ``lm_head``
 leaves ``lm_head`` uncompressed: sinq/patch_model.py:49) are PyTorch matmuls.  The dtype policy follows the reference's executable spec
 src/cobaltkernel/ref_llama.py:10-16, 82-143: fp32 normalise -> bf16 -> times w; bf16 RoPE
 tables; bf16 score/context matmuls with an fp32 softmax cast back to bf16; bf16 residuals.
+With ``model_type == "gemma3_text"`` the block follows src/cobaltkernel/ref_gemma3.py:138-294 instead:
+``bf16(x * rr * (1 + w))`` norms, a per-head norm of q and k before RoPE, a second norm on every
+branch before it joins the residual, GeGLU (tanh), embeddings times ``bf16(sqrt(hidden))``,
+sliding-window and full-attention layers with their own RoPE bases, the attention scale
+``query_pre_attn_scalar ** -0.5`` and a head tied to the embedding.
 
 One decode step has static shapes (attention runs over the whole cache with a position mask;
 token id and position live in device tensors), so ``generate`` captures it once in a CUDA
@@ -45,10 +50,55 @@ def random_raw_layer(cfg: dict, layer: int, qcfg: SparseQuantConfig, device, see
     return out
 
 
+def is_gemma(cfg: dict) -> bool:
+    return cfg.get("model_type") == "gemma3_text"
+
+
+def layer_types(cfg: dict):
+    """Per-layer attention kind: Gemma-3 alternates (src/cobaltkernel/ref_gemma3.py:57-67); Llama is uniform."""
+    L = cfg["num_hidden_layers"]
+    if not is_gemma(cfg):
+        return ["sliding_attention" if cfg.get("sliding_window") else "full_attention"] * L
+    if cfg.get("layer_types"):
+        return list(cfg["layer_types"])
+    pat = cfg.get("sliding_window_pattern", 6)
+    return ["sliding_attention" if (i + 1) % pat else "full_attention" for i in range(L)]
+
+
+def rope_inv_freq(cfg: dict, layer_type: str, device):
+    """fp32 inverse frequencies of one layer kind (src/cobaltkernel/ref_gemma3.py:70-101, src/cobaltkernel/ref_llama.py:56-60)."""
+    D = cfg["head_dim"]
+    base = float(cfg.get("rope_theta", 1e6))
+    if is_gemma(cfg) and layer_type == "sliding_attention":
+        base = float(cfg.get("rope_local_base_freq", 1e4))
+    inv = 1.0 / (base ** (torch.arange(0, D, 2, dtype=torch.float32, device=device) / D))
+    sc = cfg.get("rope_scaling") if is_gemma(cfg) and layer_type == "full_attention" else None
+    if sc:
+        kind = sc.get("rope_type", sc.get("type", "default"))
+        if kind == "linear":
+            inv = inv / float(sc["factor"])
+        elif kind != "default":
+            raise NotImplementedError(kind)
+    return inv
+
+
 def random_dense_params(cfg: dict, device, seed: int = 7):
-    """Embedding, final norm, lm_head and per-layer norm weights (bf16), seeded."""
+    """Embedding, final norm, lm_head and per-layer norm weights (bf16), seeded.  Norm weights are the identity of
+    their family: ones for Llama (``w * x``), small random values around zero for Gemma (``(1 + w) * x``)."""
     g = torch.Generator().manual_seed(seed)
     H, V = cfg["hidden_size"], cfg["vocab_size"]
+    if is_gemma(cfg):
+        def nw(n):
+            return (torch.randn(n, generator=g) * 0.05).to(torch.bfloat16).to(device)
+        P = {"model.embed_tokens.weight": (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16).to(device),
+             "model.norm.weight": nw(H)}
+        for i in range(cfg["num_hidden_layers"]):
+            pfx = f"model.layers.{i}."
+            for nm in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+                P[pfx + nm + ".weight"] = nw(H)
+            P[pfx + "self_attn.q_norm.weight"] = nw(cfg["head_dim"])
+            P[pfx + "self_attn.k_norm.weight"] = nw(cfg["head_dim"])
+        return P
     P = {"model.embed_tokens.weight": (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16).to(device),
          "lm_head.weight": (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16).to(device),
          "model.norm.weight": torch.ones(H, dtype=torch.bfloat16, device=device)}
@@ -79,7 +129,12 @@ class CobaltDecoder:
         L, nkv, D = cfg["num_hidden_layers"], cfg["num_key_value_heads"], cfg["head_dim"]
         self.k_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
         self.v_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
-        self.inv_freq = 1.0 / (float(cfg["rope_theta"]) ** (torch.arange(0, D, 2, dtype=torch.float32, device=device) / D))
+        self.gemma = is_gemma(cfg)
+        self.types = layer_types(cfg)
+        self.inv_freq = {lt: rope_inv_freq(cfg, lt, device) for lt in set(self.types)}
+        self.scale = float(cfg["query_pre_attn_scalar"]) ** -0.5 if self.gemma else float(D) ** -0.5
+        if self.gemma:
+            self.embed_scale = torch.tensor(float(cfg["hidden_size"]) ** 0.5, dtype=torch.bfloat16, device=device)
         self.kv_pos = torch.arange(max_ctx, device=device)
         self.tok = torch.zeros(1, dtype=torch.long, device=device)        # next token to feed
         self.pos = torch.zeros(1, dtype=torch.long, device=device)        # its position
@@ -98,13 +153,20 @@ class CobaltDecoder:
         h_out = torch.empty_like(h) if delta is not None else h
         rc = self._lib.cobalt_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), w.data_ptr(),
                                           h_out.data_ptr() if delta is not None else None, y.data_ptr(), T, H,
-                                          float(self.cfg["rms_norm_eps"]), torch.cuda.current_stream(self.dev).cuda_stream)
+                                          float(self.cfg["rms_norm_eps"]), 1 if self.gemma else 0,
+                                          torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_add_rmsnorm", rc)
         return h_out, y
 
+    def _norm(self, x, w):
+        """Norm only (no residual); rows are the leading dimensions of ``x``, the last one is normalised."""
+        H = x.shape[-1]
+        return self._add_rmsnorm(x.reshape(-1, H), None, w)[1].view(x.shape)
+
     def _rope_kv(self, q, k, v, positions, layer):
         cfg = self.cfg
-        rc = self._lib.cobalt_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(), self.inv_freq.data_ptr(),
+        rc = self._lib.cobalt_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(),
+                                      self.inv_freq[self.types[layer]].data_ptr(),
                                       self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(), q.shape[0],
                                       cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], self.max_ctx,
                                       torch.cuda.current_stream(self.dev).cuda_stream)
@@ -112,7 +174,7 @@ class CobaltDecoder:
 
     def _swiglu(self, g, u):
         out = torch.empty_like(g)
-        rc = self._lib.cobalt_swiglu(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(),
+        rc = self._lib.cobalt_swiglu(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), 1 if self.gemma else 0,
                                      torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_swiglu", rc)
         return out
@@ -125,30 +187,45 @@ class CobaltDecoder:
         nh, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
         T, rep, S = ids.shape[0], nh // nkv, attend_len
         h = P["model.embed_tokens.weight"].index_select(0, ids)                        # [T, H]
-        allowed = self.kv_pos[None, :S] <= positions[:, None]                          # [T, S]
-        if cfg.get("sliding_window"):
-            allowed = allowed & (self.kv_pos[None, :S] > positions[:, None] - cfg["sliding_window"])
-        blocked = ~allowed[None, :, None, :]                                           # [1, T, 1, S]
-        scale = float(D) ** -0.5
+        if self.gemma:
+            h = h * self.embed_scale                                                   # scale rounded to bf16 first
+        causal = self.kv_pos[None, :S] <= positions[:, None]                           # [T, S]
+        blocked = {}
+        for lt in set(self.types):
+            allowed = causal
+            if lt == "sliding_attention" and cfg.get("sliding_window"):
+                allowed = allowed & (self.kv_pos[None, :S] > positions[:, None] - cfg["sliding_window"])
+            blocked[lt] = ~allowed[None, :, None, :]                                   # [1, T, 1, S]
+        scale = self.scale
         delta = None
         for i in range(cfg["num_hidden_layers"]):
             p = f"model.layers.{i}."
             h, x = self._add_rmsnorm(h, delta, P[p + "input_layernorm.weight"])
             q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
+            if self.gemma:                                                             # per-head norm of q and k
+                q = self._norm(q.view(T, nh, D), P[p + "self_attn.q_norm.weight"]).view(T, nh * D)
+                k = self._norm(k.view(T, nkv, D), P[p + "self_attn.k_norm.weight"]).view(T, nkv * D)
             self._rope_kv(q, k, v, positions, i)                                       # q in place, k/v into the caches
             Kc, Vc = self.k_cache[i][:, :S], self.v_cache[i][:, :S]                    # [nkv, S, D]
             # grouped-query attention as one batched matmul per KV head (no expanded copies of K/V)
             qg = q.view(T, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, T * rep, D)
             att = torch.bmm(qg, Kc.transpose(1, 2)) * scale                            # bf16 scores, scaled in bf16
-            att = att.view(nkv, T, rep, S).masked_fill(blocked, float("-inf"))
+            att = att.view(nkv, T, rep, S).masked_fill(blocked[self.types[i]], float("-inf"))
             att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype).view(nkv, T * rep, S)
             ctx = torch.bmm(att, Vc).view(nkv, T, rep, D).permute(1, 0, 2, 3).reshape(T, nh * D)
             o = self.lin[(i, "self_attn.o_proj")](ctx)
-            h, x = self._add_rmsnorm(h, o, P[p + "post_attention_layernorm.weight"])
+            if self.gemma:                                                             # the branch is normalised before it joins
+                o = self._norm(o, P[p + "post_attention_layernorm.weight"])
+                h, x = self._add_rmsnorm(h, o, P[p + "pre_feedforward_layernorm.weight"])
+            else:
+                h, x = self._add_rmsnorm(h, o, P[p + "post_attention_layernorm.weight"])
             g, u = self.gate_up[i](x)
             delta = self.lin[(i, "mlp.down_proj")](self._swiglu(g, u))
+            if self.gemma:
+                delta = self._norm(delta, P[p + "post_feedforward_layernorm.weight"])
         h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"])
-        return F.linear(x, P["lm_head.weight"]).unsqueeze(0)                           # [1, T, V]
+        head = P["model.embed_tokens.weight"] if self.gemma else P["lm_head.weight"]   # Gemma ties the head
+        return F.linear(x, head).unsqueeze(0)                                          # [1, T, V]
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:

@@ -162,18 +162,20 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
                        void* dev_x, void* dev_y, void* scratch, size_t scratch_bytes, void* stream);
 
 /* Fused element-wise steps of a decoder block around the linears, with the dtype policy of the
- * reference's executable spec (src/cobaltkernel/ref_llama.py:82-97, 139-143; in the reference they are
- * phases of its megakernel: src/cobaltkernel/csrc/megakernel.cu:270-288, 667-774).  All tensors bf16.
- *   cobalt_add_rmsnorm : h_out = h + delta (delta, h_out may be NULL); y = w * bf16(h_out * rsqrt(mean(h_out^2) + eps)),
- *                        [T, H] row-major.
+ * reference's executable specs (src/cobaltkernel/ref_llama.py:82-97, 139-143; src/cobaltkernel/ref_gemma3.py:138-143,
+ * 173-174, 225-228; in the reference they are phases of its megakernel: src/cobaltkernel/csrc/megakernel.cu:270-288,
+ * 667-774).  All tensors bf16.
+ *   cobalt_add_rmsnorm : h_out = h + delta (delta, h_out may be NULL); rows [T, H] row-major;
+ *                        flavor 0 (Llama): y = w * bf16(h_out * rsqrt(mean(h_out^2) + eps));
+ *                        flavor 1 (Gemma): y = bf16(h_out * rsqrt(mean(h_out^2) + eps) * (1 + w)).
  *   cobalt_rope_kv     : rotates q [T, n_heads*D] in place; rotates k and copies v [T, n_kv_heads*D] into the caches
  *                        [n_kv_heads][max_ctx][D] at positions[t]; inv_freq fp32 [D/2]; cos/sin rounded to bf16.
- *   cobalt_swiglu      : out = silu(gate) * up over n elements. */
+ *   cobalt_swiglu      : out = act(gate) * up over n elements; act 0 = SiLU, act 1 = GELU (tanh approximation). */
 int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,
-                       void* stream);
+                       int flavor, void* stream);
 int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positions, const float* inv_freq, void* k_cache,
                    void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, void* stream);
-int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, void* stream);
+int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream);
 
 /* Status word written by device code when a bounded wait gives up (0 = healthy).  Reads the
  * word at the start of `scratch` region reserved for it; synchronises `stream`. */

@@ -345,3 +345,26 @@ def test_config5_gemma27b_shard_shapes(name, K, N):
     ex = exact_fp64(x, Wb)
     assert float((part - ex).norm() / ex.norm()) <= 1e-5
     assert mod.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_artifact_roundtrip_on_device(tmp_path):
+    """Blob image written from device modules, checked by the verifier with the device pass (pruned positions decode
+    to exactly zero, src/prod/verify.py:137-145), loaded back: same bytes on the device, same outputs bit for bit."""
+    from cobalt_b200 import load_artifact, save_artifact, verify_artifact
+    dev = torch.device("cuda")
+    mods = {}
+    for i, (name, K, N, bits, sp) in enumerate([("model.layers.0.self_attn.q_proj", 256, 512, 4, 0.5),
+                                               ("model.layers.0.mlp.down_proj", 200, 1024, 3, 0.6),
+                                               ("model.layers.1.mlp.up_proj", 512, 256, 2, 0.5)]):
+        W, norm = O.seeded_matrix(K, N, 70 + i)
+        keep, q, sc, zr = O.compress(W, norm, bits, sp, 0.5)
+        mods[name] = CobaltSparseLinear(q.to(dev), sc.to(dev), zr.to(dev), keep.to(dev), None, None, {"nbits": bits})
+    save_artifact(str(tmp_path), mods)
+    rep = verify_artifact(str(tmp_path), device="cuda")
+    assert rep["ok"] and all(m["pruned_nonzero"] == 0 and m["finite"] for m in rep["matrices"].values())
+    back = load_artifact(str(tmp_path), device="cuda")
+    for name, m in mods.items():
+        assert torch.equal(back[name].packed, m.packed)
+        x = O.seeded_activation(3, m.in_features, 90).to(dev)
+        assert torch.equal(back[name](x), m(x))

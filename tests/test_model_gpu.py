@@ -97,6 +97,34 @@ def test_small_model_other_bit_widths(bits, sparsity):
     compare(dec, W, cfg, torch.randint(0, 1000, (17,), generator=g), 12, "cpu")
 
 
+def gemma_small(layers=4, window=16):
+    return MO.gemma3_config(hidden=512, layers=layers, heads=8, kv_heads=2, head_dim=64, inter=1024, vocab=1000,
+                            sliding_window=window, pattern=2, query_pre_attn_scalar=96,
+                            rope_scaling={"rope_type": "linear", "factor": 8.0})
+
+
+def test_small_gemma3_against_cpu_oracle():
+    """Gemma-3 block structure (src/cobaltkernel/ref_gemma3.py:138-294) through the kernels: (1 + w) norms, q/k norms,
+    branch norms, GeGLU, scaled embeddings, tied head, sliding (window 16 < context) and full layers."""
+    cfg = gemma_small()
+    dec, W = build(cfg, SparseQuantConfig(4, 0.5, 0.5), max_ctx=96, oracle_device="cpu")
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 1000, (40,), generator=g)
+    ref_logits, _ = MO.prefill(cfg, W, prompt)
+    got = dec.prefill(prompt).cpu()
+    d = (got.double() - ref_logits[0].double())
+    assert float(d.norm() / ref_logits.double().norm()) <= 5e-3
+    compare(dec, W, cfg, prompt, 24, "cpu")
+
+
+def test_small_gemma3_three_bit_sixty_percent():
+    """The bit width and sparsity of the 27B configuration (3-bit, 60 % sparse) on the small Gemma-3 model."""
+    cfg = gemma_small(layers=2)
+    dec, W = build(cfg, SparseQuantConfig(3, 0.6, 0.5), max_ctx=64, oracle_device="cpu")
+    g = torch.Generator().manual_seed(9)
+    compare(dec, W, cfg, torch.randint(0, 1000, (17,), generator=g), 12, "cpu")
+
+
 def test_config3_full_7b_shape():
     """32 layers, hidden 4096, GQA 32/8, inter 14336, vocab 32000, 4-bit 50 %; cache pre-filled with
     2048 seeded random tokens, 256 greedy tokens.  The oracle runs the same torch code on the GPU with
