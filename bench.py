@@ -13,8 +13,9 @@ the 126 MB L2).
              activations in/out) with all inputs resident in HBM, timed with CUDA events
              around K steps replayed from a CUDA graph.  q|k|v and gate|up read the same
              activations and go out as one fused launch each (4 launches per step).
-  e2e        the same metric through cobalt_linear_host(): pinned host activations copied
-             in, result copied back, every call.
+  e2e        the same metric through cobalt_linear_host_async(): pinned host activations
+             copied in and the result copied back by every call, one stream synchronisation
+             per step (when the caller reads the seven results).
   roofline   the GEMV kernel against the measured HBM copy bandwidth.
   cpu_baseline  the reference path (dense bf16 weight, torch.matmul) on the host cores.
 
@@ -333,10 +334,11 @@ def run_ours(args):
         for name, _, _ in SHAPES_7B:
             m = blk[name]
             sp = (scr[name].data_ptr() + 255) // 256 * 256
-            rc = lib.cobalt_linear_host(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
+            rc = lib.cobalt_linear_host_async(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
                                         xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
                                         stream.cuda_stream)
-            _lib.check("cobalt_linear_host", rc)
+            _lib.check("cobalt_linear_host_async", rc)
+        stream.synchronize()                                  # the caller reads the results: one wait per block
 
     for i in range(3):
         e2e_step(blocks[i % len(blocks)])

@@ -54,6 +54,8 @@ EXPORTS = {
     "cobalt_unpack": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p]),
     "cobalt_linear_host": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
+    "cobalt_linear_host_async": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                   c_void_p, c_size_t, c_void_p]),
     "cobalt_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "cobalt_rope_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_int, c_void_p]),

@@ -490,23 +490,31 @@ int cobalt_unpack(const CobaltMat* w, uint8_t* codes, uint8_t* keep, void* strea
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
-int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M, void* dev_x,
-                       void* dev_y, void* scratch, size_t scratch_bytes, void* stream) {
+int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M, void* dev_x,
+                             void* dev_y, void* scratch, size_t scratch_bytes, void* stream) {
     int rc = check_mat(w);
     if (rc) return rc;
     if (!x_host || !y_host || !dev_x || !dev_y || M <= 0) return COBALT_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
     if (cudaMemcpyAsync(dev_x, x_host, (size_t)M * w->N * 2, cudaMemcpyHostToDevice, st) != cudaSuccess) return COBALT_ELAUNCH;
-    // the two kernels lay out their arrival counters differently: start each call from a clean prefix
-    if (scratch && scratch_bytes >= 65536 && cudaMemsetAsync(scratch, 0, 65536, st) != cudaSuccess) return COBALT_ELAUNCH;
-    if (M <= MAX_GEMV_M)
+    if (M <= MAX_GEMV_M) {
+        // the GEMV clears the status word and its arrival counters itself
         rc = gemv_impl(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, /*clear_counters=*/true, stream);
-    else
+    } else {
+        // the two kernels lay out their arrival counters differently: start the GEMM from a clean prefix
+        if (scratch && scratch_bytes >= 65536 && cudaMemsetAsync(scratch, 0, 65536, st) != cudaSuccess) return COBALT_ELAUNCH;
         rc = cobalt_gemm(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, stream);
+    }
     if (rc) return rc;
     if (cudaMemcpyAsync(y_host, dev_y, (size_t)M * w->K * 2, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
-    if (cudaStreamSynchronize(st) != cudaSuccess) return COBALT_ELAUNCH;
     return COBALT_OK;
+}
+
+int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M, void* dev_x,
+                       void* dev_y, void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = cobalt_linear_host_async(w, x_host, y_host, bias, M, dev_x, dev_y, scratch, scratch_bytes, stream);
+    if (rc) return rc;
+    return cudaStreamSynchronize((cudaStream_t)stream) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,

@@ -160,6 +160,11 @@ int cobalt_unpack(const CobaltMat* w, uint8_t* codes, uint8_t* keep, void* strea
  * (benchmarks/benchmark_suite.py:1200-1217). */
 int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M,
                        void* dev_x, void* dev_y, void* scratch, size_t scratch_bytes, void* stream);
+/* The same without the final synchronisation: everything is stream-ordered; x_host and y_host must be pinned and
+ * stay valid until the caller has synchronised the stream.  Lets a caller queue all projections of a block and
+ * wait once. */
+int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M,
+                             void* dev_x, void* dev_y, void* scratch, size_t scratch_bytes, void* stream);
 
 /* Fused element-wise steps of a decoder block around the linears, with the dtype policy of the
  * reference's executable specs (src/cobaltkernel/ref_llama.py:82-97, 139-143; src/cobaltkernel/ref_gemma3.py:138-143,

@@ -368,3 +368,31 @@ def test_artifact_roundtrip_on_device(tmp_path):
         assert torch.equal(back[name].packed, m.packed)
         x = O.seeded_activation(3, m.in_features, 90).to(dev)
         assert torch.equal(back[name](x), m(x))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 5, 200])
+def test_host_buffer_entry_points(M):
+    """cobalt_linear_host and its non-synchronising variant: pinned host activations in, host results out, equal bit for bit
+    to the module's forward on device tensors."""
+    import ctypes
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    W, norm = O.seeded_matrix(384, 1024, 21)
+    keep, q, sc, zr = O.compress(W, norm, 4, 0.5, 0.5)
+    mod = CobaltSparseLinear(q.to(dev), sc.to(dev), zr.to(dev), keep.to(dev), None, None, {"nbits": 4})
+    x = O.seeded_activation(M, 1024, 22)
+    want = mod(x.to(dev)).cpu()
+    hx, hy, hy2 = x.pin_memory(), torch.empty(M, 384, dtype=torch.bfloat16).pin_memory(), torch.empty(M, 384, dtype=torch.bfloat16).pin_memory()
+    dx, dy = torch.empty(M, 1024, dtype=torch.bfloat16, device=dev), torch.empty(M, 384, dtype=torch.bfloat16, device=dev)
+    d = mod._descriptor()
+    need = max(lib.cobalt_gemv_scratch_bytes(ctypes.byref(d), min(M, 16)), lib.cobalt_gemm_scratch_bytes(ctypes.byref(d), M), 65536)
+    scr = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+    sp = (scr.data_ptr() + 255) // 256 * 256
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.cobalt_linear_host(ctypes.byref(d), hx.data_ptr(), hy.data_ptr(), None, M, dx.data_ptr(), dy.data_ptr(), sp, need, st) == 0
+    assert torch.equal(hy, want)
+    assert lib.cobalt_linear_host_async(ctypes.byref(d), hx.data_ptr(), hy2.data_ptr(), None, M, dx.data_ptr(), dy.data_ptr(), sp, need, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(hy2, want)
