@@ -191,6 +191,15 @@ def run_ours(args):
     ys = {name: torch.empty(M, v["K"], dtype=torch.bfloat16, device=dev) for name, v in info.items()}
 
     from cobalt_b200 import FusedProjections
+    reducer = None
+    if world > 1 and not args.nccl_allreduce:
+        try:                                                 # all-reduce over peer memory; NCCL if it cannot be set up
+            from cobalt_b200.tp import PeerReducer
+            reducer = PeerReducer(M * max(v["K"] for n, v in info.items() if n in ROW_PARALLEL), dev)
+        except Exception as e:                               # noqa: BLE001 - any failure means "use NCCL"
+            if rank == 0:
+                print(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+            reducer = None
     names = [t[0] for t in SHAPES_7B]
     fuse_groups = [] if args.no_fuse else [g for g in (("q", "k", "v"), ("gate", "up")) if all(n in names for n in g)]
     fused_of = {n: g for g in fuse_groups for n in g}
@@ -208,9 +217,14 @@ def run_ours(args):
                 fused[fused_of[name]](xs[name])
                 done.update(fused_of[name])
             elif world > 1 and name in ROW_PARALLEL:        # fp32 partial sums, one all-reduce, one rounding
-                part = blk[name](xs[name], out_fp32=True)
-                dist.all_reduce(part)
-                ys[name].copy_(part)
+                if reducer is not None:
+                    n = M * info[name]["K"]
+                    blk[name](xs[name], out_fp32=True, out=reducer.slot_view(n))
+                    reducer.reduce(n, ys[name].view(-1))
+                else:
+                    part = blk[name](xs[name], out_fp32=True)
+                    dist.all_reduce(part)
+                    ys[name].copy_(part)
             else:
                 blk[name](xs[name])
 
@@ -367,7 +381,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"Mistral-7B block projections q/k/v/o/gate/up/down, {BITS}-bit, {int(SPARSITY*100)}% sparse, "
                                f"g=128, M={M} decode GEMV" + (f"; tensor-parallel x{world}, one such shard per GPU, fp32 all-reduce "
-                                                               f"after o and down" if world > 1 else ""),
+                                                               f"after o and down ({'peer-memory kernel' if reducer is not None else 'NCCL'})" if world > 1 else ""),
                    "l2": f"{copies} block copies rotated ({copies * wbytes / 1e6:.0f} MB working set > L2)",
                    "bytes_per_step": int(wbytes + abytes), "peak": peak_kind},
         "clocks": clocks,
@@ -579,6 +593,7 @@ def main():
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: use NCCL instead of the peer-memory all-reduce kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")

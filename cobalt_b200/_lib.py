@@ -60,6 +60,8 @@ EXPORTS = {
     "cobalt_rope_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_int, c_void_p]),
     "cobalt_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "cobalt_allreduce_peer": (c_int, [c_void_p, c_int, c_int, c_size_t, c_size_t, c_size_t, c_void_p, c_int, c_void_p,
+                                      c_void_p]),
     "cobalt_device_status": (c_int, [c_void_p, c_void_p, POINTER(c_uint32)]),
     "cobalt_set_tuning": (c_int, [c_int, c_int]),
 }

@@ -542,6 +542,29 @@ int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positio
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
+int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t n, size_t slot_stride_bytes,
+                          size_t flags_off_bytes, void* out, int out_fp32, void* status, void* stream) {
+    if (!peer_base || !out || world < 1 || world > PEER_MAX_RANKS || rank < 0 || rank >= world) return COBALT_EINVAL;
+    if (n == 0 || (n & 3) || n * sizeof(float) > slot_stride_bytes || n > 0xFFFFFFFFull) return COBALT_EINVAL;
+    if (((uintptr_t)out & 15)) return COBALT_EINVAL;
+    if ((slot_stride_bytes & 15) || (flags_off_bytes & 15) || flags_off_bytes < 3 * slot_stride_bytes) return COBALT_EINVAL;
+    int sms = 0;
+    int rc = device_info(&sms);
+    if (rc) return rc;
+    PeerParams P = {};
+    for (int q = 0; q < world; ++q) {
+        if (!peer_base[q] || (peer_base[q] & 15)) return COBALT_EINVAL;
+        P.base[q] = peer_base[q];
+    }
+    P.rank = rank; P.world = world; P.n = (unsigned int)n;
+    P.slot_stride = slot_stride_bytes; P.flags_off = flags_off_bytes;
+    P.out = out_fp32 ? nullptr : (uint16_t*)out;
+    P.out32 = out_fp32 ? (float*)out : nullptr;
+    P.status = (uint32_t*)status;
+    peer_allreduce_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(P);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream) {
     if (!gate || !up || !out || n <= 0 || act < 0 || act > 1) return COBALT_EINVAL;
     int sms = 0;

@@ -54,6 +54,7 @@ enum : uint32_t {
     DEV_TIMEOUT_EMPTY = 3,     // GEMM: operand stage never drained
     DEV_TIMEOUT_ACC = 4,       // GEMM: accumulator never completed
     DEV_TIMEOUT_STAGE = 5,     // GEMM: compressed tile group never arrived
+    DEV_TIMEOUT_PEER = 6,      // peer all-reduce: a peer never published its partial
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers

@@ -94,4 +94,87 @@ __global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* ou
     out[i] = float_to_bf16(bf16_round(a) * bf16_to_float(u[i]));
 }
 
+// ----------------------------------------------------------------------------- all-reduce over peer memory
+// Sum of the fp32 partial outputs of a row-parallel layer, one [n]-vector per GPU, read straight from the peers'
+// memory (NVLink loads), added in rank order and rounded to bf16 once.  Every rank runs this kernel (one CTA) on its
+// own GPU: it moves its partial from the staging area (where the GEMV wrote it) into slot (epoch & 1), publishes
+// "my partial of epoch e is written" in each peer's flag array, waits (bounded) until all peers have published epoch
+// e in its own flag array, then reads.  The epoch counter lives on the device, so replaying a captured graph
+// advances it like eager calls do.  Two slots alternate, so that a rank that is ahead never overwrites a partial
+// that a peer is still reading (a rank can only finish epoch e after every peer has started it, i.e. has finished
+// reading epoch e-1).
+constexpr int PEER_MAX_RANKS = 8;
+constexpr int PEER_EPOCH_INDEX = 16;       // u32 index of the local epoch counter behind the flags
+
+struct PeerParams {
+    unsigned long long base[PEER_MAX_RANKS];   // every rank's symmetric buffer, as mapped into this process
+    int rank, world;
+    unsigned int n;                            // floats to reduce
+    unsigned long long slot_stride, flags_off; // bytes; staging at 0, slots at slot_stride and 2 * slot_stride
+    uint16_t* out;                             // bf16 [n]
+    float* out32;                              // or fp32 [n]
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P) {
+    __shared__ uint32_t epoch_s;
+    uint32_t* my_flags = reinterpret_cast<uint32_t*>(P.base[P.rank] + P.flags_off);
+    if (threadIdx.x == 0) {
+        const uint32_t e = my_flags[PEER_EPOCH_INDEX] + 1u;
+        my_flags[PEER_EPOCH_INDEX] = e;
+        epoch_s = e;
+    }
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    const unsigned long long slot_off = (1ull + (epoch & 1u)) * P.slot_stride;
+    const unsigned int n4 = P.n >> 2;                                  // n is a multiple of 4 (checked on the host)
+    {   // staging -> this epoch's slot
+        const float4* stage = reinterpret_cast<const float4*>(P.base[P.rank]);
+        float4* slot = reinterpret_cast<float4*>(P.base[P.rank] + slot_off);
+        for (unsigned int i = threadIdx.x; i < n4; i += 1024) slot[i] = stage[i];
+    }
+    __syncthreads();                                                   // the release below covers every thread's copy
+    bool good = true;
+    if ((int)threadIdx.x < P.world) {
+        uint32_t* theirs = reinterpret_cast<uint32_t*>(P.base[threadIdx.x] + P.flags_off) + P.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        const uint32_t* mine = my_flags + threadIdx.x;
+        good = false;
+        for (uint32_t it = 0; it < (1u << 21); ++it) {                 // about a second at the longest
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if ((int32_t)(v - epoch) >= 0) { good = true; break; }
+            if (it > 1024) __nanosleep(128);
+        }
+    }
+    if (!__syncthreads_and(good ? 1 : 0)) {
+        if (threadIdx.x == 0 && P.status) atomicCAS(P.status, 0u, (uint32_t)DEV_TIMEOUT_PEER);
+        return;
+    }
+    for (unsigned int i = threadIdx.x; i < n4; i += 1024) {
+        float4 v[PEER_MAX_RANKS];
+#pragma unroll
+        for (int q = 0; q < PEER_MAX_RANKS; ++q)                       // all peers' loads in flight before the first add
+            if (q < P.world) v[q] = ld_sys_f4(reinterpret_cast<const float*>(P.base[q] + slot_off) + 4 * i);
+        float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int q = 0; q < PEER_MAX_RANKS; ++q)
+            if (q < P.world) { s.x += v[q].x; s.y += v[q].y; s.z += v[q].z; s.w += v[q].w; }
+        if (P.out32) {
+            reinterpret_cast<float4*>(P.out32)[i] = s;
+        } else {
+            uint2 o;
+            o.x = (uint32_t)float_to_bf16(s.x) | ((uint32_t)float_to_bf16(s.y) << 16);
+            o.y = (uint32_t)float_to_bf16(s.z) | ((uint32_t)float_to_bf16(s.w) << 16);
+            reinterpret_cast<uint2*>(P.out)[i] = o;
+        }
+    }
+}
+
 }  // namespace cb

@@ -135,9 +135,10 @@ class CobaltSparseLinear(nn.Module):
         return (t.data_ptr() + a - 1) // a * a
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor, out_fp32: bool = False) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out_fp32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``out_fp32`` returns the raw fp32 sums (no bias, no rounding) -- the partial output a row-parallel
-        shard hands to its all-reduce."""
+        shard hands to its all-reduce.  ``out`` (contiguous ``[M, out_features]`` of the result dtype) receives the
+        result instead of a fresh tensor, e.g. a slot of a buffer that peers read."""
         if not x.is_cuda:
             raise RuntimeError("CobaltSparseLinear.forward needs a CUDA tensor; there is no CPU path")
         if x.dtype != torch.bfloat16:
@@ -148,7 +149,13 @@ class CobaltSparseLinear(nn.Module):
         if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
             x2 = x2.contiguous()
         M = x2.shape[0]
-        y = torch.empty(M, self.out_features, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+        want = torch.float32 if out_fp32 else torch.bfloat16
+        if out is not None:
+            if out.dtype != want or out.numel() != M * self.out_features or not out.is_contiguous() or out.device != x.device:
+                raise ValueError("`out` must be a contiguous [M, out_features] tensor of the result dtype on x's device")
+            y = out.view(M, self.out_features)
+        else:
+            y = torch.empty(M, self.out_features, dtype=want, device=x.device)
         if M == 0:
             return y.reshape(*lead, self.out_features)
         d = self._descriptor()

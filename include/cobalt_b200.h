@@ -182,6 +182,21 @@ int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positio
                    void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, void* stream);
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream);
 
+/* All-reduce (sum) of the fp32 partial outputs of a row-parallel layer over peer memory, for tensor-parallel decode
+ * (the reference has no distributed code; this replaces the NCCL all-reduce that would follow cobalt_linear_f32).
+ * Every rank owns one symmetric buffer mapped into all processes: [staging: slot_stride bytes][slot 0][slot 1][flags at
+ * flags_off >= 3 * slot_stride: 32 x u32], zero-initialised.  peer_base (host array, `world` entries) holds every
+ * rank's buffer address as seen by THIS process.  The caller has its GEMV write the fp32 partial [n] into the staging
+ * area of its own buffer, then calls this on every rank with the same n (all ranks make the same sequence of calls).
+ * One CTA: copies the partial into the slot of this call's epoch (a counter kept on the device, so graph replays
+ * advance it), publishes the epoch in every peer's flags, waits (bounded, about a second; on expiry the status word is
+ * set and the output is not written) until all peers have published theirs, reads all partials with peer loads, adds
+ * them in rank order (deterministic) and writes bf16 (out_fp32 = 0) or fp32.  n % 4 == 0, n <= slot_stride/4, out 16-byte
+ * aligned, world <= 8.  Plain
+ * peer loads and stores only (no multicast). */
+int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t n, size_t slot_stride_bytes,
+                          size_t flags_off_bytes, void* out, int out_fp32, void* status, void* stream);
+
 /* Status word written by device code when a bounded wait gives up (0 = healthy).  Reads the
  * word at the start of `scratch` region reserved for it; synchronises `stream`. */
 int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out);

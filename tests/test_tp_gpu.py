@@ -60,3 +60,52 @@ def test_tensor_parallel_shards_through_kernels():
         for M, (rel_c, rel_r, maxabs) in out[rank].items():
             assert rel_c <= 1e-3, f"rank {rank} M={M}: column-parallel rel-L2 {rel_c}"
             assert rel_r <= 1e-3, f"rank {rank} M={M}: row-parallel rel-L2 {rel_r}"
+
+
+def _peer_worker(rank, world, port, out):
+    import torch.distributed as dist
+    from cobalt_b200 import CobaltSparseLinear, tp
+    from oracle import cobalt_oracle as O
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        try:
+            red = tp.PeerReducer(4 * 256, torch.device("cuda", rank))
+        except Exception as e:                                # no peer mappings on this machine: nothing to test
+            out[rank] = ("unavailable", f"{type(e).__name__}: {e}")
+            return
+        raw = O.synth_raw(256, 2048, 0.5, 4, seed=31)
+        keep, q, sc, zr = raw["keep"], raw["q"], raw["scale"], raw["zero"]
+        k, qq, s, z = tp.shard_raw("row", keep, q, sc, zr, rank, world)
+        local = CobaltSparseLinear(qq.cuda(), s.cuda(), z.cuda(), k.cuda(), None, None, {"nbits": 4})
+        c0, c1 = tp.shard_bounds(2048, rank, world, 128)
+        via_peer, via_nccl = tp.RowParallelLinear(local, reducer=red), tp.RowParallelLinear(local)
+        same = True
+        for it in range(7):                                   # odd count: both slots, several epochs
+            M = (1, 4, 2, 1, 3, 1, 4)[it]
+            x = O.seeded_activation(M, 2048, 40 + it)[:, c0:c1].contiguous().cuda()
+            a, b = via_peer(x), via_nccl(x)
+            same = same and bool(torch.equal(a, b))            # two ranks: a + b in either order is the same sum
+        torch.cuda.synchronize()
+        out[rank] = (same, red.device_status())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_memory_allreduce_matches_nccl():
+    """Row-parallel layer with the all-reduce done by the peer-memory kernel (plain NVLink loads, flags with bounded
+    waits) against the same layer with NCCL: identical outputs over several calls that use both slots."""
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_peer_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    if any(out[r][0] == "unavailable" for r in range(world)):
+        pytest.skip(f"symmetric memory unavailable: {out[0][1]}")
+    for rank in range(world):
+        same, status = out[rank]
+        assert status == 0, f"rank {rank}: peer wait expired (status {status})"
+        assert same, f"rank {rank}: peer all-reduce differs from NCCL"
