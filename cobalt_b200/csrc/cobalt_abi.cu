@@ -561,8 +561,16 @@ int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t
     P.out = out_fp32 ? nullptr : (uint16_t*)out;
     P.out32 = out_fp32 ? (float*)out : nullptr;
     P.status = (uint32_t*)status;
-    peer_allreduce_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(P);
-    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream) {

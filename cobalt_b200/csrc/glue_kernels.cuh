@@ -124,6 +124,10 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
 
 __global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P) {
     __shared__ uint32_t epoch_s;
+    // Programmatic dependent launch: wait for the kernel that wrote the partial, and let the next kernel in the
+    // stream begin its own prologue (it waits for this grid before it touches activations).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint32_t* my_flags = reinterpret_cast<uint32_t*>(P.base[P.rank] + P.flags_off);
     if (threadIdx.x == 0) {
         const uint32_t e = my_flags[PEER_EPOCH_INDEX] + 1u;
