@@ -17,6 +17,9 @@ __device__ __forceinline__ float bf16_round(float f) { return bf16_to_float(floa
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, const uint16_t* delta, const uint16_t* w,
                                                           uint16_t* h_out, uint16_t* y, int H, float eps, int flavor) {
     __shared__ float red[8];
+    // the next kernel in the stream (usually a GEMV launched with programmatic serialisation) may run its prologue now;
+    // it waits for this grid before it reads y
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t base = (size_t)blockIdx.x * H;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < H; i += 256) {
@@ -49,6 +52,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, con
 __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v, const long long* positions,
                                const float* inv_freq, uint16_t* k_cache, uint16_t* v_cache, int T, int nh, int nkv,
                                int D, int max_ctx) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int half = D / 2;
     const int per_tok = (nh + 2 * nkv) * half;
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -80,6 +84,7 @@ __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v
 
 // out = bf16( bf16(act(g)) * u ); act 0 = SiLU, act 1 = GELU with the tanh approximation
 __global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* out, long long n, int act) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = bf16_to_float(g[i]);
