@@ -14,8 +14,8 @@ the 126 MB L2).
              around K steps replayed from a CUDA graph.  q|k|v and gate|up read the same
              activations and go out as one fused launch each (4 launches per step).
   e2e        the same metric through cobalt_linear_host_async(): pinned host activations
-             copied in and the result copied back by every call, one stream synchronisation
-             per step (when the caller reads the seven results).
+             copied in and the result copied back by every call; the seven calls of a step
+             alternate between two streams and the caller waits for both once per step.
   roofline   the GEMV kernel against the measured HBM copy bandwidth.
   cpu_baseline  the reference path (dense bf16 weight, torch.matmul) on the host cores.
 
@@ -344,15 +344,19 @@ def run_ours(args):
         need = lib.cobalt_gemv_scratch_bytes(ctypes.byref(m._descriptor()), M)
         scr[name] = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
 
+    side = torch.cuda.Stream(dev)                            # the seven calls are independent: two streams let one
+    e2e_streams = (stream, side)                             # call's copy-out overlap the next call's copy-in and kernel
+
     def e2e_step(blk):
-        for name, _, _ in SHAPES_7B:
+        for i, (name, _, _) in enumerate(SHAPES_7B):
             m = blk[name]
             sp = (scr[name].data_ptr() + 255) // 256 * 256
             rc = lib.cobalt_linear_host_async(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
-                                        xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
-                                        stream.cuda_stream)
+                                              xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
+                                              e2e_streams[i & 1].cuda_stream)
             _lib.check("cobalt_linear_host_async", rc)
         stream.synchronize()                                  # the caller reads the results: one wait per block
+        side.synchronize()
 
     for i in range(3):
         e2e_step(blocks[i % len(blocks)])

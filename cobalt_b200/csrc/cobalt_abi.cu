@@ -106,7 +106,11 @@ int gemv_config(const GemvGeom& g, int M, int num_sms, GemvCfg* c) {
     c->total_warps = (uint32_t)(grid * GEMV_WARPS);
     if ((unsigned long long)(tiles + 1) * c->total_warps >= (1ull << 32)) return COBALT_ETOOBIG;   // 32-bit partition arithmetic
     c->counters_off = SCRATCH_STATUS_BYTES;
+    // the counters of both kernels live in the first 64 KB behind the status word and their partial sums behind
+    // that, so that one zero-initialised buffer can serve GEMV and GEMM calls in any order (each kernel returns
+    // its counters to zero; neither ever sees the other's partial sums where it expects counters)
     c->partials_off = c->counters_off + round_up((size_t)RB * 4, 256);
+    if (c->partials_off < SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES) c->partials_off = SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES;
     c->total = c->partials_off + (size_t)c->total_warps * 2 * 4 * c->mt * 32 * sizeof(float);
     return COBALT_OK;
 }
@@ -162,6 +166,7 @@ int gemm_config(const CobaltMat* w, int M, int num_sms, GemmCfg* c) {
     c->grid = dim3((unsigned)row_tiles, (unsigned)tok_tiles, (unsigned)splits);
     c->counters_off = SCRATCH_STATUS_BYTES;
     c->partials_off = c->counters_off + round_up((size_t)units * 4, 256);
+    if (c->partials_off < SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES) c->partials_off = SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES;
     c->total = c->partials_off + (splits > 1 ? (size_t)units * splits * GEMM_TOKENS * GEMM_ROWS * sizeof(float) : 0);
     return COBALT_OK;
 }
@@ -242,7 +247,7 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     if (clear_counters) {
         // the status word and the per-row-block arrival counters must start at zero; the partial
         // sums behind them are always written before they are read
-        if (cudaMemsetAsync(scratch, 0, c.partials_off, st) != cudaSuccess) return COBALT_ELAUNCH;
+        if (cudaMemsetAsync(scratch, 0, c.counters_off + round_up((size_t)g.RB * 4, 256), st) != cudaSuccess) return COBALT_ELAUNCH;
     }
     GemvParams P = {};
     P.n_mats = n;
@@ -497,14 +502,11 @@ int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_hos
     if (!x_host || !y_host || !dev_x || !dev_y || M <= 0) return COBALT_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
     if (cudaMemcpyAsync(dev_x, x_host, (size_t)M * w->N * 2, cudaMemcpyHostToDevice, st) != cudaSuccess) return COBALT_ELAUNCH;
-    if (M <= MAX_GEMV_M) {
-        // the GEMV clears the status word and its arrival counters itself
-        rc = gemv_impl(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, /*clear_counters=*/true, stream);
-    } else {
-        // the two kernels lay out their arrival counters differently: start the GEMM from a clean prefix
-        if (scratch && scratch_bytes >= 65536 && cudaMemsetAsync(scratch, 0, 65536, st) != cudaSuccess) return COBALT_ELAUNCH;
+    // both kernels return their arrival counters to zero, so a scratch buffer that was zeroed once stays usable by either
+    if (M <= MAX_GEMV_M)
+        rc = gemv_impl(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, /*clear_counters=*/false, stream);
+    else
         rc = cobalt_gemm(w, dev_x, w->N, dev_y, w->K, bias, M, scratch, scratch_bytes, stream);
-    }
     if (rc) return rc;
     if (cudaMemcpyAsync(y_host, dev_y, (size_t)M * w->K * 2, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
     return COBALT_OK;

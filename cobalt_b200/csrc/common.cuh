@@ -16,6 +16,7 @@ constexpr int MAX_GEMV_M = 16;
 
 // scratch layout shared by the GEMV and GEMM entry points
 constexpr size_t SCRATCH_STATUS_BYTES = 256;     // [0]: status word written by bounded waits
+constexpr size_t SCRATCH_COUNTER_BYTES = 65536;  // arrival counters of either kernel; partial sums start behind them
 
 // device-side copy of CobaltMat with derived sizes
 struct MatView {

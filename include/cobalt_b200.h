@@ -155,7 +155,8 @@ int cobalt_unpack(const CobaltMat* w, uint8_t* codes, uint8_t* keep, void* strea
  * (M <= 16) or GEMM, copies y device->host and synchronises `stream`.  The matrix itself
  * stays resident on the device.  `x_host` / `y_host` should be pinned for full speed.
  * `dev_x`, `dev_y`, `scratch` are caller-owned device staging buffers of at least
- * M*N*2, M*K*2 and max(cobalt_gemv_scratch_bytes, cobalt_gemm_scratch_bytes) bytes.
+ * M*N*2, M*K*2 and max(cobalt_gemv_scratch_bytes, cobalt_gemm_scratch_bytes) bytes; `scratch` must be zeroed once
+ * before its first use and then serves GEMV- and GEMM-sized calls in any order (every kernel leaves it clean).
  * Mirrors what a caller of SparseQuantLinear.forward pays when its tensors live on the host
  * (benchmarks/benchmark_suite.py:1200-1217). */
 int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M,

@@ -396,3 +396,30 @@ def test_host_buffer_entry_points(M):
     assert lib.cobalt_linear_host_async(ctypes.byref(d), hx.data_ptr(), hy2.data_ptr(), None, M, dx.data_ptr(), dy.data_ptr(), sp, need, st) == 0
     torch.cuda.synchronize()
     assert torch.equal(hy2, want)
+
+
+@pytest.mark.gpu
+def test_one_scratch_serves_gemv_and_gemm_in_any_order():
+    """A scratch buffer zeroed once is reused by GEMM-sized (split-K) and GEMV-sized host calls in turn: every kernel
+    returns its arrival counters to zero and neither finds the other's partial sums where it expects counters."""
+    import ctypes
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    W, norm = O.seeded_matrix(384, 2048, 23)
+    keep, q, sc, zr = O.compress(W, norm, 3, 0.6, 0.5)
+    mod = CobaltSparseLinear(q.to(dev), sc.to(dev), zr.to(dev), keep.to(dev), None, None, {"nbits": 3})
+    d = mod._descriptor()
+    Ms = (200, 1, 64, 5, 16, 130, 2)
+    need = max(max(lib.cobalt_gemv_scratch_bytes(ctypes.byref(d), min(M, 16)), lib.cobalt_gemm_scratch_bytes(ctypes.byref(d), M)) for M in Ms)
+    scr = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+    sp = (scr.data_ptr() + 255) // 256 * 256
+    st = torch.cuda.current_stream().cuda_stream
+    for rnd in range(2):
+        for M in Ms:
+            x = O.seeded_activation(M, 2048, 24 + M)
+            want = mod(x.to(dev)).cpu()
+            hx, hy = x.pin_memory(), torch.empty(M, 384, dtype=torch.bfloat16).pin_memory()
+            dx, dy = torch.empty(M, 2048, dtype=torch.bfloat16, device=dev), torch.empty(M, 384, dtype=torch.bfloat16, device=dev)
+            assert lib.cobalt_linear_host(ctypes.byref(d), hx.data_ptr(), hy.data_ptr(), None, M, dx.data_ptr(), dy.data_ptr(), sp, need, st) == 0
+            assert torch.equal(hy, want), (rnd, M)
