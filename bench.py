@@ -543,13 +543,29 @@ def run_model(args):
     from a CUDA graph.  Prints tokens/s over the replayed decode steps (the prefill is not timed)."""
     from cobalt_b200 import SparseQuantConfig
     from cobalt_b200.decoder import build_random_decoder
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    dist, reducer = None, None
     cfg = dict(model_type="mistral", hidden_size=4096, num_hidden_layers=args.layers, num_attention_heads=32,
                num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rms_norm_eps=1e-5,
                rope_theta=1e6, sliding_window=None)
+    if world > 1:                                            # tensor parallel: heads and MLP columns split over the ranks
+        import datetime
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        if not args.nccl_allreduce:
+            try:
+                from cobalt_b200.tp import PeerReducer
+                reducer = PeerReducer(16 * cfg["hidden_size"], dev)
+            except Exception as e:                           # noqa: BLE001 - any failure means "use NCCL"
+                if rank == 0:
+                    print(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
     ctx, n_new = args.context, args.new_tokens
-    dec = build_random_decoder(cfg, SparseQuantConfig(BITS, SPARSITY, BETA), ctx + n_new, dev)
+    dec = build_random_decoder(cfg, SparseQuantConfig(BITS, SPARSITY, BETA), ctx + n_new, dev, tp_rank=rank, tp_world=world,
+                               reducer=reducer)
     g = torch.Generator().manual_seed(2048)
     prompt = torch.randint(0, cfg["vocab_size"], (ctx,), generator=g)
     t0 = time.perf_counter()
@@ -558,26 +574,40 @@ def run_model(args):
     warm_s = time.perf_counter() - t0
     # timed: replay the captured step n_new times (token and position advance on the device)
     dec.pos.fill_(ctx)
-    sampler = ClockSampler(0)
-    sampler.start()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
     torch.cuda.synchronize()
     e0.record()
     for _ in range(n_new):
         dec._graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    if dist is not None:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
     ms = e0.elapsed_time(e1) / n_new
-    wbytes = sum(m.compressed_bytes() for m in dec.lin.values())
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    wbytes = sum(m.compressed_bytes() for m in dec.lin.values()) * world
     status = max(m.device_status() for m in dec.lin.values())
+    if rank != 0:
+        _finish(dist)
+        return
     print(json.dumps({"metric": "7B-shape decode tokens/s (batch 1)", "value": round(1e3 / ms, 2), "unit": "tokens/s",
-                      "ms_per_token": round(ms, 4), "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "ms_per_token": round(ms, 4), "n_gpus": world, "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": f"Mistral-7B shape, {cfg['num_hidden_layers']} layers, {BITS}-bit {int(SPARSITY*100)}% sparse, "
-                                             f"context {ctx}, {n_new} greedy tokens, CUDA graph; dense bf16 lm_head",
+                                             f"context {ctx}, {n_new} greedy tokens, CUDA graph; dense bf16 lm_head"
+                                             + (f"; tensor-parallel x{world} ({'peer-memory' if reducer is not None else 'NCCL'} all-reduce)" if world > 1 else ""),
                                  "compressed_bytes_per_token": int(wbytes), "lm_head_bytes": 32000 * 4096 * 2},
                       "linear_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "clocks": clocks, "device_status": status,
                       "warmup_s": round(warm_s, 1)}), flush=True)
+    _finish(dist)
 
 
 def main():

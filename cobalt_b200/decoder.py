@@ -12,6 +12,11 @@ branch before it joins the residual, GeGLU (tanh), embeddings times ``bf16(sqrt(
 sliding-window and full-attention layers with their own RoPE bases, the attention scale
 ``query_pre_attn_scalar ** -0.5`` and a head tied to the embedding.
 
+Tensor parallel (``tp_world > 1``, one process per GPU): every rank holds its heads' rows of q/k/v, its
+columns of o, its rows of gate/up and its columns of down (``tp.shard_raw``); attention runs on the local
+heads; the fp32 partial outputs of o and down are summed over ranks (peer-memory kernel for decode-sized
+outputs, NCCL otherwise) and rounded once.  Norms, residuals, embedding and head are replicated.
+
 One decode step has static shapes (attention runs over the whole cache with a position mask;
 token id and position live in device tensors), so ``generate`` captures it once in a CUDA
 graph and replays it per token with no host round trip.
@@ -124,9 +129,13 @@ class CobaltDecoder:
     ``CobaltSparseLinear`` modules; ``dense`` holds embedding / norms / lm_head."""
 
     def __init__(self, cfg: dict, linears: Dict[tuple, CobaltSparseLinear], dense: Dict[str, torch.Tensor],
-                 max_ctx: int, device):
+                 max_ctx: int, device, tp_world: int = 1, reducer=None, group=None):
         self.cfg, self.lin, self.P, self.max_ctx, self.dev = cfg, linears, dense, max_ctx, device
-        L, nkv, D = cfg["num_hidden_layers"], cfg["num_key_value_heads"], cfg["head_dim"]
+        self.world, self.reducer, self.group = tp_world, reducer, group
+        if cfg["num_attention_heads"] % tp_world or cfg["num_key_value_heads"] % tp_world:
+            raise ValueError("heads must split evenly over the tensor-parallel ranks")
+        self.nh, self.nkv = cfg["num_attention_heads"] // tp_world, cfg["num_key_value_heads"] // tp_world   # local heads
+        L, nkv, D = cfg["num_hidden_layers"], self.nkv, cfg["head_dim"]
         self.k_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
         self.v_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
         self.gemma = is_gemma(cfg)
@@ -168,9 +177,22 @@ class CobaltDecoder:
         rc = self._lib.cobalt_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(),
                                       self.inv_freq[self.types[layer]].data_ptr(),
                                       self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(), q.shape[0],
-                                      cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], self.max_ctx,
+                                      self.nh, self.nkv, cfg["head_dim"], self.max_ctx,
                                       torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_rope_kv", rc)
+
+    def _row_parallel(self, lin, x):
+        """o / down: the whole layer on one GPU; with tensor parallelism the sum over ranks of the local fp32 partials."""
+        if self.world == 1:
+            return lin(x)
+        T, K = x.shape[0], lin.out_features
+        if self.reducer is not None and T * K * 4 <= self.reducer.stride:
+            lin(x, out_fp32=True, out=self.reducer.slot_view(T * K))
+            return self.reducer.reduce(T * K, torch.empty(T * K, dtype=x.dtype, device=x.device)).view(T, K)
+        import torch.distributed as dist
+        acc = lin(x, out_fp32=True)
+        dist.all_reduce(acc, group=self.group)
+        return acc.to(x.dtype)
 
     def _swiglu(self, g, u):
         out = torch.empty_like(g)
@@ -184,7 +206,7 @@ class CobaltDecoder:
         """ids, positions: [T] device tensors.  Keys/values are written at ``positions``; attention
         looks at cache slots [0, attend_len) under the causal mask ``slot <= position``."""
         cfg, P = self.cfg, self.P
-        nh, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+        nh, nkv, D = self.nh, self.nkv, cfg["head_dim"]                                # heads of this rank
         T, rep, S = ids.shape[0], nh // nkv, attend_len
         h = P["model.embed_tokens.weight"].index_select(0, ids)                        # [T, H]
         if self.gemma:
@@ -213,14 +235,14 @@ class CobaltDecoder:
             att = att.view(nkv, T, rep, S).masked_fill(blocked[self.types[i]], float("-inf"))
             att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype).view(nkv, T * rep, S)
             ctx = torch.bmm(att, Vc).view(nkv, T, rep, D).permute(1, 0, 2, 3).reshape(T, nh * D)
-            o = self.lin[(i, "self_attn.o_proj")](ctx)
+            o = self._row_parallel(self.lin[(i, "self_attn.o_proj")], ctx)
             if self.gemma:                                                             # the branch is normalised before it joins
                 o = self._norm(o, P[p + "post_attention_layernorm.weight"])
                 h, x = self._add_rmsnorm(h, o, P[p + "pre_feedforward_layernorm.weight"])
             else:
                 h, x = self._add_rmsnorm(h, o, P[p + "post_attention_layernorm.weight"])
             g, u = self.gate_up[i](x)
-            delta = self.lin[(i, "mlp.down_proj")](self._swiglu(g, u))
+            delta = self._row_parallel(self.lin[(i, "mlp.down_proj")], self._swiglu(g, u))
             if self.gemma:
                 delta = self._norm(delta, P[p + "post_feedforward_layernorm.weight"])
         h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"])
@@ -280,15 +302,20 @@ class CobaltDecoder:
         return torch.cat(toks).cpu(), torch.stack(all_logits)
 
 
-def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, device, keep_raw: bool = False):
+def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, device, keep_raw: bool = False,
+                         tp_rank: int = 0, tp_world: int = 1, reducer=None, group=None):
     """Random-init model of the given shape with every projection compressed.  Returns the decoder
-    and, when ``keep_raw``, the RAW tensors per (layer, proj) for an oracle to dequantise."""
+    and, when ``keep_raw``, the RAW tensors per (layer, proj) for an oracle to dequantise.  With
+    ``tp_world > 1`` every matrix is compressed whole (same seeds on every rank) and this rank keeps its shard."""
+    from .tp import kind_of, shard_raw
     lin, raws = {}, {}
     for i in range(cfg["num_hidden_layers"]):
         layer = random_raw_layer(cfg, i, qcfg, device)
         for name, (keep, q, sc, zr) in layer.items():
-            lin[(i, name)] = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": qcfg.bits})
             if keep_raw:
                 raws[(i, name)] = (keep, q, sc, zr)
-    dec = CobaltDecoder(cfg, lin, random_dense_params(cfg, device), max_ctx, device)
+            if tp_world > 1:
+                keep, q, sc, zr = shard_raw(kind_of(name), keep, q, sc, zr, tp_rank, tp_world)
+            lin[(i, name)] = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": qcfg.bits})
+    dec = CobaltDecoder(cfg, lin, random_dense_params(cfg, device), max_ctx, device, tp_world=tp_world, reducer=reducer, group=group)
     return (dec, raws) if keep_raw else dec
