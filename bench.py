@@ -405,13 +405,13 @@ def run_ours(args):
         "l2_resident": l2_resident,
     }
     if world == 1:
-        out["cpu_baseline"] = cpu_baseline(info, M, budget_s=15.0)
+        out["cpu_baseline"] = cpu_baseline(info, M, limit_s=15.0)
     print(json.dumps(out), flush=True)
     _finish(dist)
 
 
 # ----------------------------------------------------------------------------- CPU arm (reference path)
-def cpu_baseline(info, M, budget_s=15.0, steps=None, warmup=1):
+def cpu_baseline(info, M, limit_s=15.0, steps=None, warmup=1):
     """The reference path on the host cores: SparseQuantLinear keeps a dense bf16 copy of the
     dequantised weight after its first call and multiplies with torch.matmul
     (benchmarks/benchmark_suite.py:1200-1217).  The weight values do not influence the time, so a
@@ -434,7 +434,7 @@ def cpu_baseline(info, M, budget_s=15.0, steps=None, warmup=1):
         step()
         n += 1
         el = time.perf_counter() - t0
-        if (steps is not None and n >= steps) or (steps is None and (el > budget_s or n >= 50)):
+        if (steps is not None and n >= steps) or (steps is None and (el > limit_s or n >= 50)):
             break
     ms = el * 1e3 / n
     wbytes, abytes = step_bytes(info, M)
@@ -552,6 +552,13 @@ def run_model(args):
     cfg = dict(model_type="mistral", hidden_size=4096, num_hidden_layers=args.layers, num_attention_heads=32,
                num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=32000, rms_norm_eps=1e-5,
                rope_theta=1e6, sliding_window=None)
+    bits, sparsity, label = BITS, SPARSITY, "Mistral-7B"
+    if args.model == "gemma27b":                             # Gemma-3-27B text shape, 3-bit / 60 % sparse
+        cfg = dict(model_type="gemma3_text", hidden_size=5376, num_hidden_layers=62 if args.layers == 32 else args.layers,
+                   num_attention_heads=32, num_key_value_heads=16, head_dim=128, intermediate_size=21504, vocab_size=262144,
+                   rms_norm_eps=1e-6, sliding_window=1024, sliding_window_pattern=6, query_pre_attn_scalar=168,
+                   rope_theta=1e6, rope_local_base_freq=1e4, rope_scaling={"rope_type": "linear", "factor": 8.0})
+        bits, sparsity, label = 3, 0.6, "Gemma-3-27B"
     if world > 1:                                            # tensor parallel: heads and MLP columns split over the ranks
         import datetime
         import torch.distributed as dist
@@ -564,8 +571,8 @@ def run_model(args):
                 if rank == 0:
                     print(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
     ctx, n_new = args.context, args.new_tokens
-    dec = build_random_decoder(cfg, SparseQuantConfig(BITS, SPARSITY, BETA), ctx + n_new, dev, tp_rank=rank, tp_world=world,
-                               reducer=reducer)
+    dec = build_random_decoder(cfg, SparseQuantConfig(bits, sparsity, BETA), ctx + n_new, dev, tp_rank=rank, tp_world=world,
+                               reducer=reducer, clone_first_layer=args.model == "gemma27b")
     g = torch.Generator().manual_seed(2048)
     prompt = torch.randint(0, cfg["vocab_size"], (ctx,), generator=g)
     t0 = time.perf_counter()
@@ -599,12 +606,14 @@ def run_model(args):
     if rank != 0:
         _finish(dist)
         return
-    print(json.dumps({"metric": "7B-shape decode tokens/s (batch 1)", "value": round(1e3 / ms, 2), "unit": "tokens/s",
+    head_bytes = cfg["vocab_size"] * cfg["hidden_size"] * 2
+    print(json.dumps({"metric": f"{label}-shape decode tokens/s (batch 1)", "value": round(1e3 / ms, 2), "unit": "tokens/s",
                       "ms_per_token": round(ms, 4), "n_gpus": world, "dtype": "bf16", "data": "synthetic",
-                      "config": {"workload": f"Mistral-7B shape, {cfg['num_hidden_layers']} layers, {BITS}-bit {int(SPARSITY*100)}% sparse, "
+                      "config": {"workload": f"{label} shape, {cfg['num_hidden_layers']} layers, {bits}-bit {int(sparsity*100)}% sparse, "
                                              f"context {ctx}, {n_new} greedy tokens, CUDA graph; dense bf16 lm_head"
+                                             + ("; every layer holds its own copy of the first layer's seeded matrices" if args.model == "gemma27b" else "")
                                              + (f"; tensor-parallel x{world} ({'peer-memory' if reducer is not None else 'NCCL'} all-reduce)" if world > 1 else ""),
-                                 "compressed_bytes_per_token": int(wbytes), "lm_head_bytes": 32000 * 4096 * 2},
+                                 "compressed_bytes_per_token": int(wbytes), "lm_head_bytes": head_bytes},
                       "linear_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "clocks": clocks, "device_status": status,
                       "warmup_s": round(warm_s, 1)}), flush=True)
     _finish(dist)
@@ -627,6 +636,7 @@ def main():
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--model", default="mistral7b", choices=["mistral7b", "gemma27b"], help="shape of --workload model")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: use NCCL instead of the peer-memory all-reduce kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
     ap.add_argument("--profile", action="store_true",

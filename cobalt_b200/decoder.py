@@ -303,13 +303,23 @@ class CobaltDecoder:
 
 
 def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, device, keep_raw: bool = False,
-                         tp_rank: int = 0, tp_world: int = 1, reducer=None, group=None):
+                         tp_rank: int = 0, tp_world: int = 1, reducer=None, group=None, clone_first_layer: bool = False):
     """Random-init model of the given shape with every projection compressed.  Returns the decoder
     and, when ``keep_raw``, the RAW tensors per (layer, proj) for an oracle to dequantise.  With
-    ``tp_world > 1`` every matrix is compressed whole (same seeds on every rank) and this rank keeps its shard."""
+    ``tp_world > 1`` every matrix is compressed whole (same seeds on every rank) and this rank keeps its shard.
+    ``clone_first_layer`` compresses only layer 0 and gives every other layer its own copy of those packed bytes
+    (for timing very large shapes: the bytes streamed per token are the same, the compression time is not)."""
+    from .format import TileImage
     from .tp import kind_of, shard_raw
     lin, raws = {}, {}
     for i in range(cfg["num_hidden_layers"]):
+        if clone_first_layer and i > 0:
+            for name in PROJ:
+                src = lin[(0, name)]
+                m = CobaltSparseLinear._blank()
+                m._install(TileImage.from_meta(src.packed.clone(), src._img_meta), None, None, {"nbits": src.bits})
+                lin[(i, name)] = m
+            continue
         layer = random_raw_layer(cfg, i, qcfg, device)
         for name, (keep, q, sc, zr) in layer.items():
             if keep_raw:
