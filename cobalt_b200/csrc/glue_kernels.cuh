@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
         const uint32_t* mine = my_flags + threadIdx.x;
         good = false;
-        for (uint32_t it = 0; it < (1u << 21); ++it) {                 // about a second at the longest
+        for (uint32_t it = 0; it < (1u << 20); ++it) {                 // about a second at the longest
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if ((int32_t)(v - epoch) >= 0) { good = true; break; }

@@ -423,3 +423,38 @@ def test_one_scratch_serves_gemv_and_gemm_in_any_order():
             dx, dy = torch.empty(M, 2048, dtype=torch.bfloat16, device=dev), torch.empty(M, 384, dtype=torch.bfloat16, device=dev)
             assert lib.cobalt_linear_host(ctypes.byref(d), hx.data_ptr(), hy.data_ptr(), None, M, dx.data_ptr(), dy.data_ptr(), sp, need, st) == 0
             assert torch.equal(hy, want), (rnd, M)
+
+
+@pytest.mark.gpu
+def test_peer_allreduce_wait_expires_cleanly():
+    """Failure detection without a fault: a peer that never publishes its flag (here: a second buffer in the same
+    process that nothing writes to) makes the bounded wait of the all-reduce kernel run out; the kernel records the
+    status code, writes no output, returns, and the context keeps working."""
+    import ctypes
+    import time
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    n, stride = 1024, 4096
+    flags_off = 3 * stride
+    mine = torch.zeros((flags_off + 256) // 4, dtype=torch.float32, device=dev)
+    silent = torch.zeros_like(mine)                       # stands for a rank that never arrives
+    mine[:n] = 1.0
+    out = torch.full((n,), -7.0, dtype=torch.float32, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    ptrs = (ctypes.c_uint64 * 2)(mine.data_ptr(), silent.data_ptr())
+    t0 = time.time()
+    rc = lib.cobalt_allreduce_peer(ptrs, 0, 2, n, stride, flags_off, out.data_ptr(), 1, status.data_ptr(),
+                                   torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 20.0
+    assert int(status[0]) == 6                             # DEV_TIMEOUT_PEER
+    assert bool((out == -7.0).all())                       # nothing was written
+    # the context is intact: an ordinary call still works
+    W, norm = O.seeded_matrix(64, 256, 3)
+    keep, q, sc, zr = O.compress(W, norm, 4, 0.5, 0.5)
+    mod = CobaltSparseLinear(q.to(dev), sc.to(dev), zr.to(dev), keep.to(dev), None, None, {"nbits": 4})
+    x = O.seeded_activation(1, 256, 4)
+    Wb = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)
+    check_output(mod(x.to(dev)), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
