@@ -636,12 +636,19 @@ def main():
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--bits", type=int, default=0, help="decode workload: code width (default 4, the headline configuration)")
+    ap.add_argument("--sparsity", type=float, default=-1.0, help="decode workload: pruned fraction (default 0.5)")
     ap.add_argument("--model", default="mistral7b", choices=["mistral7b", "gemma27b"], help="shape of --workload model")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: use NCCL instead of the peer-memory all-reduce kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")
     args = ap.parse_args()
+    global BITS, SPARSITY
+    if args.bits:
+        BITS = args.bits
+    if args.sparsity >= 0:
+        SPARSITY = args.sparsity
     if args.workload == "prefill":
         run_prefill(args)
     elif args.workload == "model":
