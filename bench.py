@@ -573,12 +573,23 @@ def run_model(args):
     ctx, n_new = args.context, args.new_tokens
     dec = build_random_decoder(cfg, SparseQuantConfig(bits, sparsity, BETA), ctx + n_new, dev, tp_rank=rank, tp_world=world,
                                reducer=reducer, clone_first_layer=args.model == "gemma27b")
+    dec.fused_prompt_attention = bool(args.fused_prompt_attention)
     g = torch.Generator().manual_seed(2048)
     prompt = torch.randint(0, cfg["vocab_size"], (ctx,), generator=g)
     t0 = time.perf_counter()
     dec.generate(prompt, 4, use_graph=True)                     # prefill + graph capture + a few steps (warm-up)
     torch.cuda.synchronize()
     warm_s = time.perf_counter() - t0
+    # time to first token: one more prefill of the same prompt through the tcgen05 GEMM (kernels are configured now)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    p0.record()
+    dec.prefill(prompt)
+    p1.record()
+    torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
     # timed: replay the captured step n_new times (token and position advance on the device)
     dec.pos.fill_(ctx)
     sampler = ClockSampler(local)
@@ -615,6 +626,8 @@ def run_model(args):
                                              + (f"; tensor-parallel x{world} ({'peer-memory' if reducer is not None else 'NCCL'} all-reduce)" if world > 1 else ""),
                                  "compressed_bytes_per_token": int(wbytes), "lm_head_bytes": head_bytes},
                       "linear_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "clocks": clocks, "device_status": status,
+                      "prefill_attention": "fused library kernel (not the spec's rounding points)" if args.fused_prompt_attention else "spec arithmetic",
+                      "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(ctx / (prefill_ms * 1e-3), 1),
                       "warmup_s": round(warm_s, 1)}), flush=True)
     _finish(dist)
 
@@ -638,6 +651,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--bits", type=int, default=0, help="decode workload: code width (default 4, the headline configuration)")
     ap.add_argument("--sparsity", type=float, default=-1.0, help="decode workload: pruned fraction (default 0.5)")
+    ap.add_argument("--fused-prompt-attention", action="store_true", help="--workload model: fused library attention for the prompt")
     ap.add_argument("--model", default="mistral7b", choices=["mistral7b", "gemma27b"], help="shape of --workload model")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: use NCCL instead of the peer-memory all-reduce kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")

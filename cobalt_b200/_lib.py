@@ -56,9 +56,10 @@ EXPORTS = {
                                    c_void_p, c_size_t, c_void_p]),
     "cobalt_linear_host_async": (c_int, [POINTER(CobaltMat), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
-    "cobalt_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
+    "cobalt_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p,
+                                   c_void_p]),
     "cobalt_rope_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                               c_int, c_void_p]),
+                               c_int, c_void_p, c_void_p, c_float, c_void_p]),
     "cobalt_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "cobalt_allreduce_peer": (c_int, [c_void_p, c_int, c_int, c_size_t, c_size_t, c_size_t, c_void_p, c_int, c_void_p,
                                       c_void_p]),

@@ -520,23 +520,33 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
 }
 
 int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,
-                       int flavor, void* stream) {
+                       int flavor, const void* w_branch, void* stream) {
     if (!h || !w || !y || T <= 0 || H <= 0 || flavor < 0 || flavor > 1) return COBALT_EINVAL;
+    if (w_branch && (flavor != 1 || !delta)) return COBALT_EINVAL;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
     add_rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)h, (const uint16_t*)delta, (const uint16_t*)w,
-                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps, flavor);
+                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps, flavor, (const uint16_t*)w_branch);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positions, const float* inv_freq, void* k_cache,
-                   void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, void* stream) {
+                   void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, const void* q_norm_w,
+                   const void* k_norm_w, float eps, void* stream) {
     if (!q || !k || !v || !positions || !inv_freq || !k_cache || !v_cache) return COBALT_EINVAL;
     if (T <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || max_ctx <= 0) return COBALT_EINVAL;
+    if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return COBALT_EINVAL;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
+    if (q_norm_w) {
+        const long long warps = (long long)T * (n_heads + 2 * n_kv_heads);
+        rope_kv_norm_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            (uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, (const long long*)positions, inv_freq, (uint16_t*)k_cache,
+            (uint16_t*)v_cache, T, n_heads, n_kv_heads, head_dim, max_ctx, (const uint16_t*)q_norm_w, (const uint16_t*)k_norm_w, eps);
+        return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+    }
     const long long n = (long long)T * (n_heads + 2 * n_kv_heads) * (head_dim / 2);
     rope_kv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         (uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, (const long long*)positions, inv_freq, (uint16_t*)k_cache,

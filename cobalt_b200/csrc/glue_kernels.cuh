@@ -10,35 +10,56 @@ namespace cb {
 
 __device__ __forceinline__ float bf16_round(float f) { return bf16_to_float(float_to_bf16(f)); }
 
-// h_out = bf16(h + delta) (delta may be null);
-// flavor 0 (Llama):  y = w * bf16( h_out * rsqrt(mean(h_out^2) + eps) )
-// flavor 1 (Gemma):  y = bf16( h_out * rsqrt(mean(h_out^2) + eps) * (1 + w) ), all in fp32 before the one rounding
+// h_out = bf16(h + delta') (delta may be null);
+// flavor 0 (Llama):  y = w * bf16( h_out * rsqrt(mean(h_out^2) + eps) ),  delta' = delta
+// flavor 1 (Gemma):  y = bf16( h_out * rsqrt(mean(h_out^2) + eps) * (1 + w) ), all in fp32 before the one rounding;
+//                    with w_branch the branch is normalised first: delta' = bf16( delta * rsqrt(mean(delta^2) + eps) * (1 + w_branch) )
+//                    (the post-attention / post-feedforward norm of src/cobaltkernel/ref_gemma3.py:262-270)
 // one block per row
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, const uint16_t* delta, const uint16_t* w,
-                                                          uint16_t* h_out, uint16_t* y, int H, float eps, int flavor) {
+                                                          uint16_t* h_out, uint16_t* y, int H, float eps, int flavor,
+                                                          const uint16_t* w_branch) {
     __shared__ float red[8];
     // the next kernel in the stream (usually a GEMV launched with programmatic serialisation) may run its prologue now;
     // it waits for this grid before it reads y
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t base = (size_t)blockIdx.x * H;
+    auto block_sum = [&](float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        __syncthreads();                                               // `red` may still be read from the previous sum
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tot += red[k];
+        return tot;
+    };
+    float rb = 0.0f;                                                   // branch norm factor
+    const bool norm_branch = delta != nullptr && w_branch != nullptr;
+    if (norm_branch) {
+        float sb = 0.0f;
+        for (int i = threadIdx.x; i < H; i += 256) { const float d = bf16_to_float(delta[base + i]); sb += d * d; }
+        rb = rsqrtf(block_sum(sb) / (float)H + eps);
+    }
+    auto joined = [&](int i) {                                         // bf16(h + delta')
+        float v = bf16_to_float(h[base + i]);
+        if (delta) {
+            float d = bf16_to_float(delta[base + i]);
+            if (norm_branch) d = bf16_round(__fmul_rn(__fmul_rn(d, rb), __fadd_rn(1.0f, bf16_to_float(w_branch[i]))));
+            v = bf16_round(v + d);
+        }
+        return v;
+    };
     float ss = 0.0f;
     for (int i = threadIdx.x; i < H; i += 256) {
-        float v = bf16_to_float(h[base + i]);
-        if (delta) v = bf16_round(v + bf16_to_float(delta[base + i]));
+        const float v = joined(i);
         if (h_out) h_out[base + i] = float_to_bf16(v);
         ss += v * v;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) tot += red[k];
-    const float r = rsqrtf(tot / (float)H + eps);
+    const float r = rsqrtf(block_sum(ss) / (float)H + eps);
     for (int i = threadIdx.x; i < H; i += 256) {
-        float v = bf16_to_float(h[base + i]);
-        if (delta) v = bf16_round(v + bf16_to_float(delta[base + i]));
+        const float v = h_out ? bf16_to_float(h_out[base + i]) : joined(i);
         if (flavor == 0) {
             const float n = bf16_round(v * r);
             y[base + i] = float_to_bf16(bf16_to_float(w[i]) * n);
@@ -79,6 +100,48 @@ __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v
         uint16_t* dst = v_cache + ((size_t)hv * max_ctx + (size_t)pos) * D;
         dst[d] = src[d];
         dst[d + half] = src[d + half];
+    }
+}
+
+// The same with Gemma-3's per-head norm of q and k in front (src/cobaltkernel/ref_gemma3.py:181-185): one warp per (token, head);
+// x' = bf16( x * rsqrt(mean_D(x^2) + eps) * (1 + w[d]) ), then the rotation on x'.  v is copied unchanged.
+__global__ void __launch_bounds__(256) rope_kv_norm_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v, const long long* positions,
+                                                           const float* inv_freq, uint16_t* k_cache, uint16_t* v_cache, int T, int nh,
+                                                           int nkv, int D, int max_ctx, const uint16_t* q_norm_w,
+                                                           const uint16_t* k_norm_w, float eps) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int half = D / 2;
+    const int heads = nh + 2 * nkv;
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)T * heads) return;
+    const int t = (int)(wid / heads), head = (int)(wid - (long long)t * heads);
+    const long long pos = positions[t];
+    if (head >= nh + nkv) {                                            // v: plain copy into the cache
+        const int hv = head - nh - nkv;
+        const uint16_t* src = v + ((size_t)t * nkv + hv) * D;
+        uint16_t* dst = v_cache + ((size_t)hv * max_ctx + (size_t)pos) * D;
+        for (int d = lane; d < D; d += 32) dst[d] = src[d];
+        return;
+    }
+    const bool is_q = head < nh;
+    const uint16_t* src = is_q ? q + ((size_t)t * nh + head) * D : k + ((size_t)t * nkv + (head - nh)) * D;
+    const uint16_t* nw = is_q ? q_norm_w : k_norm_w;
+    uint16_t* dst = is_q ? q + ((size_t)t * nh + head) * D : k_cache + ((size_t)(head - nh) * max_ctx + (size_t)pos) * D;
+    float ss = 0.0f;
+    for (int d = lane; d < D; d += 32) { const float x = bf16_to_float(src[d]); ss += x * x; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    const float r = rsqrtf(ss / (float)D + eps);
+    for (int d = lane; d < half; d += 32) {
+        const float x1 = bf16_round(__fmul_rn(__fmul_rn(bf16_to_float(src[d]), r), __fadd_rn(1.0f, bf16_to_float(nw[d]))));
+        const float x2 = bf16_round(__fmul_rn(__fmul_rn(bf16_to_float(src[d + half]), r), __fadd_rn(1.0f, bf16_to_float(nw[d + half]))));
+        const float ang = (float)pos * inv_freq[d];
+        const float c = bf16_round(cosf(ang)), s = bf16_round(sinf(ang));
+        const float o1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * s));
+        const float o2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
+        dst[d] = float_to_bf16(o1);
+        dst[d + half] = float_to_bf16(o2);
     }
 }
 

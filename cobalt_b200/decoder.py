@@ -132,6 +132,7 @@ class CobaltDecoder:
                  max_ctx: int, device, tp_world: int = 1, reducer=None, group=None):
         self.cfg, self.lin, self.P, self.max_ctx, self.dev = cfg, linears, dense, max_ctx, device
         self.world, self.reducer, self.group = tp_world, reducer, group
+        self.fused_prompt_attention = False
         if cfg["num_attention_heads"] % tp_world or cfg["num_key_value_heads"] % tp_world:
             raise ValueError("heads must split evenly over the tensor-parallel ranks")
         self.nh, self.nkv = cfg["num_attention_heads"] // tp_world, cfg["num_key_value_heads"] // tp_world   # local heads
@@ -155,14 +156,15 @@ class CobaltDecoder:
         self._logits = None
 
     # ------------------------------------------------------------------ fused element-wise steps (C ABI)
-    def _add_rmsnorm(self, h, delta, w):
-        """(h + delta, rmsnorm(h + delta) * w); ``delta`` may be None."""
+    def _add_rmsnorm(self, h, delta, w, w_branch=None):
+        """(h + delta, rmsnorm(h + delta) * w); ``delta`` may be None.  Gemma: ``w_branch`` normalises ``delta`` first."""
         T, H = h.shape
         y = torch.empty_like(h)
         h_out = torch.empty_like(h) if delta is not None else h
         rc = self._lib.cobalt_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(), w.data_ptr(),
                                           h_out.data_ptr() if delta is not None else None, y.data_ptr(), T, H,
                                           float(self.cfg["rms_norm_eps"]), 1 if self.gemma else 0,
+                                          None if (w_branch is None or delta is None) else w_branch.data_ptr(),
                                           torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_add_rmsnorm", rc)
         return h_out, y
@@ -174,10 +176,14 @@ class CobaltDecoder:
 
     def _rope_kv(self, q, k, v, positions, layer):
         cfg = self.cfg
+        qn = kn = None
+        if self.gemma:                                                                 # per-head norm of q and k, fused in
+            qn = self.P[f"model.layers.{layer}.self_attn.q_norm.weight"].data_ptr()
+            kn = self.P[f"model.layers.{layer}.self_attn.k_norm.weight"].data_ptr()
         rc = self._lib.cobalt_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(),
                                       self.inv_freq[self.types[layer]].data_ptr(),
                                       self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(), q.shape[0],
-                                      self.nh, self.nkv, cfg["head_dim"], self.max_ctx,
+                                      self.nh, self.nkv, cfg["head_dim"], self.max_ctx, qn, kn, float(cfg["rms_norm_eps"]),
                                       torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_rope_kv", rc)
 
@@ -212,40 +218,46 @@ class CobaltDecoder:
         if self.gemma:
             h = h * self.embed_scale                                                   # scale rounded to bf16 first
         causal = self.kv_pos[None, :S] <= positions[:, None]                           # [T, S]
-        blocked = {}
+        blocked, allowed_of = {}, {}
         for lt in set(self.types):
             allowed = causal
             if lt == "sliding_attention" and cfg.get("sliding_window"):
                 allowed = allowed & (self.kv_pos[None, :S] > positions[:, None] - cfg["sliding_window"])
             blocked[lt] = ~allowed[None, :, None, :]                                   # [1, T, 1, S]
+            allowed_of[lt] = allowed[None, None]                                       # [1, 1, T, S]
         scale = self.scale
-        delta = None
+        delta, delta_w = None, None                                                    # pending branch and (Gemma) its norm weight
         for i in range(cfg["num_hidden_layers"]):
             p = f"model.layers.{i}."
-            h, x = self._add_rmsnorm(h, delta, P[p + "input_layernorm.weight"])
+            h, x = self._add_rmsnorm(h, delta, P[p + "input_layernorm.weight"], delta_w)
             q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
-            if self.gemma:                                                             # per-head norm of q and k
-                q = self._norm(q.view(T, nh, D), P[p + "self_attn.q_norm.weight"]).view(T, nh * D)
-                k = self._norm(k.view(T, nkv, D), P[p + "self_attn.k_norm.weight"]).view(T, nkv * D)
             self._rope_kv(q, k, v, positions, i)                                       # q in place, k/v into the caches
             Kc, Vc = self.k_cache[i][:, :S], self.v_cache[i][:, :S]                    # [nkv, S, D]
-            # grouped-query attention as one batched matmul per KV head (no expanded copies of K/V)
-            qg = q.view(T, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, T * rep, D)
-            att = torch.bmm(qg, Kc.transpose(1, 2)) * scale                            # bf16 scores, scaled in bf16
-            att = att.view(nkv, T, rep, S).masked_fill(blocked[self.types[i]], float("-inf"))
-            att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype).view(nkv, T * rep, S)
-            ctx = torch.bmm(att, Vc).view(nkv, T, rep, D).permute(1, 0, 2, 3).reshape(T, nh * D)
+            if self.fused_prompt_attention and T > 16:
+                # opt-in for prompts: the library's fused attention (fp32 scores and softmax inside; no [T, S] score
+                # tensor in memory).  It skips the spec's bf16 rounding of scores and probabilities; on a small model the
+                # prefill logits then sit 7e-3 (rel-L2) from the spec against 2e-3 for a change of accumulation order,
+                # which is why it is off by default.
+                ctx = F.scaled_dot_product_attention(q.view(1, T, nh, D).transpose(1, 2), Kc.unsqueeze(0), Vc.unsqueeze(0),
+                                                     attn_mask=allowed_of[self.types[i]], scale=scale, enable_gqa=True)
+                ctx = ctx.transpose(1, 2).reshape(T, nh * D)
+            else:
+                # grouped-query attention as one batched matmul per KV head (no expanded copies of K/V)
+                qg = q.view(T, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, T * rep, D)
+                att = torch.bmm(qg, Kc.transpose(1, 2)) * scale                        # bf16 scores, scaled in bf16
+                att = att.view(nkv, T, rep, S).masked_fill(blocked[self.types[i]], float("-inf"))
+                att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype).view(nkv, T * rep, S)
+                ctx = torch.bmm(att, Vc).view(nkv, T, rep, D).permute(1, 0, 2, 3).reshape(T, nh * D)
             o = self._row_parallel(self.lin[(i, "self_attn.o_proj")], ctx)
             if self.gemma:                                                             # the branch is normalised before it joins
-                o = self._norm(o, P[p + "post_attention_layernorm.weight"])
-                h, x = self._add_rmsnorm(h, o, P[p + "pre_feedforward_layernorm.weight"])
+                h, x = self._add_rmsnorm(h, o, P[p + "pre_feedforward_layernorm.weight"], P[p + "post_attention_layernorm.weight"])
             else:
                 h, x = self._add_rmsnorm(h, o, P[p + "post_attention_layernorm.weight"])
             g, u = self.gate_up[i](x)
             delta = self._row_parallel(self.lin[(i, "mlp.down_proj")], self._swiglu(g, u))
             if self.gemma:
-                delta = self._norm(delta, P[p + "post_feedforward_layernorm.weight"])
-        h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"])
+                delta_w = P[p + "post_feedforward_layernorm.weight"]
+        h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"], delta_w)
         head = P["model.embed_tokens.weight"] if self.gemma else P["lm_head.weight"]   # Gemma ties the head
         return F.linear(x, head).unsqueeze(0)                                          # [1, T, V]
 

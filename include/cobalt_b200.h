@@ -173,14 +173,19 @@ int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_hos
  * 667-774).  All tensors bf16.
  *   cobalt_add_rmsnorm : h_out = h + delta (delta, h_out may be NULL); rows [T, H] row-major;
  *                        flavor 0 (Llama): y = w * bf16(h_out * rsqrt(mean(h_out^2) + eps));
- *                        flavor 1 (Gemma): y = bf16(h_out * rsqrt(mean(h_out^2) + eps) * (1 + w)).
+ *                        flavor 1 (Gemma): y = bf16(h_out * rsqrt(mean(h_out^2) + eps) * (1 + w)); with w_branch (may be
+ *                        NULL) delta is first normalised the same way with (1 + w_branch) - the norm Gemma-3 applies to a
+ *                        branch before it joins the residual.
  *   cobalt_rope_kv     : rotates q [T, n_heads*D] in place; rotates k and copies v [T, n_kv_heads*D] into the caches
- *                        [n_kv_heads][max_ctx][D] at positions[t]; inv_freq fp32 [D/2]; cos/sin rounded to bf16.
+ *                        [n_kv_heads][max_ctx][D] at positions[t]; inv_freq fp32 [D/2]; cos/sin rounded to bf16.  With
+ *                        q_norm_w / k_norm_w (bf16 [D], both or neither) q and k first get Gemma-3's per-head norm
+ *                        bf16(x * rsqrt(mean_D(x^2) + eps) * (1 + w)) (src/cobaltkernel/ref_gemma3.py:181-185).
  *   cobalt_swiglu      : out = act(gate) * up over n elements; act 0 = SiLU, act 1 = GELU (tanh approximation). */
 int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,
-                       int flavor, void* stream);
+                       int flavor, const void* w_branch, void* stream);
 int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positions, const float* inv_freq, void* k_cache,
-                   void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, void* stream);
+                   void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, const void* q_norm_w,
+                   const void* k_norm_w, float eps, void* stream);
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream);
 
 /* All-reduce (sum) of the fp32 partial outputs of a row-parallel layer over peer memory, for tensor-parallel decode
