@@ -241,6 +241,19 @@ class CobaltDecoder:
                 ctx = F.scaled_dot_product_attention(q.view(1, T, nh, D).transpose(1, 2), Kc.unsqueeze(0), Vc.unsqueeze(0),
                                                      attn_mask=allowed_of[self.types[i]], scale=scale, enable_gqa=True)
                 ctx = ctx.transpose(1, 2).reshape(T, nh * D)
+            elif T > 64:
+                # prompts: one KV head at a time, so that its [T * rep, S] scores (bf16), probabilities (fp32, then bf16)
+                # stay in the L2 cache between the element-wise passes; same arithmetic as below
+                ctx = torch.empty(T, nkv, rep, D, dtype=q.dtype, device=q.device)
+                q4 = q.view(T, nkv, rep, D)
+                blk = blocked[self.types[i]][0]                                        # [T, 1, S]
+                for hk in range(nkv):
+                    att = torch.mm(q4[:, hk].reshape(T * rep, D), Kc[hk].t())
+                    att.mul_(scale)
+                    att.view(T, rep, S).masked_fill_(blk, float("-inf"))
+                    pr = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
+                    ctx[:, hk] = torch.mm(pr, Vc[hk]).view(T, rep, D)
+                ctx = ctx.view(T, nh * D)
             else:
                 # grouped-query attention as one batched matmul per KV head (no expanded copies of K/V)
                 qg = q.view(T, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, T * rep, D)
