@@ -585,6 +585,42 @@ int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t
     return cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
+size_t cobalt_attn_decode_scratch_bytes(int n_heads, int head_dim, int max_ctx) {
+    if (n_heads <= 0 || head_dim <= 0 || max_ctx <= 0) return 0;
+    const size_t chunks = ((size_t)max_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    return round_up((size_t)n_heads * max_ctx * 4, 256) + round_up((size_t)n_heads * chunks * 8, 256) +
+           round_up(chunks * n_heads * head_dim * 4, 256);
+}
+
+int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions, void* scratch,
+                       size_t scratch_bytes, void* out, int n_heads, int n_kv_heads, int head_dim, int max_ctx, int window,
+                       float scale, void* stream) {
+    if (!q || !k_cache || !v_cache || !positions || !scratch || !out) return COBALT_EINVAL;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads / n_kv_heads > ATTN_MAX_REP) return COBALT_EINVAL;
+    if (head_dim < 64 || head_dim > 256 || head_dim % 64 != 0 || max_ctx <= 0) return COBALT_EINVAL;
+    if (((uintptr_t)k_cache & 3) || ((uintptr_t)q & 3) || ((uintptr_t)scratch & 255)) return COBALT_EINVAL;
+    const int chunks = (max_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    if (chunks > ATTN_MAX_CHUNKS) return COBALT_ETOOBIG;
+    if (scratch_bytes < cobalt_attn_decode_scratch_bytes(n_heads, head_dim, max_ctx)) return COBALT_ESCRATCH;
+    int sms = 0;
+    int rc = device_info(&sms);
+    if (rc) return rc;
+    const int rep = n_heads / n_kv_heads;
+    float* att = (float*)scratch;
+    float* stat = (float*)((uint8_t*)scratch + round_up((size_t)n_heads * max_ctx * 4, 256));
+    float* part = (float*)((uint8_t*)stat + round_up((size_t)n_heads * chunks * 8, 256));
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid((unsigned)chunks, (unsigned)n_kv_heads);
+    attn_scores_kernel<<<grid, 256, 0, st>>>((const uint16_t*)q, (const uint16_t*)k_cache, (const long long*)positions, att, stat,
+                                             rep, head_dim, max_ctx, window, scale);
+    attn_context_kernel<<<grid, 256, 0, st>>>(att, stat, (const uint16_t*)v_cache, (const long long*)positions, part, rep,
+                                              head_dim, max_ctx, window, n_heads);
+    const int n = n_heads * head_dim;
+    attn_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, (const long long*)positions, (uint16_t*)out, n, chunks,
+                                                                     window);
+    return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+}
+
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream) {
     if (!gate || !up || !out || n <= 0 || act < 0 || act > 1) return COBALT_EINVAL;
     int sms = 0;

@@ -1,5 +1,5 @@
 // Small fused kernels around the compressed linears of a decoder block: residual add + RMSNorm,
-// RoPE + KV-cache append, SwiGLU / GeGLU.  They follow the dtype policy of the reference's
+// RoPE + KV-cache append, SwiGLU / GeGLU, single-token attention over the KV cache.  They follow the dtype policy of the reference's
 // executable specs (src/cobaltkernel/ref_llama.py:82-97, 139-143; src/cobaltkernel/ref_gemma3.py:138-143, 173-174,
 // 225-228): every intermediate that the spec holds in a bf16 tensor is rounded to bf16 here as
 // well, so that results agree with the spec up to the summation order of the mean.
@@ -160,6 +160,174 @@ __global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* ou
         a = 0.5f * x * (1.0f + tanhf(inner));
     }
     out[i] = float_to_bf16(bf16_round(a) * bf16_to_float(u[i]));
+}
+
+// ----------------------------------------------------------------------------- single-token attention
+// Grouped-query attention of ONE new token over the KV caches [n_kv][max_ctx][D], with the rounding points of the
+// reference's executable spec (src/cobaltkernel/ref_llama.py:117-137): scores = bf16(q . k) (fp32 sum), times the scale
+// rounded to bf16, softmax in fp32 over the allowed slots, probabilities rounded to bf16, context = bf16(sum p * v).
+// The number of slots comes from positions[0] on the device, so a captured graph does the work of the current length.
+// Three small kernels over (slot chunk, KV head) so that every SM takes part:
+//   1. scores of a chunk of 64 slots into att [n_heads][max_ctx] (fp32 holding bf16 values) + the chunk's max and
+//      sum of exp per head;
+//   2. global max / sum from the chunk statistics (a few dozen values), probabilities of the chunk, partial context
+//      [chunk][n_heads][D] in fp32;
+//   3. partial contexts added in chunk order, rounded to bf16.
+// They are launched plainly: with programmatic serialisation their CTAs were scheduled early only to wait, and the
+// three took 22.5 us instead of 19.2 us per layer.
+constexpr int ATTN_MAX_REP = 8;            // query heads per KV head
+constexpr int ATTN_CHUNK = 64;             // cache slots per CTA
+constexpr int ATTN_MAX_CHUNKS = 1024;      // max_ctx <= 65536
+
+__device__ __forceinline__ bool attn_allowed(int s, long long pos, int window, int max_ctx) {
+    return s < max_ctx && s <= pos && (window <= 0 || s > pos - window);
+}
+
+// grid (chunks, n_kv), block 256: warp w takes slots s0 + w + 8 i; lane holds D/32 contiguous dims (D % 64 == 0, D <= 256)
+__global__ void __launch_bounds__(256) attn_scores_kernel(const uint16_t* q, const uint16_t* k_cache, const long long* positions,
+                                                          float* att, float* chunk_stat, int rep, int D, int max_ctx, int window,
+                                                          float scale) {
+    __shared__ float sc[ATTN_MAX_REP][ATTN_CHUNK];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kvh = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
+    const long long pos = positions[0];
+    const int s0 = chunk * ATTN_CHUNK;
+    float* stat = chunk_stat + ((size_t)(kvh * rep) * nchunks + chunk) * 2;     // [head][chunk][max, sum]
+    if (s0 > pos || (window > 0 && s0 + ATTN_CHUNK - 1 <= pos - window)) {      // nothing allowed in this chunk
+        if (threadIdx.x < rep) { stat[(size_t)threadIdx.x * nchunks * 2] = -INFINITY; stat[(size_t)threadIdx.x * nchunks * 2 + 1] = 0.0f; }
+        return;
+    }
+    const int per = D / 32;
+    uint32_t kraw[ATTN_CHUNK / 8][4], qraw[ATTN_MAX_REP][4];
+    bool ok[ATTN_CHUNK / 8];
+#pragma unroll
+    for (int i = 0; i < ATTN_CHUNK / 8; ++i) {                          // all loads first: their latencies overlap
+        const int s = s0 + warp + 8 * i;
+        ok[i] = attn_allowed(s, pos, window, max_ctx);
+        const uint32_t* kp = reinterpret_cast<const uint32_t*>(k_cache + ((size_t)kvh * max_ctx + (ok[i] ? s : 0)) * D + lane * per);
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) kraw[i][e2] = (ok[i] && e2 * 2 < per) ? __ldg(kp + e2) : 0u;
+    }
+#pragma unroll
+    for (int h = 0; h < ATTN_MAX_REP; ++h) {
+        const uint32_t* qp = reinterpret_cast<const uint32_t*>(q + ((size_t)kvh * rep + (h < rep ? h : 0)) * D + lane * per);
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) qraw[h][e2] = (h < rep && e2 * 2 < per) ? __ldg(qp + e2) : 0u;
+    }
+#pragma unroll
+    for (int h = 0; h < ATTN_MAX_REP; ++h) {
+        if (h >= rep) break;
+        float acc[ATTN_CHUNK / 8];
+#pragma unroll
+        for (int i = 0; i < ATTN_CHUNK / 8; ++i) {
+            acc[i] = 0.0f;
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+                acc[i] = fmaf(__uint_as_float(qraw[h][e2] << 16), __uint_as_float(kraw[i][e2] << 16), acc[i]);
+                acc[i] = fmaf(__uint_as_float(qraw[h][e2] & 0xFFFF0000u), __uint_as_float(kraw[i][e2] & 0xFFFF0000u), acc[i]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < ATTN_CHUNK / 8; ++i) acc[i] += __shfl_xor_sync(0xFFFFFFFFu, acc[i], o);
+        if (lane < ATTN_CHUNK / 8) {                                    // lane i keeps slot i of this warp
+            float mine = 0.0f;
+            bool w_ok = false;
+#pragma unroll
+            for (int i = 0; i < ATTN_CHUNK / 8; ++i)
+                if (lane == i) { mine = acc[i]; w_ok = ok[i]; }
+            const float v = w_ok ? bf16_round(bf16_round(mine) * scale) : -INFINITY;
+            sc[h][warp + 8 * lane] = v;
+            if (w_ok) att[((size_t)kvh * rep + h) * max_ctx + s0 + warp + 8 * lane] = v;
+        }
+    }
+    __syncthreads();
+    if (warp < rep) {                                                   // warp h: max and sum of exp of head h over the chunk
+        const float a = sc[warp][lane], b = sc[warp][lane + 32];
+        float m = fmaxf(a, b);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        float z = (a == -INFINITY ? 0.0f : expf(a - m)) + (b == -INFINITY ? 0.0f : expf(b - m));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xFFFFFFFFu, z, o);
+        if (lane == 0) { stat[(size_t)warp * nchunks * 2] = m; stat[(size_t)warp * nchunks * 2 + 1] = z; }
+    }
+}
+
+// grid (chunks, n_kv), block 256 = 8 warps x 32 dims: thread (w, l) adds the slots s0 + w + 8 i of dims l, l+32, ... ;
+// partial context of the chunk -> part [chunk][n_heads][D]
+__global__ void __launch_bounds__(256) attn_context_kernel(const float* att, const float* chunk_stat, const uint16_t* v_cache,
+                                                           const long long* positions, float* part, int rep, int D, int max_ctx,
+                                                           int window, int n_heads) {
+    __shared__ float gm[ATTN_MAX_REP], gz[ATTN_MAX_REP];
+    __shared__ float pr[ATTN_MAX_REP][ATTN_CHUNK];
+    __shared__ float red[8][ATTN_MAX_REP][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kvh = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
+    const long long pos = positions[0];
+    const int s0 = chunk * ATTN_CHUNK;
+    float* mine = part + ((size_t)chunk * n_heads + (size_t)kvh * rep) * D;
+    if (s0 > pos || (window > 0 && s0 + ATTN_CHUNK - 1 <= pos - window)) return;   // the combine step skips chunks outside the range
+    if (warp < rep) {                                                   // global max and sum of head `warp` from the chunk statistics
+        const float* st = chunk_stat + (size_t)(kvh * rep + warp) * nchunks * 2;
+        float m = -INFINITY;
+        for (int c = lane; c < nchunks; c += 32) m = fmaxf(m, st[2 * c]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        float z = 0.0f;
+        for (int c = lane; c < nchunks; c += 32) { const float mc = st[2 * c]; if (mc != -INFINITY) z += st[2 * c + 1] * expf(mc - m); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xFFFFFFFFu, z, o);
+        if (lane == 0) { gm[warp] = m; gz[warp] = z; }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rep * ATTN_CHUNK; i += 256) {        // probabilities of the chunk, rounded to bf16
+        const int h = i / ATTN_CHUNK, j = i - h * ATTN_CHUNK, s = s0 + j;
+        pr[h][j] = attn_allowed(s, pos, window, max_ctx) ? bf16_round(expf(att[((size_t)kvh * rep + h) * max_ctx + s] - gm[h]) / gz[h]) : 0.0f;
+    }
+    __syncthreads();
+    for (int d0 = 0; d0 < D; d0 += 32) {
+        float vv[ATTN_CHUNK / 8];
+#pragma unroll
+        for (int i = 0; i < ATTN_CHUNK / 8; ++i) {
+            const int s = s0 + warp + 8 * i;
+            vv[i] = attn_allowed(s, pos, window, max_ctx) ? bf16_to_float(v_cache[((size_t)kvh * max_ctx + s) * D + d0 + lane]) : 0.0f;
+        }
+#pragma unroll
+        for (int h = 0; h < ATTN_MAX_REP; ++h) {
+            if (h >= rep) break;
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < ATTN_CHUNK / 8; ++i) a = fmaf(pr[h][warp + 8 * i], vv[i], a);
+            red[warp][h][lane] = a;
+        }
+        __syncthreads();
+        if (warp < rep) {
+            float a = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) a += red[w][warp][lane];
+            mine[(size_t)warp * D + d0 + lane] = a;
+        }
+        __syncthreads();
+    }
+}
+
+// grid ceil(n_heads * D / 256): out[h][d] = bf16( sum over chunks, in order, of part[chunk][h][d] ) for the chunks in range;
+// the next kernel (the o projection's GEMV) may start its prologue at once
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float* part, const long long* positions, uint16_t* out, int n, int nchunks,
+                                                           int window) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    const long long pos = positions[0];
+    int c1 = (int)(pos / ATTN_CHUNK) + 1;
+    if (c1 > nchunks) c1 = nchunks;
+    int c0 = 0;
+    if (window > 0 && pos - window + 1 > 0) c0 = (int)((pos - window + 1) / ATTN_CHUNK);
+    float a = 0.0f;
+    for (int c = c0; c < c1; ++c) a += part[(size_t)c * n + i];
+    out[i] = float_to_bf16(a);
 }
 
 // ----------------------------------------------------------------------------- all-reduce over peer memory

@@ -146,6 +146,9 @@ class CobaltDecoder:
         if self.gemma:
             self.embed_scale = torch.tensor(float(cfg["hidden_size"]) ** 0.5, dtype=torch.bfloat16, device=device)
         self.kv_pos = torch.arange(max_ctx, device=device)
+        need = _lib.load().cobalt_attn_decode_scratch_bytes(self.nh, D, max_ctx)
+        self.att_scratch = torch.empty(need, dtype=torch.uint8, device=device) if self.nh // self.nkv <= 8 and D % 64 == 0 and D <= 256 \
+            and max_ctx <= 65536 else None
         self.tok = torch.zeros(1, dtype=torch.long, device=device)        # next token to feed
         self.pos = torch.zeros(1, dtype=torch.long, device=device)        # its position
         self.qkv = [FusedProjections([linears[(i, "self_attn.q_proj")], linears[(i, "self_attn.k_proj")],
@@ -186,6 +189,18 @@ class CobaltDecoder:
                                       self.nh, self.nkv, cfg["head_dim"], self.max_ctx, qn, kn, float(cfg["rms_norm_eps"]),
                                       torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_rope_kv", rc)
+
+    def _attn_one(self, q, positions, layer):
+        """Attention of one new token over cache slots 0..positions[0] (three small launches, length read on the device)."""
+        cfg = self.cfg
+        ctx = torch.empty_like(q)
+        window = int(cfg.get("sliding_window") or 0) if self.types[layer] == "sliding_attention" else 0
+        rc = self._lib.cobalt_attn_decode(q.data_ptr(), self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(),
+                                          positions.data_ptr(), self.att_scratch.data_ptr(), self.att_scratch.numel(), ctx.data_ptr(),
+                                          self.nh, self.nkv, cfg["head_dim"], self.max_ctx, window, self.scale,
+                                          torch.cuda.current_stream(self.dev).cuda_stream)
+        _lib.check("cobalt_attn_decode", rc)
+        return ctx
 
     def _row_parallel(self, lin, x):
         """o / down: the whole layer on one GPU; with tensor parallelism the sum over ranks of the local fp32 partials."""
@@ -233,7 +248,9 @@ class CobaltDecoder:
             q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
             self._rope_kv(q, k, v, positions, i)                                       # q in place, k/v into the caches
             Kc, Vc = self.k_cache[i][:, :S], self.v_cache[i][:, :S]                    # [nkv, S, D]
-            if self.fused_prompt_attention and T > 16:
+            if T == 1 and self.att_scratch is not None:
+                ctx = self._attn_one(q, positions, i)
+            elif self.fused_prompt_attention and T > 16:
                 # opt-in for prompts: the library's fused attention (fp32 scores and softmax inside; no [T, S] score
                 # tensor in memory).  It skips the spec's bf16 rounding of scores and probabilities; on a small model the
                 # prefill logits then sit 7e-3 (rel-L2) from the spec against 2e-3 for a change of accumulation order,

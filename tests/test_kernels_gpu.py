@@ -458,3 +458,43 @@ def test_peer_allreduce_wait_expires_cleanly():
     x = O.seeded_activation(1, 256, 4)
     Wb = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)
     check_output(mod(x.to(dev)), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nh,nkv,D,ctx,pos,window", [(32, 8, 128, 2304, 2047, 0), (32, 8, 128, 300, 0, 0), (16, 16, 64, 512, 511, 0),
+                                                     (32, 16, 128, 1024, 700, 256), (8, 1, 256, 200, 130, 0), (4, 2, 64, 130, 129, 70)])
+def test_attn_decode_matches_torch(nh, nkv, D, ctx, pos, window):
+    """Single-token attention over the KV cache against the same arithmetic in torch (rounding points of
+    src/cobaltkernel/ref_llama.py:117-137).  The two differ only in fp32 summation order, so outputs may differ
+    by a bf16 rounding step on a few elements: rel-L2 <= 2e-3, max-abs <= 2 % of the largest output."""
+    import torch.nn.functional as F
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(1234 + nh + ctx)
+    q = torch.randn(1, nh * D, generator=g).to(torch.bfloat16).to(dev)
+    kc = torch.randn(nkv, ctx, D, generator=g).to(torch.bfloat16).to(dev)
+    vc = torch.randn(nkv, ctx, D, generator=g).to(torch.bfloat16).to(dev)
+    positions = torch.tensor([pos], dtype=torch.long, device=dev)
+    need = lib.cobalt_attn_decode_scratch_bytes(nh, D, ctx)
+    scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(q)
+    scale = float(D) ** -0.5
+    rc = lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), positions.data_ptr(), scratch.data_ptr(), need, out.data_ptr(),
+                                nh, nkv, D, ctx, window, scale, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    rep = nh // nkv
+    qg = q.view(1, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, rep, D)
+    att = torch.bmm(qg, kc.transpose(1, 2)) * scale
+    kv_pos = torch.arange(ctx, device=dev)
+    allowed = kv_pos <= pos
+    if window:
+        allowed &= kv_pos > pos - window
+    att = att.masked_fill(~allowed[None, None, :], float("-inf"))
+    att = F.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
+    ref = torch.bmm(att, vc).reshape(1, nh * D)
+    torch.cuda.synchronize()
+    d = (out.float() - ref.float())
+    rel = float(d.norm() / ref.float().norm())
+    assert rel <= 2e-3, rel
+    assert float(d.abs().max()) <= 0.02 * float(ref.float().abs().max()), float(d.abs().max())
