@@ -611,9 +611,9 @@ int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
     float* part = (float*)((uint8_t*)stat + round_up((size_t)n_heads * chunks * 8, 256));
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 grid((unsigned)chunks, (unsigned)n_kv_heads);
-    attn_scores_kernel<<<grid, 256, 0, st>>>((const uint16_t*)q, (const uint16_t*)k_cache, (const long long*)positions, att, stat,
+    attn_scores_kernel<<<grid, ATTN_THREADS, 0, st>>>((const uint16_t*)q, (const uint16_t*)k_cache, (const long long*)positions, att, stat,
                                              rep, head_dim, max_ctx, window, scale);
-    attn_context_kernel<<<grid, 256, 0, st>>>(att, stat, (const uint16_t*)v_cache, (const long long*)positions, part, rep,
+    attn_context_kernel<<<grid, ATTN_THREADS, 0, st>>>(att, stat, (const uint16_t*)v_cache, (const long long*)positions, part, rep,
                                               head_dim, max_ctx, window, n_heads);
     const int n = n_heads * head_dim;
     attn_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, (const long long*)positions, (uint16_t*)out, n, chunks,

@@ -168,7 +168,7 @@ __global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* ou
 // rounded to bf16, softmax in fp32 over the allowed slots, probabilities rounded to bf16, context = bf16(sum p * v).
 // The number of slots comes from positions[0] on the device, so a captured graph does the work of the current length.
 // Three small kernels over (slot chunk, KV head) so that every SM takes part:
-//   1. scores of a chunk of 64 slots into att [n_heads][max_ctx] (fp32 holding bf16 values) + the chunk's max and
+//   1. scores of a chunk of slots into att [n_heads][max_ctx] (fp32 holding bf16 values) + the chunk's max and
 //      sum of exp per head;
 //   2. global max / sum from the chunk statistics (a few dozen values), probabilities of the chunk, partial context
 //      [chunk][n_heads][D] in fp32;
@@ -176,15 +176,17 @@ __global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* ou
 // They are launched plainly: with programmatic serialisation their CTAs were scheduled early only to wait, and the
 // three took 22.5 us instead of 19.2 us per layer.
 constexpr int ATTN_MAX_REP = 8;            // query heads per KV head
-constexpr int ATTN_CHUNK = 64;             // cache slots per CTA
+constexpr int ATTN_CHUNK = 128;            // cache slots per CTA
+constexpr int ATTN_WARPS = ATTN_CHUNK / 8; // every warp takes 8 slots of the chunk
+constexpr int ATTN_THREADS = ATTN_WARPS * 32;
 constexpr int ATTN_MAX_CHUNKS = 1024;      // max_ctx <= 65536
 
 __device__ __forceinline__ bool attn_allowed(int s, long long pos, int window, int max_ctx) {
     return s < max_ctx && s <= pos && (window <= 0 || s > pos - window);
 }
 
-// grid (chunks, n_kv), block 256: warp w takes slots s0 + w + 8 i; lane holds D/32 contiguous dims (D % 64 == 0, D <= 256)
-__global__ void __launch_bounds__(256) attn_scores_kernel(const uint16_t* q, const uint16_t* k_cache, const long long* positions,
+// grid (chunks, n_kv), block ATTN_THREADS: warp w takes slots s0 + w + ATTN_WARPS * i; lane holds D/32 contiguous dims (D % 64 == 0, D <= 256)
+__global__ void __launch_bounds__(ATTN_THREADS) attn_scores_kernel(const uint16_t* q, const uint16_t* k_cache, const long long* positions,
                                                           float* att, float* chunk_stat, int rep, int D, int max_ctx, int window,
                                                           float scale) {
     __shared__ float sc[ATTN_MAX_REP][ATTN_CHUNK];
@@ -198,11 +200,11 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const uint16_t* q, con
         return;
     }
     const int per = D / 32;
-    uint32_t kraw[ATTN_CHUNK / 8][4], qraw[ATTN_MAX_REP][4];
-    bool ok[ATTN_CHUNK / 8];
+    uint32_t kraw[8][4], qraw[ATTN_MAX_REP][4];
+    bool ok[8];
 #pragma unroll
-    for (int i = 0; i < ATTN_CHUNK / 8; ++i) {                          // all loads first: their latencies overlap
-        const int s = s0 + warp + 8 * i;
+    for (int i = 0; i < 8; ++i) {                          // all loads first: their latencies overlap
+        const int s = s0 + warp + ATTN_WARPS * i;
         ok[i] = attn_allowed(s, pos, window, max_ctx);
         const uint32_t* kp = reinterpret_cast<const uint32_t*>(k_cache + ((size_t)kvh * max_ctx + (ok[i] ? s : 0)) * D + lane * per);
 #pragma unroll
@@ -217,9 +219,9 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const uint16_t* q, con
 #pragma unroll
     for (int h = 0; h < ATTN_MAX_REP; ++h) {
         if (h >= rep) break;
-        float acc[ATTN_CHUNK / 8];
+        float acc[8];
 #pragma unroll
-        for (int i = 0; i < ATTN_CHUNK / 8; ++i) {
+        for (int i = 0; i < 8; ++i) {
             acc[i] = 0.0f;
 #pragma unroll
             for (int e2 = 0; e2 < 4; ++e2) {
@@ -230,39 +232,42 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const uint16_t* q, con
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-            for (int i = 0; i < ATTN_CHUNK / 8; ++i) acc[i] += __shfl_xor_sync(0xFFFFFFFFu, acc[i], o);
-        if (lane < ATTN_CHUNK / 8) {                                    // lane i keeps slot i of this warp
+            for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xFFFFFFFFu, acc[i], o);
+        if (lane < 8) {                                    // lane i keeps slot i of this warp
             float mine = 0.0f;
             bool w_ok = false;
 #pragma unroll
-            for (int i = 0; i < ATTN_CHUNK / 8; ++i)
+            for (int i = 0; i < 8; ++i)
                 if (lane == i) { mine = acc[i]; w_ok = ok[i]; }
             const float v = w_ok ? bf16_round(bf16_round(mine) * scale) : -INFINITY;
-            sc[h][warp + 8 * lane] = v;
-            if (w_ok) att[((size_t)kvh * rep + h) * max_ctx + s0 + warp + 8 * lane] = v;
+            sc[h][warp + ATTN_WARPS * lane] = v;
+            if (w_ok) att[((size_t)kvh * rep + h) * max_ctx + s0 + warp + ATTN_WARPS * lane] = v;
         }
     }
     __syncthreads();
     if (warp < rep) {                                                   // warp h: max and sum of exp of head h over the chunk
-        const float a = sc[warp][lane], b = sc[warp][lane + 32];
-        float m = fmaxf(a, b);
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < ATTN_CHUNK; j += 32) m = fmaxf(m, sc[warp][lane + j]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-        float z = (a == -INFINITY ? 0.0f : expf(a - m)) + (b == -INFINITY ? 0.0f : expf(b - m));
+        float z = 0.0f;
+#pragma unroll
+        for (int j = 0; j < ATTN_CHUNK; j += 32) { const float a = sc[warp][lane + j]; z += a == -INFINITY ? 0.0f : expf(a - m); }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xFFFFFFFFu, z, o);
         if (lane == 0) { stat[(size_t)warp * nchunks * 2] = m; stat[(size_t)warp * nchunks * 2 + 1] = z; }
     }
 }
 
-// grid (chunks, n_kv), block 256 = 8 warps x 32 dims: thread (w, l) adds the slots s0 + w + 8 i of dims l, l+32, ... ;
+// grid (chunks, n_kv), block ATTN_THREADS = ATTN_WARPS warps x 32 dims: thread (w, l) adds the slots s0 + w + ATTN_WARPS * i of dims l, l+32, ... ;
 // partial context of the chunk -> part [chunk][n_heads][D]
-__global__ void __launch_bounds__(256) attn_context_kernel(const float* att, const float* chunk_stat, const uint16_t* v_cache,
+__global__ void __launch_bounds__(ATTN_THREADS) attn_context_kernel(const float* att, const float* chunk_stat, const uint16_t* v_cache,
                                                            const long long* positions, float* part, int rep, int D, int max_ctx,
                                                            int window, int n_heads) {
     __shared__ float gm[ATTN_MAX_REP], gz[ATTN_MAX_REP];
     __shared__ float pr[ATTN_MAX_REP][ATTN_CHUNK];
-    __shared__ float red[8][ATTN_MAX_REP][32];
+    __shared__ float red[ATTN_WARPS][ATTN_MAX_REP][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
     const long long pos = positions[0];
@@ -282,16 +287,16 @@ __global__ void __launch_bounds__(256) attn_context_kernel(const float* att, con
         if (lane == 0) { gm[warp] = m; gz[warp] = z; }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < rep * ATTN_CHUNK; i += 256) {        // probabilities of the chunk, rounded to bf16
+    for (int i = threadIdx.x; i < rep * ATTN_CHUNK; i += ATTN_THREADS) {        // probabilities of the chunk, rounded to bf16
         const int h = i / ATTN_CHUNK, j = i - h * ATTN_CHUNK, s = s0 + j;
         pr[h][j] = attn_allowed(s, pos, window, max_ctx) ? bf16_round(expf(att[((size_t)kvh * rep + h) * max_ctx + s] - gm[h]) / gz[h]) : 0.0f;
     }
     __syncthreads();
     for (int d0 = 0; d0 < D; d0 += 32) {
-        float vv[ATTN_CHUNK / 8];
+        float vv[8];
 #pragma unroll
-        for (int i = 0; i < ATTN_CHUNK / 8; ++i) {
-            const int s = s0 + warp + 8 * i;
+        for (int i = 0; i < 8; ++i) {
+            const int s = s0 + warp + ATTN_WARPS * i;
             vv[i] = attn_allowed(s, pos, window, max_ctx) ? bf16_to_float(v_cache[((size_t)kvh * max_ctx + s) * D + d0 + lane]) : 0.0f;
         }
 #pragma unroll
@@ -299,14 +304,14 @@ __global__ void __launch_bounds__(256) attn_context_kernel(const float* att, con
             if (h >= rep) break;
             float a = 0.0f;
 #pragma unroll
-            for (int i = 0; i < ATTN_CHUNK / 8; ++i) a = fmaf(pr[h][warp + 8 * i], vv[i], a);
+            for (int i = 0; i < 8; ++i) a = fmaf(pr[h][warp + ATTN_WARPS * i], vv[i], a);
             red[warp][h][lane] = a;
         }
         __syncthreads();
         if (warp < rep) {
             float a = 0.0f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) a += red[w][warp][lane];
+            for (int w = 0; w < ATTN_WARPS; ++w) a += red[w][warp][lane];
             mine[(size_t)warp * D + d0 + lane] = a;
         }
         __syncthreads();
