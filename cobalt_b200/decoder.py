@@ -113,17 +113,6 @@ def random_dense_params(cfg: dict, device, seed: int = 7):
     return P
 
 
-def _rms_norm(x, w, eps):
-    h = x.float()
-    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
-    return w * h.to(x.dtype)
-
-
-def _rotate_half(x):
-    d = x.shape[-1] // 2
-    return torch.cat((-x[..., d:], x[..., :d]), dim=-1)
-
-
 class CobaltDecoder:
     """Batch-1 decoder over compressed projections.  ``linears[(layer, proj)]`` are
     ``CobaltSparseLinear`` modules; ``dense`` holds embedding / norms / lm_head."""
@@ -171,11 +160,6 @@ class CobaltDecoder:
                                           torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_add_rmsnorm", rc)
         return h_out, y
-
-    def _norm(self, x, w):
-        """Norm only (no residual); rows are the leading dimensions of ``x``, the last one is normalised."""
-        H = x.shape[-1]
-        return self._add_rmsnorm(x.reshape(-1, H), None, w)[1].view(x.shape)
 
     def _rope_kv(self, q, k, v, positions, layer):
         cfg = self.cfg
