@@ -23,6 +23,7 @@ bool g_dev_known[MAX_DEVICES];
 int g_tune_tiles_per_split = 0;     // 0 = heuristic
 int g_tune_gemv_stages = 0;
 int g_tune_gemm_stages = 0;
+int g_tune_gemv_mode = 0;           // 0 = heuristic, 1 = CTAs hold whole row blocks, 2 = balanced words
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -65,7 +66,9 @@ int check_io(const void* x, int64_t ldx, const void* y, int64_t ldy, int M, int 
 // ----------------------------------------------------------------------------- GEMV configuration
 struct GemvCfg {
     int stages, mt, grid;
-    uint32_t slot, nib, total_warps;
+    bool xs;                           // activations staged in shared memory
+    bool aligned;                      // every CTA holds whole row blocks
+    uint32_t slot, xs_bytes, total_warps, part_q, part_r;
     size_t smem, counters_off, partials_off, total;
 };
 
@@ -79,32 +82,43 @@ GemvGeom geom_of(const CobaltMat* w) {
     return g;
 }
 
-int gemv_config(const GemvGeom& g, int M, int num_sms, GemvCfg* c) {
+int gemv_config(const GemvGeom& g, int N, int M, int num_sms, GemvCfg* c) {
     const int RB = g.RB, CT = g.CT;
     c->mt = M > 8 ? 2 : 1;
     c->slot = (uint32_t)round_up((size_t)g.max_tile_bytes + 32, 128);
-    c->nib = g.bits == 4 ? 0u : (uint32_t)round_up((size_t)g.max_tile_nnz / 2 + 64, 128);
     const size_t fixed = GEMV_LUT_BYTES + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES + gemv_red_bytes(c->mt) + 64;
-    int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : GEMV_MAX_STAGES;
+    // Two ring slots per warp keep one tile in flight behind the one being decoded.  The activations are staged in
+    // shared memory when they fit beside such a ring (always for one token); what is left goes to deeper rings.
+    const size_t xs_want = c->mt == 1 ? round_up((size_t)M * N * 2 + 64, 256) : 0;
+    c->xs = xs_want != 0 && fixed + xs_want + (size_t)GEMV_WARPS * 2 * c->slot <= SMEM_LIMIT;
+    c->xs_bytes = c->xs ? (uint32_t)xs_want : 0u;
+    int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : 3;
     if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
-    while (stages > 1 && fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) --stages;
-    if (fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib) > SMEM_LIMIT) return COBALT_EINVAL;
+    while (stages > 1 && fixed + c->xs_bytes + (size_t)GEMV_WARPS * stages * c->slot > SMEM_LIMIT) --stages;
+    if (fixed + c->xs_bytes + (size_t)GEMV_WARPS * stages * c->slot > SMEM_LIMIT) return COBALT_EINVAL;
     c->stages = stages;
-    c->smem = fixed + (size_t)GEMV_WARPS * ((size_t)stages * c->slot + c->nib);
-    // persistent grid: one CTA per SM.  When there is at most one tile per warp, the grid is chosen so that
-    // every CTA holds whole row blocks (their parts then meet in shared memory instead of global scratch).
+    c->smem = fixed + c->xs_bytes + (size_t)GEMV_WARPS * stages * c->slot;
+    // Persistent grid, at most one CTA per SM.  Preferred: every CTA holds whole row blocks, so that no partial sums
+    // cross CTAs - the grid is the smallest one that reaches the minimal number of row blocks per CTA.  When that
+    // leaves more than 15 % of the machine idle (few, long row blocks), the words are balanced over all SMs instead
+    // and the blocks that straddle CTAs are exchanged through global scratch.
     const long tiles = (long)RB * CT;
-    long grid = num_sms;
-    if (tiles <= (long)num_sms * GEMV_WARPS && CT <= GEMV_WARPS) {
-        for (long r = 8 / CT > 0 ? 8 / CT : 1; r * CT <= GEMV_WARPS; ++r)      // r row blocks per CTA; start with half the warps busy
-            if (RB % r == 0 && RB / r <= num_sms) { grid = RB / r; break; }
-    }
-    if (g_tune_tiles_per_split > 0) grid = g_tune_tiles_per_split;                  // tuning key 0 overrides the grid size
+    const long per_cta = (RB + num_sms - 1) / num_sms;                  // row blocks of the busiest CTA
+    long grid = (RB + per_cta - 1) / per_cta;
+    bool aligned = (double)RB / ((double)per_cta * num_sms) >= 0.85;
+    if (g_tune_gemv_mode == 1) aligned = true;
+    if (g_tune_gemv_mode == 2) aligned = false;
+    if (!aligned) grid = num_sms;
+    if (g_tune_tiles_per_split > 0) { grid = g_tune_tiles_per_split; aligned = false; }   // tuning key 0 overrides the grid size
     if (grid > tiles) grid = tiles;
     if (grid < 1) grid = 1;
     c->grid = (int)grid;
+    c->aligned = aligned;
+    const unsigned long units = aligned ? (unsigned long)RB : (unsigned long)tiles * TILE_WORDS;
+    c->part_q = (uint32_t)(units / (unsigned long)grid);
+    c->part_r = (uint32_t)(units % (unsigned long)grid);
     c->total_warps = (uint32_t)(grid * GEMV_WARPS);
-    if ((unsigned long long)(tiles + 1) * c->total_warps >= (1ull << 32)) return COBALT_ETOOBIG;   // 32-bit partition arithmetic
+    if ((unsigned long long)(tiles + 1) * TILE_WORDS * (unsigned long long)grid >= (1ull << 32)) return COBALT_ETOOBIG;   // 32-bit partition arithmetic
     c->counters_off = SCRATCH_STATUS_BYTES;
     // the counters of both kernels live in the first 64 KB behind the status word and their partial sums behind
     // that, so that one zero-initialised buffer can serve GEMV and GEMM calls in any order (each kernel returns
@@ -115,13 +129,13 @@ int gemv_config(const GemvGeom& g, int M, int num_sms, GemvCfg* c) {
     return COBALT_OK;
 }
 
-template <int BITS, int MT>
+template <int BITS, int MT, bool XS>
 int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
     static bool configured[MAX_DEVICES];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(gemv_mma_kernel<BITS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_mma_kernel<BITS, MT, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
             return COBALT_ELAUNCH;
         configured[dev] = true;
     }
@@ -138,7 +152,7 @@ int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<BITS, MT>, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<BITS, MT, XS>, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 // ----------------------------------------------------------------------------- GEMM configuration
@@ -240,7 +254,7 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     int rc = device_info(&sms);
     if (rc) return rc;
     GemvCfg c;
-    rc = gemv_config(g, M, sms, &c);
+    rc = gemv_config(g, w[0]->N, M, sms, &c);
     if (rc) return rc;
     if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
     cudaStream_t st = (cudaStream_t)stream;
@@ -268,22 +282,31 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.x = (const uint16_t*)x; P.ldx = ldx;
     P.M = M;
     P.stages = c.stages;
-    P.slot_bytes = c.slot; P.nib_bytes = c.nib;
+    P.slot_bytes = c.slot; P.xs_bytes = c.xs_bytes;
     P.total_warps = c.total_warps;
+    P.aligned = c.aligned ? 1 : 0;
+    P.part_q = c.part_q; P.part_r = c.part_r;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);
+    if (c.mt == 1 && c.xs) {
+        switch (g.bits) {
+            case 2: return launch_gemv<2, 1, true>(P, c, st);
+            case 3: return launch_gemv<3, 1, true>(P, c, st);
+            default: return launch_gemv<4, 1, true>(P, c, st);
+        }
+    }
     if (c.mt == 1) {
         switch (g.bits) {
-            case 2: return launch_gemv<2, 1>(P, c, st);
-            case 3: return launch_gemv<3, 1>(P, c, st);
-            default: return launch_gemv<4, 1>(P, c, st);
+            case 2: return launch_gemv<2, 1, false>(P, c, st);
+            case 3: return launch_gemv<3, 1, false>(P, c, st);
+            default: return launch_gemv<4, 1, false>(P, c, st);
         }
     }
     switch (g.bits) {
-        case 2: return launch_gemv<2, 2>(P, c, st);
-        case 3: return launch_gemv<3, 2>(P, c, st);
-        default: return launch_gemv<4, 2>(P, c, st);
+        case 2: return launch_gemv<2, 2, false>(P, c, st);
+        case 3: return launch_gemv<3, 2, false>(P, c, st);
+        default: return launch_gemv<4, 2, false>(P, c, st);
     }
 }
 
@@ -320,6 +343,7 @@ int cobalt_set_tuning(int key, int value) {
         case 0: g_tune_tiles_per_split = value; return COBALT_OK;
         case 1: g_tune_gemv_stages = value; return COBALT_OK;
         case 2: g_tune_gemm_stages = value; return COBALT_OK;
+        case 3: g_tune_gemv_mode = value; return COBALT_OK;
         default: return COBALT_EINVAL;
     }
 }
@@ -329,7 +353,7 @@ size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M) {
     if (check_mat(w) != COBALT_OK || M <= 0 || M > MAX_GEMV_M) return 0;
     if (device_info(&sms) != COBALT_OK) return 0;
     GemvCfg c;
-    if (gemv_config(geom_of(w), M, sms, &c) != COBALT_OK) return 0;
+    if (gemv_config(geom_of(w), w->N, M, sms, &c) != COBALT_OK) return 0;
     return c.total;
 }
 
@@ -354,7 +378,7 @@ int cobalt_gemv_static(const CobaltMat* w, const void* x, int64_t ldx, void* y, 
     rc = device_info(&sms);
     if (rc) return rc;
     GemvCfg c;
-    rc = gemv_config(geom_of(w), M, sms, &c);
+    rc = gemv_config(geom_of(w), w->N, M, sms, &c);
     if (rc) return rc;
     if (c.total > (size_t)COBALT_STATIC_SCRATCH_BYTES) return COBALT_ETOOBIG;
     int dev = 0;
@@ -383,7 +407,7 @@ size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, in
     int sms = 0;
     if (device_info(&sms) != COBALT_OK) return 0;
     GemvCfg c;
-    if (gemv_config(g, M, sms, &c) != COBALT_OK) return 0;
+    if (gemv_config(g, w[0]->N, M, sms, &c) != COBALT_OK) return 0;
     return c.total;
 }
 

@@ -223,6 +223,7 @@ constexpr LutTable make_expand_lut() {
 // ----------------------------------------------------------------------------- per-segment constants
 struct SegParams {
     float s, z;            // fp32 values of the stored fp16 scale / zero
+    uint32_t zq;           // zero point as an integer (fast path)
     uint32_t zb24;         // zero point << 24 (fast path)
     uint32_t zb2;          // bf16x2 {-(128+z), -(128+z)}: added, so that no per-use negation is needed
     uint32_t shi2, slo2;   // bf16x2 {s_hi, s_hi}, {s_lo, s_lo}
@@ -239,6 +240,7 @@ CB_HD SegParams make_seg_params(uint32_t sz_bits, int bits, bool has_col_scale) 
     bool s_ok = (f2u(p.s) & 0x7F800000u) != 0x7F800000u;   // finite
     p.fast = z_ok && s_ok && !has_col_scale;
     uint32_t zq = p.fast ? (uint32_t)zi : 0u;
+    p.zq = zq;
     p.zb24 = zq << 24;
     uint32_t zb = 0xC300u | zq;                            // sign bit set
     p.zb2 = zb | (zb << 16);
@@ -349,6 +351,71 @@ CB_HD void decode32_fast(uint32_t m, uint32_t w0, uint32_t w1, uint32_t w2, uint
                          LutFn lut, uint32_t out[16]) {
     decode16_fast(m & 0xFFFFu, w0, w1, w2, w3, p, lut, out);
     decode16_fast(m >> 16, w0, w1, w2, w3, p, lut, out + 8);
+}
+
+
+// ----------------------------------------------------------------------------- 8 positions, any bit width
+// One mask byte of a fast segment, decoded straight from the `BITS`-wide code stream (no re-pack to
+// nibbles).  `w0` holds the codes of this byte's survivors from bit 0 upwards (8 * BITS bits are looked
+// at).  code_view() turns them into a word whose byte k carries rank 2k in its low bits and whose copy
+// shifted right by HI_SHIFT carries rank 2k+1 there; bits above the code width are junk and are masked
+// off when the bf16 pattern is formed.
+//   4 bit: the stream itself (nibbles);
+//   3 bit: three shift-and-select steps spread the eight 3-bit fields to nibbles (bit 3 of each is junk);
+//   2 bit: one byte permute puts ranks 0,2,4,6 into bits 0..1 of bytes 0..3 and ranks 1,3,5,7 into bits 2..3.
+// selA / selB / self are the table fields of the mask byte (see Lut4), out[i] = bf16x2 weights of
+// positions (2i, 2i+1).
+struct Lut4 { uint32_t selA, selB, self, amt; };   // amt = BITS * number of survivors: window advance in bits
+
+constexpr Lut4 make_lut4(const LutEntry& e, int bits) {
+    return Lut4{e.x & 0xFFFFu, e.y & 0xFFFFu, e.x >> 16, ((e.y >> 16) / 4u) * (uint32_t)bits};
+}
+
+template <int BITS>
+CB_HD uint32_t code_view(uint32_t w0) {
+    if (BITS == 4) return w0;
+    if (BITS == 2) return prmt(w0, w0 >> 4, 0x5140u);
+    const uint32_t t = (w0 & 0x0000FFFFu) | ((w0 << 4) & 0xFFFF0000u);
+    const uint32_t u = (t & 0x00FF00FFu) | ((t << 2) & 0xFF00FF00u);
+    return (u & 0x0F0F0F0Fu) | ((u << 1) & 0xF0F0F0F0u);
+}
+
+template <int BITS>
+CB_HD void decode8(uint32_t w0, uint32_t selA, uint32_t selB, uint32_t self, const SegParams& p, uint32_t out[4]) {
+    constexpr uint32_t HI_SHIFT = BITS == 2 ? 2u : 4u;
+    constexpr uint32_t CM = ((1u << BITS) - 1u) * 0x00010001u;
+    const uint32_t v = code_view<BITS>(w0);
+    const uint32_t hi = prmt(v >> HI_SHIFT, p.zq, self);      // byte 3 <- zero point unless all eight are kept
+    const uint32_t d0 = prmt(v, hi, selA), d1 = prmt(v, hi, selB);
+    out[0] = dq_pair(and_or(d0, CM, 0x43004300u), p);
+    out[1] = dq_pair(and_or(d0 >> 8, CM, 0x43004300u), p);
+    out[2] = dq_pair(and_or(d1, CM, 0x43004300u), p);
+    out[3] = dq_pair(and_or(d1 >> 8, CM, 0x43004300u), p);
+}
+
+// Literal fp32 path for 32 positions of any segment (off-grid zero point, column scale): codes are read
+// one at a time from the `BITS`-wide stream.  `stream` is a little-endian word stream, `bitpos` the bit
+// offset of the first survivor of this word.  cs may be null.
+template <class LoadWord>
+CB_HD void decode32_slow(uint32_t m, LoadWord word_at, uint32_t bitpos, int bits, const SegParams& p, const float* cs,
+                         uint32_t out[16]) {
+    const uint32_t cmask = (1u << bits) - 1u;
+    for (int i = 0; i < 16; ++i) {
+        uint32_t packed = 0;
+        for (int h = 0; h < 2; ++h) {
+            const int pos = 2 * i + h;
+            float wv = 0.0f;
+            if ((m >> pos) & 1u) {
+                const uint32_t wi = bitpos >> 5, sh = bitpos & 31u;
+                uint32_t v = word_at(wi) >> sh;
+                if (sh + (uint32_t)bits > 32u) v |= word_at(wi + 1) << (32u - sh);
+                wv = dequant_fp32((float)(v & cmask), p.z, p.s, cs ? cs[pos] : 1.0f);
+                bitpos += (uint32_t)bits;
+            }
+            packed |= float_to_bf16_bits(wv) << (16 * h);
+        }
+        out[i] = packed;
+    }
 }
 
 // ----------------------------------------------------------------------------- 2/3-bit -> nibble

@@ -1,24 +1,38 @@
 // Decode GEMV for M <= 16 tokens.
 //
-// Persistent kernel, one CTA per SM.  The tiles of the matrix (row-block-major) are cut into
-// one contiguous range per warp, balanced to +-1 tile over all warps of the grid, so every SM
-// gets the same share whatever the matrix shape.  Each warp pulls its tiles with 1-D bulk async
-// copies into a private shared-memory ring (mbarrier completion), locates every segment's
-// survivor codes with a popcount prefix sum over the warp, expands them to dense bf16 weights
-// in registers (decode_core.cuh) and contracts them against the activations with mma.sync
-// m16n8k16 (A = 16 rows x 16 columns of weights, B = 16 columns x 8 tokens).  Lane
-// (g = lane/4, t = lane%4) owns rows g and g+8 of the row block and group t of the tile; in
-// MMA step s it supplies columns 4s..4s+3 of that group, so the 16 k-slots of one MMA are 4
-// consecutive columns from each of the tile's 4 groups and the B fragment of the lane is
-// simply 8 contiguous bytes of x.
+// Persistent kernel, one CTA per SM.  The matrix is a sequence of tiles (row-block-major); a tile is four
+// "words" of 32 columns x 4 groups x 16 rows.  The words of the launch are cut into one contiguous range
+// per warp, balanced to +-1 word over all warps of the grid, so every SM gets the same share whatever the
+// matrix shape and no warp waits for a neighbour that drew a whole extra tile.  Each warp pulls the tiles its
+// range touches with 1-D bulk async copies into a private shared-memory ring (mbarrier completion), locates
+// every segment's survivor codes with a popcount prefix sum over the warp, expands them to dense bf16 weights
+// in registers (decode_core.cuh) and contracts them against the activations with mma.sync m16n8k16
+// (A = 16 rows x 16 columns of weights, B = 16 columns x 8 tokens).  Lane (g = lane/4, t = lane%4) owns rows g
+// and g+8 of the row block and group t of the tile; in MMA step s it supplies columns 4s..4s+3 of that group,
+// so the 16 k-slots of one MMA are 4 consecutive columns from each of the tile's 4 groups and the B fragment
+// of the lane is simply 8 contiguous bytes of x.
 //
-// A row block that is covered by several warps is finished in two deterministic stages.  The
-// parts held by one CTA meet in shared memory: the last of its warps to arrive adds the fp32
-// fragments in range order.  If the block straddles CTAs, that subtotal goes to global scratch and
-// the last CTA to arrive adds the subtotals in CTA order (fence + atomic + L2 round trips,
-// microseconds).  Warps whose range ends in a block that continues into the next CTA walk their
-// range backwards, so that this slow exchange happens at the start of both neighbours' work
-// instead of at the very end of the kernel.
+// The inner loop works in units of 16 columns (two mask bytes per row).  Everything a unit needs from shared
+// memory - three words of the code stream at the unit's bit offset, the expansion table entries of its four
+// mask bytes, its activations - is requested one unit ahead, so the loads of unit u+1 are in flight while unit
+// u is being expanded.  Codes are decoded straight from the 2-, 3- or 4-bit stream (decode8), there is no
+// re-pack pass.
+//
+// Activations: when M * N * 2 bytes fit beside the ring (always for one token), the CTA copies x into shared
+// memory once, 16-byte chunks XOR-swizzled so that the 32 lanes of a fragment load hit 8 distinct bank groups
+// per quarter warp; otherwise every lane reads its fragment from global memory (read-only path), also one
+// unit ahead.
+//
+// Row blocks covered by several warps.  Every warp holds at most two partial sums: of the row block its range
+// starts in and of the one it ends in.  They are combined deterministically, in warp order:
+//   * a block whose words all belong to this CTA: each warp parks its fp32 fragments in shared memory, tagged
+//     with the row block; after one CTA barrier at the end of the walk the first holder of every tag adds the
+//     fragments in warp order and stores the rows;
+//   * a block that straddles CTAs: its holders in this CTA meet early through a shared-memory arrival counter
+//     (the last of them adds the fragments in warp order), that subtotal goes to global scratch and the last
+//     CTA to arrive adds the subtotals in CTA order (fence + atomic + L2 round trips, microseconds).  Warps
+//     whose range ends in a block that continues into the next CTA walk their tiles backwards, so that this slow
+//     exchange happens at the start of both neighbours' work instead of at the very end of the kernel.
 //
 // Behaviour replaced: cbk::gemv_sparse / gemv_sparse_expand, one warp per row with a 32-lane
 // prefix scan per 1024-column window (src/cobaltkernel/csrc/cobalt_gemv.cuh:216-393).
@@ -30,13 +44,20 @@ namespace cb {
 constexpr int GEMV_WARPS = 16;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 4;
-constexpr uint32_t GEMV_LUT_BYTES = LUT_ENTRIES * LUT_COPIES * 8;      // 32 KB
-constexpr uint32_t GEMV_BAR_BYTES = GEMV_WARPS * GEMV_MAX_STAGES * 8;  // 512 B
-constexpr uint32_t GEMV_REDCNT_BYTES = 128;                            // in-CTA arrival counters: one per first owner + one
+constexpr int TILE_WORDS = 4;                                              // 32-column words per tile
+// expansion table in shared memory: 16-byte entries, 8 replicas.  A 128-bit shared load is served one
+// quarter warp at a time, so 8 replicas (lane & 7) make every lookup conflict-free.
+constexpr int GEMV_LUT_COPIES = 8;
+constexpr uint32_t GEMV_LUT_BYTES = LUT_ENTRIES * GEMV_LUT_COPIES * 16;    // 32 KB; the staged activations follow
+constexpr uint32_t GEMV_BAR_BYTES = (GEMV_WARPS * GEMV_MAX_STAGES + 2) * 8;   // tile barriers + the "activations staged" barrier
+// in-CTA bookkeeping: arrival counters of the straddling blocks (one per first owner + one), then the
+// row-block tags of the parked fragments [warp][head|tail]
+constexpr uint32_t GEMV_REDCNT_BYTES = 128 + GEMV_WARPS * 2 * 4;
 // in-CTA reduction fragments: [warp][head|tail][4 * MT * 32] floats
 constexpr uint32_t gemv_red_bytes(int mt) { return GEMV_WARPS * 2 * 4 * mt * 32 * 4; }
 
 constexpr int GEMV_MAX_MATS = 4;
+static_assert(GEMV_WARPS * 2 == 32, "the end-of-walk reduction keeps one parked-fragment tag per lane");
 
 // one matrix of a (possibly fused) launch; all matrices of a launch share x, N and the bit width
 struct GemvMat {
@@ -58,17 +79,19 @@ struct GemvParams {
     const uint16_t* x; int64_t ldx;
     int M;
     int stages;
-    uint32_t slot_bytes, nib_bytes;
+    uint32_t slot_bytes;
+    uint32_t xs_bytes;                   // shared-memory bytes reserved for staged activations (0: read x from global)
     uint32_t total_warps;                // grid * GEMV_WARPS
-    float* partials;                     // [total_warps][2][4 * MT * 32]
+    int aligned;                         // CTAs hold whole row blocks (no exchange between CTAs)
+    uint32_t part_q, part_r;             // partition quotient and remainder, see cta_range_start()
+    float* partials;                     // [grid][2][4 * MT * 32]: CTA subtotals of straddling row blocks
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -80,197 +103,227 @@ __device__ __forceinline__ uint16_t finish_output(float acc, const uint16_t* bia
     return r;
 }
 
-// Read-only 16-byte load kept in program order with the shared-memory loads of the decoder, so
-// that it is issued before the decode of the word it belongs to and its latency hides behind it.
-__device__ __forceinline__ uint4 ldg_nc_early(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+// Partition of the U words of a launch over G CTAs.  The host passes q = X / G and r = X % G, where X is the
+// number of row blocks (`aligned`: every CTA holds whole row blocks, none is shared between CTAs) or the number
+// of words (balanced ranges); CTA c starts at unit c*q + min(c, r), i.e. the first r CTAs hold one unit more.
+// Warp w of a CTA gets [w*L/16, (w+1)*L/16) of the CTA's L words.  No division on the kernel's start-up path.
+__device__ __forceinline__ uint32_t cta_range_start(uint32_t c, uint32_t q, uint32_t r, uint32_t WPB, bool aligned) {
+    const uint32_t unit = c * q + (c < r ? c : r);
+    return aligned ? unit * WPB : unit;
+}
+__device__ __forceinline__ uint32_t cta_of_word(uint32_t u, uint32_t q, uint32_t r) {      // balanced ranges only
+    const uint32_t thr = r * (q + 1u);
+    return u < thr ? u / (q + 1u) : r + (u - thr) / q;
+}
+__device__ __forceinline__ uint32_t warp_range_start(uint32_t cta_u0, uint32_t L, uint32_t w) { return cta_u0 + ((w * L) / GEMV_WARPS); }
+
+__device__ __forceinline__ uint32_t atom_add_acq_rel_cta_shared(uint32_t* p, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+// L2 eviction policies: the weight stream is read once (evict first), the small tile-offset tables are read
+// by every launch and should survive the stream (evict last)
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p; asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p; asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+__device__ __forceinline__ uint32_t ldg_hint(const uint32_t* p, uint64_t pol) {
+    uint32_t v; asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol)); return v;
+}
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
 }
 
-// nibble stream window of one 32-column word: 128 bits starting at nibble `nib_off`
-__device__ __forceinline__ void load_window(uint32_t cbase, uint32_t nib_off, uint32_t& w0, uint32_t& w1,
-                                            uint32_t& w2, uint32_t& w3) {
-    const uint32_t bitpos = nib_off * 4u;
-    const uint32_t a = cbase + (bitpos >> 5) * 4u;
-    const uint32_t r0 = lds32(a), r1 = lds32(a + 4), r2 = lds32(a + 8), r3 = lds32(a + 12), r4 = lds32(a + 16);
-    const uint32_t o = bitpos & 31u;
-    w0 = funnel_r(r0, r1, o); w1 = funnel_r(r1, r2, o); w2 = funnel_r(r2, r3, o); w3 = funnel_r(r3, r4, o);
+// table entry of one mask byte, computed (no global read on the kernel's critical path); same contents as
+// make_lut4(build_expand_lut()[mb], bits)
+__device__ __forceinline__ uint4 gemv_lut_entry(uint32_t mb, int bits) {
+    uint32_t s[8];
+    uint32_t rank = 0;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const uint32_t kept = (mb >> p) & 1u;
+        const uint32_t sel = (rank & 1u) ? 4u + (rank >> 1) : (rank >> 1);
+        s[p] = kept ? sel : 7u;
+        rank += kept;
+    }
+    return make_uint4(s[0] | (s[2] << 4) | (s[1] << 8) | (s[3] << 12), s[4] | (s[6] << 4) | (s[5] << 8) | (s[7] << 12),
+                      rank == 8u ? 0x3210u : 0x4210u, rank * (uint32_t)bits);
 }
 
-// first tile of warp gw / warp that owns tile tau, for the balanced contiguous partition
-__device__ __forceinline__ uint32_t range_start(uint32_t gw, uint32_t T, uint32_t Wt) { return (uint32_t)(((uint64_t)gw * T) / Wt); }
-__device__ __forceinline__ uint32_t tile_owner(uint32_t tau, uint32_t T, uint32_t Wt) { return ((tau + 1u) * Wt - 1u) / T; }
+// what one unit (16 columns of both rows of a lane) reads from memory; requested one unit ahead
+template <int MT>
+struct GemvUnit {
+    uint32_t ra0, ra1, ra2, rb0, rb1, rb2;     // code-stream words at the unit's bit offset, rows A and B
+    uint4 ea0, ea1, eb0, eb1;                  // table entries of the unit's mask bytes
+    uint4 x[MT][2];                            // activations: 16 columns x token g (+8)
+};
 
-template <int BITS, int MT>
+template <int BITS, int MT, bool XS>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t full = 0xFFFFFFFFu;
-    auto mat_of = [&](int rbg) {                                       // matrix that owns row block rbg of the launch
+    // Fields of the matrix that owns row block rbg of the launch.  Selected with compares over the (at most four)
+    // parameter slots: indexing the parameter block with a run-time value would turn every access into a load from
+    // the constant cache, cold at every launch and on the path to the first tile request.
+    auto mat_of = [&](int rbg) {
         int m = 0;
 #pragma unroll
         for (int k = 1; k < GEMV_MAX_MATS; ++k)
             if (k < P.n_mats && rbg >= P.mat[k].rb_start) m = k;
         return m;
     };
+#define MAT_FIELD(m, f) ((m) == 0 ? P.mat[0].f : (m) == 1 ? P.mat[1].f : (m) == 2 ? P.mat[2].f : P.mat[3].f)
 
-    // ---- block set-up: barriers first, so that the first tiles are in flight while the
-    //      expansion table replicas are being written
-    LutEntry* lut_s = reinterpret_cast<LutEntry*>(smem);
-    const uint32_t bar0 = smem_u32(smem + GEMV_LUT_BYTES) + warp * GEMV_MAX_STAGES * 8;
+    // ---- shared-memory map: table | staged activations | barriers | in-CTA counters, tags | in-CTA fragments | rings
+    uint4* lut_s = reinterpret_cast<uint4*>(smem);
+    uint8_t* xs = smem + GEMV_LUT_BYTES;
+    uint8_t* after_x = xs + P.xs_bytes;
+    const uint32_t bar0 = smem_u32(after_x) + warp * GEMV_MAX_STAGES * 8;
+    const uint32_t xbar = smem_u32(after_x) + GEMV_WARPS * GEMV_MAX_STAGES * 8;     // every thread arrives once x and the table are in place
+    constexpr int FR = 4 * MT * 32;                                    // floats of one accumulator fragment set
+    uint32_t* red_cnt = reinterpret_cast<uint32_t*>(after_x + GEMV_BAR_BYTES);
+    int* red_tag = reinterpret_cast<int*>(after_x + GEMV_BAR_BYTES + 128);          // [warp][head|tail] row block or -1
+    float* red = reinterpret_cast<float*>(after_x + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES);
+    // ---- this warp's share of the launch, and the offsets of its first tiles (their loads fly during the set-up)
+    const int M = P.M, CT = P.CT;
+    const uint32_t WPB = (uint32_t)TILE_WORDS * (uint32_t)CT;          // words per row block
+    const bool aligned = P.aligned != 0;
+    const uint32_t cta_u0 = cta_range_start(blockIdx.x, P.part_q, P.part_r, WPB, aligned);
+    const uint32_t cta_u1 = cta_range_start(blockIdx.x + 1u, P.part_q, P.part_r, WPB, aligned);
+    const uint32_t Lc = cta_u1 - cta_u0;
+    const uint32_t u0 = warp_range_start(cta_u0, Lc, (uint32_t)warp), u1 = warp_range_start(cta_u0, Lc, (uint32_t)warp + 1u);
+    const bool busy = u1 > u0;
+    const uint32_t ta = u0 / TILE_WORDS, tb = busy ? (u1 - 1u) / TILE_WORDS : ta;   // first and last tile the range touches
+    const int n = busy ? (int)(tb - ta + 1u) : 0;
+    // row blocks of this CTA that it shares with a neighbour (-1: none on that side; never with aligned ranges)
+    int blk_left = -1, blk_right = -1;
+    bool rev = false;
+    if (!aligned && Lc != 0u) {
+        if (cta_u0 % WPB != 0u) blk_left = (int)(cta_u0 / WPB);
+        if (cta_u1 % WPB != 0u) blk_right = (int)((cta_u1 - 1u) / WPB);
+        // A warp whose range ends in the row block that continues into the next CTA walks backwards: that block's
+        // exchange through global scratch then starts early in both CTAs instead of ending the kernel.
+        rev = busy && blk_right >= 0 && u1 - 1u >= (uint32_t)blk_right * WPB;
+    }
+    auto tile_at = [&](int i) { return rev ? tb - (uint32_t)i : ta + (uint32_t)i; };
+    const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+
+    // offsets of the i-th tile of the walk, requested by lane i for the first 32 tiles; they are turned into an
+    // address and a size only when the copy is issued, so the loads fly during the block set-up
+    auto tile_offsets = [&](uint32_t tau, uint32_t& o0, uint32_t& o1, const uint8_t*& base) {
+        const int m = mat_of((int)(tau / (uint32_t)P.CT));
+        const uint32_t local = tau - (uint32_t)MAT_FIELD(m, rb_start) * (uint32_t)P.CT;
+        const uint32_t* toff = MAT_FIELD(m, tile_off);
+        base = MAT_FIELD(m, tiles);
+        o0 = ldg_hint(toff + local, pol_keep);
+        o1 = ldg_hint(toff + local + 1, pol_keep);
+    };
+    const uint8_t* my_base = nullptr;
+    uint32_t my_o0 = 0, my_o1 = 0;
+    if (lane < n) tile_offsets(tile_at(lane), my_o0, my_o1, my_base);
+
+    // ---- block set-up: barriers first, so that the first tiles are in flight while the table is being written
     if (lane == 0)
         for (int s = 0; s < P.stages; ++s) mbar_init(bar0 + 8 * s, 1);
-    constexpr int FR = 4 * MT * 32;                                    // floats of one accumulator fragment set
-    uint32_t* red_cnt = reinterpret_cast<uint32_t*>(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES);
-    float* red = reinterpret_cast<float*>(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES);
-    if (threadIdx.x <= GEMV_WARPS) red_cnt[threadIdx.x] = 0u;
+    if (threadIdx.x == 0) mbar_init(xbar, GEMV_THREADS);
+    if (threadIdx.x < 2) red_cnt[threadIdx.x] = 0u;
+    if (threadIdx.x < GEMV_WARPS * 2) red_tag[threadIdx.x] = -1;
     mbar_fence_init();
     fence_proxy_async();
     __syncthreads();
 
-    const int M = P.M, CT = P.CT;
-    const uint32_t T = (uint32_t)P.RB * (uint32_t)P.CT, Wt = P.total_warps;
-    const uint32_t gw = blockIdx.x * GEMV_WARPS + warp;
-    const uint32_t t0 = range_start(gw, T, Wt), t1 = range_start(gw + 1, T, Wt);
-    const int n = (int)(t1 - t0);
+    uint8_t* ring_p = after_x + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES + gemv_red_bytes(MT) + (size_t)warp * P.stages * P.slot_bytes;
+    const uint32_t ring = smem_u32(ring_p);
+    const uint4* lut_lane = lut_s + (lane & (GEMV_LUT_COPIES - 1));
 
-    const uint32_t per_warp = P.stages * P.slot_bytes + P.nib_bytes;
-    const uint32_t ring = smem_u32(smem + GEMV_LUT_BYTES + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES + gemv_red_bytes(MT)) + warp * per_warp;
-    const uint32_t cta_t0 = range_start(blockIdx.x * GEMV_WARPS, T, Wt), cta_t1 = range_start((blockIdx.x + 1) * GEMV_WARPS, T, Wt);
-    // A warp whose range ends in the row block that continues into the next CTA walks backwards: that block's
-    // exchange through global scratch then starts early in both CTAs instead of ending the kernel.
-    const bool rev = n > 0 && ((t1 - 1u) / (uint32_t)P.CT + 1u) * (uint32_t)P.CT > cta_t1;
-    auto tile_at = [&](int i) { return rev ? t1 - 1u - (uint32_t)i : t0 + (uint32_t)i; };
-    const uint32_t nib = ring + P.stages * P.slot_bytes;
-    const uint32_t lut_lane = smem_u32(smem) + (uint32_t)(lane & (LUT_COPIES - 1)) * 8u;
-    const LutEntry* lut_lane_ptr = lut_s + (lane & (LUT_COPIES - 1));
-
-    // address and size of the i-th tile of the walk, looked up by lane i for the first 32 tiles
-    auto tile_src = [&](uint32_t tau, const uint8_t*& src, uint32_t& bytes) {
-        const int rbg = (int)(tau / (uint32_t)P.CT);
-        const GemvMat& mt = P.mat[mat_of(rbg)];
-        const uint32_t local = tau - (uint32_t)mt.rb_start * (uint32_t)P.CT;
-        const uint32_t o0 = mt.tile_off[local], o1 = mt.tile_off[local + 1];
-        src = mt.tiles + (size_t)o0 * 16;
-        bytes = (o1 - o0) * 16u;
-    };
-    const uint8_t* my_src = nullptr;
-    uint32_t my_bytes = 0;
-    if (lane < n) tile_src(tile_at(lane), my_src, my_bytes);
-
-    auto issue = [&](int i, int slot_idx) {                            // all lanes call; lane 0 acts
-        const uint8_t* src;
-        uint32_t bytes;
+    auto issue = [&](int i, int slot_idx, bool drained) {              // all lanes call; lane 0 acts
+        const uint8_t* base;
+        uint32_t o0, o1;
         if (i < 32) {
-            const unsigned long long a = __shfl_sync(full, (unsigned long long)my_src, i);
-            src = (const uint8_t*)a;
-            bytes = __shfl_sync(full, my_bytes, i);
+            base = (const uint8_t*)__shfl_sync(full, (unsigned long long)my_base, i);
+            o0 = __shfl_sync(full, my_o0, i);
+            o1 = __shfl_sync(full, my_o1, i);
         } else {
-            tile_src(tile_at(i), src, bytes);
+            tile_offsets(tile_at(i), o0, o1, base);
         }
         if (lane == 0) {
             const uint32_t bar = bar0 + 8 * slot_idx;
-            fence_proxy_async();
+            const uint32_t bytes = (o1 - o0) * 16u;
+            if (drained) fence_proxy_async();                          // the slot was read through the generic proxy before
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_g2s(ring + slot_idx * P.slot_bytes, src, bytes, bar);
+            bulk_g2s_hint(ring + slot_idx * P.slot_bytes, base + (size_t)o0 * 16, bytes, bar, pol_stream);
         }
     };
 
     int issued = n < P.stages ? n : P.stages;
-    for (int i = 0; i < issued; ++i) issue(i, i);
-
-    for (int i = threadIdx.x; i < LUT_ENTRIES * LUT_COPIES; i += GEMV_THREADS) lut_s[i] = g_lut.e[i / LUT_COPIES];
-    __syncthreads();
+    if (issued > 0) issue(0, 0, false);                               // the first tile is on its way before anything else
     // Programmatic dependent launch: everything above touched only the weights and this CTA's shared
     // memory.  From here on the activations and the scratch of the previous kernel in the stream are used.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // x -> shared memory, rows of N bf16, 16-byte chunk c of token m stored at chunk c ^ swizzle(group, m).  The
+    // first chunks of every thread are requested before the table is built, so that their latency hides behind it.
+    constexpr int XPRE = 2;
+    const int chunks_per_row = P.N / 8;
+    const int x_total = XS ? chunks_per_row * M : 0;
+    uint4 xpre[XPRE];
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+        if (i < x_total) {
+            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            xpre[q] = __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c);
+        }
+    }
+    static_assert(GEMV_THREADS == 2 * LUT_ENTRIES && GEMV_LUT_COPIES == 8, "table fill: one entry and four replicas per thread");
+    {
+        const uint32_t mb = threadIdx.x & (LUT_ENTRIES - 1), half = threadIdx.x / LUT_ENTRIES;
+        const uint4 e = gemv_lut_entry(mb, BITS);
+        uint4* dst = lut_s + mb * GEMV_LUT_COPIES + half * (GEMV_LUT_COPIES / 2);
+#pragma unroll
+        for (int c = 0; c < GEMV_LUT_COPIES / 2; ++c) dst[c] = e;
+    }
+    {
+        auto stage_chunk = [&](int i, const uint4& v) {
+            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            const int pc = c ^ (((c >> 4) & 3) | ((m & 1) << 2));
+            *reinterpret_cast<uint4*>(xs + ((size_t)m * chunks_per_row + pc) * 16) = v;
+        };
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+            if (i < x_total) stage_chunk(i, xpre[q]);
+        }
+        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            stage_chunk(i, __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c));
+        }
+        mbar_arrive(xbar);                                             // releases this thread's table and x stores
+    }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (n == 0) return;
+    for (int i = 1; i < issued; ++i) issue(i, i, false);               // the rest of the ring, off the path to the first decode
 
     float acc[MT][4];
 #pragma unroll
     for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
 
-    // ---- finish one row block: direct store, or deterministic reduction by the last arriver
-    auto flush = [&](int rb) {
-        const uint32_t first = (uint32_t)rb * P.CT, last = first + P.CT - 1;
-        const GemvMat& mt = P.mat[mat_of(rb)];
+    // ---- rows of one finished row block -> y
+    auto store_rows = [&](int rb) {
+        const int mi = mat_of(rb);
+        GemvMat mt;
+        mt.y = MAT_FIELD(mi, y); mt.y32 = MAT_FIELD(mi, y32); mt.bias = MAT_FIELD(mi, bias); mt.ldy = MAT_FIELD(mi, ldy);
+        mt.K = MAT_FIELD(mi, K); mt.rb_start = MAT_FIELD(mi, rb_start);
         const int row0 = (rb - mt.rb_start) * TILE_ROWS + g, row1 = row0 + 8;
-        const bool whole = (t0 <= first) && (t1 > last);
-        if (!whole) {
-            // ---- stage 1, shared memory: the parts held by this CTA's warps, added in range order by the last of them
-            const uint32_t o_first = tile_owner(first, T, Wt), o_last = tile_owner(last, T, Wt);
-            const uint32_t cta_lo = blockIdx.x * GEMV_WARPS;
-            const uint32_t lo_t = first > cta_t0 ? first : cta_t0, hi_t = last < cta_t1 - 1u ? last : cta_t1 - 1u;   // tiles of the block in this CTA
-            const uint32_t o_lo = o_first > cta_lo ? o_first : cta_lo;
-            const uint32_t o_hi = o_last < cta_lo + GEMV_WARPS - 1u ? o_last : cta_lo + GEMV_WARPS - 1u;
-            const uint32_t nlocal = (T < Wt) ? hi_t - lo_t + 1u : o_hi - o_lo + 1u;      // at most one tile per warp when T < Wt
-            if (nlocal > 1u) {
-                float* mine = red + (warp * 2 + (t0 >= first ? 0 : 1)) * FR;
-#pragma unroll
-                for (int b = 0; b < MT; ++b)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
-                __threadfence_block();
-                __syncwarp();
-                // counter: keyed by the first owner inside the CTA; the block that began in an earlier CTA has its own
-                const uint32_t key = o_first < cta_lo ? (uint32_t)GEMV_WARPS : o_first - cta_lo;
-                uint32_t old = 0;
-                if (lane == 0) old = atomicAdd(&red_cnt[key], 1u);
-                old = __shfl_sync(full, old, 0);
-                if (old != nlocal - 1u) return;
-                __threadfence_block();
-#pragma unroll
-                for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
-                if (T < Wt) {                                          // one tile per owner, owners not consecutive
-                    for (uint32_t tau = lo_t; tau <= hi_t; ++tau) {
-                        const volatile float* src = red + (tile_owner(tau, T, Wt) - cta_lo) * 2u * FR;
-#pragma unroll
-                        for (int b = 0; b < MT; ++b)
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
-                    }
-                } else {                                               // consecutive owners; only the block's first owner can hold it as a tail
-                    for (uint32_t o = o_lo; o <= o_hi; ++o) {
-                        const uint32_t tail = (o == o_first && range_start(o, T, Wt) < first) ? 1u : 0u;
-                        const volatile float* src = red + ((o - cta_lo) * 2u + tail) * FR;
-#pragma unroll
-                        for (int b = 0; b < MT; ++b)
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
-                    }
-                }
-            }
-            // ---- stage 2, global scratch: one subtotal per CTA, added in CTA order by the last CTA to arrive
-            const uint32_t c_first = o_first / GEMV_WARPS, c_last = o_last / GEMV_WARPS;
-            if (c_first != c_last) {
-                float* mine = P.partials + (size_t)(blockIdx.x * 2u + (cta_t0 >= first ? 0u : 1u)) * FR;
-#pragma unroll
-                for (int b = 0; b < MT; ++b)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) mine[(b * 4 + r) * 32 + lane] = acc[b][r];
-                fence_acq_rel_gpu();
-                __syncwarp();
-                uint32_t old = 0;
-                if (lane == 0) old = atomicAdd(&P.counters[rb], 1u);
-                old = __shfl_sync(full, old, 0);
-                if (old != c_last - c_first) return;
-                fence_acq_rel_gpu();
-#pragma unroll
-                for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
-                for (uint32_t c = c_first; c <= c_last; ++c) {         // only the first CTA can hold the block as a tail
-                    const uint32_t tail = (c == c_first && range_start(c * GEMV_WARPS, T, Wt) < first) ? 1u : 0u;
-                    const float* src = P.partials + (size_t)(c * 2u + tail) * FR;
-#pragma unroll
-                    for (int b = 0; b < MT; ++b)
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) acc[b][r] += __ldcg(src + (b * 4 + r) * 32 + lane);
-                }
-                if (lane == 0) P.counters[rb] = 0u;
-            }
-        }
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
@@ -295,11 +348,88 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             }
         }
     };
+    auto park = [&](float* dst) {
+#pragma unroll
+        for (int b = 0; b < MT; ++b)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) dst[(b * 4 + r) * 32 + lane] = acc[b][r];
+    };
+    auto clear_acc = [&]() {
+#pragma unroll
+        for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+    };
+
+    // ---- the warp has added its last word of row block rb
+    auto finish_block = [&](int rb) {
+        const uint32_t first = (uint32_t)rb * WPB, last = first + WPB - 1u;
+        if (u0 <= first && u1 > last) { store_rows(rb); return; }      // the whole block was this warp's
+        const int side = u0 >= first ? 0 : 1;                          // the block the range starts in / ends in
+        float* mine = red + (warp * 2 + side) * FR;
+        if (rb != blk_left && rb != blk_right) {                       // all holders are in this CTA: combined after the walk
+            park(mine);
+            if (lane == 0) red_tag[warp * 2 + side] = rb;
+            return;
+        }
+        // ---- straddling block, stage 1: its holders in this CTA (consecutive warps), added in warp order by the
+        //      last of them to arrive.  Lane w < 16 works out warp w's range; two ballots give the holders and which
+        //      of them hold the block as the one their range ends in.
+        const uint32_t wl0 = warp_range_start(cta_u0, Lc, (uint32_t)(lane & 15)), wl1 = warp_range_start(cta_u0, Lc, (uint32_t)(lane & 15) + 1u);
+        const bool holds = lane < GEMV_WARPS && wl1 > wl0 && wl0 <= last && wl1 > first;
+        const uint32_t holders = __ballot_sync(full, holds), tails = __ballot_sync(full, holds && wl0 < first);
+        const uint32_t nlocal = (uint32_t)__popc(holders);
+        if (nlocal > 1u) {
+            park(mine);
+            __syncwarp();
+            uint32_t old = 0;
+            if (lane == 0) old = atom_add_acq_rel_cta_shared(&red_cnt[rb == blk_left ? 0 : 1], 1u);
+            old = __shfl_sync(full, old, 0);
+            if (old != nlocal - 1u) return;
+            clear_acc();
+            for (uint32_t hm = holders; hm; hm &= hm - 1u) {
+                const uint32_t o = (uint32_t)__ffs(hm) - 1u;
+                const volatile float* src = red + (o * 2u + ((tails >> o) & 1u)) * FR;
+#pragma unroll
+                for (int b = 0; b < MT; ++b)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
+            }
+        }
+        // ---- stage 2, global scratch: one subtotal per CTA, added in CTA order by the last CTA to arrive
+        const uint32_t c_first = cta_of_word(first, P.part_q, P.part_r), c_last = cta_of_word(last, P.part_q, P.part_r);
+        if (c_first != c_last) {
+            float* sub = P.partials + (size_t)(blockIdx.x * 2u + (cta_u0 >= first ? 0u : 1u)) * FR;
+            park(sub);
+            __syncwarp();
+            uint32_t old = 0;
+            if (lane == 0) old = atom_add_acq_rel_gpu(&P.counters[rb], 1u);
+            old = __shfl_sync(full, old, 0);
+            if (old != c_last - c_first) return;
+            clear_acc();
+            for (uint32_t c = c_first; c <= c_last; ++c) {             // only the first CTA can hold the block as a tail
+                const uint32_t tail = (c == c_first && cta_range_start(c, P.part_q, P.part_r, WPB, false) < first) ? 1u : 0u;
+                const float* src = P.partials + (size_t)(c * 2u + tail) * FR;
+#pragma unroll
+                for (int b = 0; b < MT; ++b)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[b][r] += __ldcg(src + (b * 4 + r) * 32 + lane);
+            }
+            if (lane == 0) P.counters[rb] = 0u;
+        }
+        store_rows(rb);
+    };
+
+    // tokens of this lane's B fragments: g and g + 8; columns of tokens beyond M are computed from the last
+    // real token and never stored
+    int tok[MT];
+#pragma unroll
+    for (int b = 0; b < MT; ++b) { tok[b] = g + 8 * b; if (tok[b] > M - 1) tok[b] = M - 1; }
+    const uint32_t x_row_bytes = (uint32_t)P.N * 2u;
 
     bool healthy = true;
+    bool staged = false;                                              // has this warp seen the table and the staged x yet?
     int st = -1;                                                      // ring slot and phase parity of tile i
     uint32_t par = 0;
-    const uint32_t tau0 = rev ? t1 - 1u : t0;                           // first tile of the walk
+    const uint32_t tau0 = rev ? tb : ta;                                // first tile of the walk
     int cur_rb = (int)(tau0 / (uint32_t)P.CT);
     int rb = cur_rb, ct = (int)(tau0 - (uint32_t)cur_rb * P.CT) + (rev ? 1 : -1);   // stepped at the top of every iteration
     for (int i = 0; i < issued; ++i) {
@@ -311,23 +441,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         if (rev) { if (--ct < 0) { ct = CT - 1; --rb; } }
         else if (++ct == CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {
-            flush(cur_rb);
-#pragma unroll
-            for (int b = 0; b < MT; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f; }
+            finish_block(cur_rb);
+            clear_acc();
             cur_rb = rb;
         }
+        // words of this tile that belong to the range
+        const uint32_t tau = tile_at(i);
+        const int ja = tau == ta ? (int)(u0 % TILE_WORDS) : 0;
+        const int jb = tau == tb ? (int)((u1 - 1u) % TILE_WORDS) + 1 : TILE_WORDS;
         int w = P.G - TILE_GROUPS * ct;
         if (w > TILE_GROUPS) w = TILE_GROUPS;
         const bool active = t < w;
-        const uint32_t slot = ring + st * P.slot_bytes;
+        const uint8_t* slot = ring_p + (size_t)st * P.slot_bytes;
         const int segA = g * w + t, segB = (g + 8) * w + t;
         uint4 mA = make_uint4(0, 0, 0, 0), mB = make_uint4(0, 0, 0, 0);
         uint32_t szA = 0, szB = 0;
         if (active) {
-            mA = lds128(slot + segA * 16);
-            mB = lds128(slot + segB * 16);
-            szA = lds32(slot + TILE_ROWS * w * 16 + segA * 4);
-            szB = lds32(slot + TILE_ROWS * w * 16 + segB * 4);
+            mA = *reinterpret_cast<const uint4*>(slot + segA * 16);
+            mB = *reinterpret_cast<const uint4*>(slot + segB * 16);
+            szA = *reinterpret_cast<const uint32_t*>(slot + TILE_ROWS * w * 16 + segA * 4);
+            szB = *reinterpret_cast<const uint32_t*>(slot + TILE_ROWS * w * 16 + segB * 4);
         }
         const uint32_t cntA = __popc(mA.x) + __popc(mA.y) + __popc(mA.z) + __popc(mA.w);
         const uint32_t cntB = __popc(mB.x) + __popc(mB.y) + __popc(mB.z) + __popc(mB.w);
@@ -340,87 +473,115 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         }
         const uint32_t tot = __shfl_sync(full, inc, 31);
         const uint32_t exc = inc - v;
-        uint32_t offA = exc & 0xFFFFu;                                 // in codes
-        uint32_t offB = (tot & 0xFFFFu) + (exc >> 16);
-
-        uint32_t cbase = slot + TILE_ROWS * w * 20;
-        if (BITS < 4) {                                                // re-pack the tile's codes as nibbles
-            const uint32_t total = (tot & 0xFFFFu) + (tot >> 16);
-            const uint32_t nchunks = (total + 7u) >> 3;
-            for (uint32_t c = lane; c < nchunks; c += 32) {
-                uint32_t outv;
-                if (BITS == 3) {
-                    const uint32_t bo = 3u * c, a = cbase + (bo & ~3u);
-                    outv = spread3(funnel_r(lds32(a), lds32(a + 4), (bo & 3u) * 8u) & 0x00FFFFFFu);
-                } else {
-                    outv = spread2(lds32(cbase + (c >> 1) * 4u) >> (16u * (c & 1u)));
-                }
-                sts32(nib + c * 4u, outv);
-            }
-            __syncwarp();
-            cbase = nib;
+        uint32_t bitA = (exc & 0xFFFFu) * BITS;                        // bit offset of the lane's first code, row A / row B
+        uint32_t bitB = ((tot & 0xFFFFu) + (exc >> 16)) * BITS;
+        const uint32_t* cw = reinterpret_cast<const uint32_t*>(slot + TILE_ROWS * w * 20);   // code stream of the tile
+        for (int r = 0; r < ja; ++r) {                                 // skip the words in front of the range
+            bitA += BITS * __popc(mA.x); bitB += BITS * __popc(mB.x);
+            mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
+            mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
         }
 
+        if (!staged) {                                                 // first tile: the table and the staged x must be in place
+            healthy = __all_sync(full, mbar_wait_bounded(xbar, 0u, P.status, DEV_TIMEOUT_TILE));
+            staged = true;
+            if (!healthy) continue;
+        }
         const SegParams pA = make_seg_params(szA, BITS, P.col_scale != nullptr);
         const SegParams pB = make_seg_params(szB, BITS, P.col_scale != nullptr);
         const bool all_fast = __all_sync(full, pA.fast && pB.fast);
-        const int col0 = (ct * TILE_GROUPS + t) * GROUP;               // first column of this lane's group
-        // Tokens beyond M read the last real token (their MMA columns are never stored); lanes beyond a
-        // partial tile read column 0 of x, which their all-zero weights cancel.
+        const int col0 = active ? (ct * TILE_GROUPS + t) * GROUP : 0;  // first column of this lane's group; lanes beyond a
+                                                                       // partial tile read column 0, their zero weights cancel it
+        // activations of this lane's group: staged copy (byte offset with the swizzle folded in) or global rows
+        uint32_t xs_lane[MT];
         const uint16_t* xrow[MT];
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
-            int tok = g + 8 * b;
-            if (tok > M - 1) tok = M - 1;
-            xrow[b] = P.x + (size_t)tok * P.ldx + (active ? col0 : 0);
+            xs_lane[b] = (uint32_t)tok[b] * x_row_bytes + (uint32_t)col0 * 2u + ((uint32_t)((t & 3) | ((tok[b] & 1) << 2)) << 4);
+            xrow[b] = P.x + (size_t)tok[b] * P.ldx + col0;
         }
-        auto lut = [lut_lane](uint32_t idx) {
-            const uint2 e = lds64(lut_lane + idx * (LUT_COPIES * 8u));
-            return LutEntry{e.x, e.y};
-        };
 
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t mAj = mA.x, mBj = mB.x;                     // rotate instead of indexing registers
-            mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
-            mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
-            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-            load_window(cbase, offA, a0, a1, a2, a3);
-            load_window(cbase, offB, b0, b1, b2, b3);
-            offA += __popc(mAj);
-            offB += __popc(mBj);
-            if (all_fast) {
+        if (all_fast) {
+            // ---- request everything unit `u` (16 columns: half h of mask word j) needs
+            auto load_unit = [&](uint32_t m16A, uint32_t m16B, uint32_t bA, uint32_t bB, int j, int h) {
+                GemvUnit<MT> Un;
+                const uint32_t* pa = cw + (bA >> 5);
+                const uint32_t* pb = cw + (bB >> 5);
+                Un.ra0 = pa[0]; Un.ra1 = pa[1]; Un.ra2 = BITS == 2 ? 0u : pa[2];
+                Un.rb0 = pb[0]; Un.rb1 = pb[1]; Un.rb2 = BITS == 2 ? 0u : pb[2];
+                Un.ea0 = lut_lane[(m16A & 0xFFu) * GEMV_LUT_COPIES];
+                Un.ea1 = lut_lane[(m16A >> 8) * GEMV_LUT_COPIES];
+                Un.eb0 = lut_lane[(m16B & 0xFFu) * GEMV_LUT_COPIES];
+                Un.eb1 = lut_lane[(m16B >> 8) * GEMV_LUT_COPIES];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {                          // 16 columns at a time keeps fewer registers live
-                    uint4 xv[MT][2];
-#pragma unroll
-                    for (int b = 0; b < MT; ++b) {
-                        const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * j + 16 * h);
-                        xv[b][0] = ldg_nc_early(xp);
-                        xv[b][1] = ldg_nc_early(xp + 1);
-                    }
-                    uint32_t ea[8], eb[8];
-                    decode16_fast(h ? (mAj >> 16) : (mAj & 0xFFFFu), a0, a1, a2, a3, pA, lut, ea);
-                    decode16_fast(h ? (mBj >> 16) : (mBj & 0xFFFFu), b0, b1, b2, b3, pB, lut, eb);
-#pragma unroll
-                    for (int b = 0; b < MT; ++b) {
-                        mma_bf16_16816(acc[b], ea[0], eb[0], ea[1], eb[1], xv[b][0].x, xv[b][0].y);
-                        mma_bf16_16816(acc[b], ea[2], eb[2], ea[3], eb[3], xv[b][0].z, xv[b][0].w);
-                        mma_bf16_16816(acc[b], ea[4], eb[4], ea[5], eb[5], xv[b][1].x, xv[b][1].y);
-                        mma_bf16_16816(acc[b], ea[6], eb[6], ea[7], eb[7], xv[b][1].z, xv[b][1].w);
+                for (int b = 0; b < MT; ++b) {
+                    if (XS) {
+                        const uint32_t jo = (uint32_t)j << 6;
+                        Un.x[b][0] = *reinterpret_cast<const uint4*>(xs + (xs_lane[b] ^ (jo | (uint32_t)(32 * h))));
+                        Un.x[b][1] = *reinterpret_cast<const uint4*>(xs + (xs_lane[b] ^ (jo | (uint32_t)(32 * h + 16))));
+                    } else {
+                        const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * (j & 3) + 16 * h);   // j == 4: the unused look-ahead
+                        Un.x[b][0] = __ldg(xp);
+                        Un.x[b][1] = __ldg(xp + 1);
                     }
                 }
-            } else {
+                return Un;
+            };
+            // ---- expand one unit and feed the tensor cores
+            auto compute_unit = [&](const GemvUnit<MT>& Un, uint32_t bA, uint32_t bB) {
+                uint32_t oa[8], ob[8];
+                const uint32_t a0 = funnel_r(Un.ra0, Un.ra1, bA);
+                const uint32_t a1 = BITS == 2 ? a0 >> Un.ea0.w : funnel_rc(a0, funnel_r(Un.ra1, Un.ra2, bA), Un.ea0.w);
+                decode8<BITS>(a0, Un.ea0.x, Un.ea0.y, Un.ea0.z, pA, oa);
+                decode8<BITS>(a1, Un.ea1.x, Un.ea1.y, Un.ea1.z, pA, oa + 4);
+                const uint32_t b0 = funnel_r(Un.rb0, Un.rb1, bB);
+                const uint32_t b1 = BITS == 2 ? b0 >> Un.eb0.w : funnel_rc(b0, funnel_r(Un.rb1, Un.rb2, bB), Un.eb0.w);
+                decode8<BITS>(b0, Un.eb0.x, Un.eb0.y, Un.eb0.z, pB, ob);
+                decode8<BITS>(b1, Un.eb1.x, Un.eb1.y, Un.eb1.z, pB, ob + 4);
+#pragma unroll
+                for (int b = 0; b < MT; ++b) {
+                    mma_bf16_16816(acc[b], oa[0], ob[0], oa[1], ob[1], Un.x[b][0].x, Un.x[b][0].y);
+                    mma_bf16_16816(acc[b], oa[2], ob[2], oa[3], ob[3], Un.x[b][0].z, Un.x[b][0].w);
+                    mma_bf16_16816(acc[b], oa[4], ob[4], oa[5], ob[5], Un.x[b][1].x, Un.x[b][1].y);
+                    mma_bf16_16816(acc[b], oa[6], ob[6], oa[7], ob[7], Un.x[b][1].z, Un.x[b][1].w);
+                }
+            };
+
+            GemvUnit<MT> cur = load_unit(mA.x & 0xFFFFu, mB.x & 0xFFFFu, bitA, bitB, ja, 0);
+#pragma unroll 1
+            for (int j = ja; j < jb; ++j) {
+                const uint32_t mAj = mA.x, mBj = mB.x;                 // rotate instead of indexing registers
+                mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
+                mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
+                const uint32_t bitA1 = bitA + BITS * __popc(mAj & 0xFFFFu), bitB1 = bitB + BITS * __popc(mBj & 0xFFFFu);
+                const GemvUnit<MT> nxt = load_unit(mAj >> 16, mBj >> 16, bitA1, bitB1, j, 1);
+                compute_unit(cur, bitA, bitB);
+                const uint32_t bitA2 = bitA + BITS * __popc(mAj), bitB2 = bitB + BITS * __popc(mBj);
+                // after the last word this requests a unit that is never expanded (harmless in-bounds reads)
+                cur = load_unit(mA.x & 0xFFFFu, mB.x & 0xFFFFu, bitA2, bitB2, j + 1, 0);
+                compute_unit(nxt, bitA1, bitB1);
+                bitA = bitA2; bitB = bitB2;
+            }
+        } else {
+            // ---- literal fp32 path (off-grid zero points, column scale): one 32-column word at a time
+            auto word_at = [&](uint32_t k) { return cw[k]; };
+#pragma unroll 1
+            for (int j = ja; j < jb; ++j) {
+                const uint32_t mAj = mA.x, mBj = mB.x;
+                mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
+                mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
                 uint32_t ea[16], eb[16];
                 float cs[32];
                 const float* csp = nullptr;
-                if (P.col_scale != nullptr && active) {
+                if (P.col_scale != nullptr) {
 #pragma unroll
                     for (int q = 0; q < 32; ++q) cs[q] = half_bits_to_float(P.col_scale[col0 + 32 * j + q]);
                     csp = cs;
                 }
-                decode32<LUT_COPIES>(mAj, a0, a1, a2, a3, pA, lut_lane_ptr, csp, ea);
-                decode32<LUT_COPIES>(mBj, b0, b1, b2, b3, pB, lut_lane_ptr, csp, eb);
+                decode32_slow(mAj, word_at, bitA, BITS, pA, csp, ea);
+                decode32_slow(mBj, word_at, bitB, BITS, pB, csp, eb);
+                bitA += BITS * __popc(mAj);
+                bitB += BITS * __popc(mBj);
 #pragma unroll
                 for (int b = 0; b < MT; ++b) {
                     const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * j);
@@ -438,10 +599,33 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         }
 
         __syncwarp();
-        if (issued < n) { issue(issued, st); ++issued; }       // tile i + stages reuses the slot just drained
+        if (issued < n) { issue(issued, st, true); ++issued; }       // tile i + stages reuses the slot just drained
     }
+    if (healthy && busy) finish_block(cur_rb);
+
+    // ---- row blocks shared by warps of this CTA only: first holder adds the parked fragments in warp order
+    __syncthreads();
     if (!healthy) return;
-    flush(cur_rb);
+    const int lane_tag = red_tag[lane];                                // GEMV_WARPS * 2 == 32 slots: one per lane
+#pragma unroll 1
+    for (int side = 0; side < 2; ++side) {
+        const int slot_id = warp * 2 + side;
+        const int tag = __shfl_sync(full, lane_tag, slot_id);
+        if (tag < 0) continue;
+        uint32_t holders = __ballot_sync(full, lane_tag == tag);       // parked fragments of this row block, in warp order
+        if ((int)__ffs(holders) - 1 != slot_id) continue;              // only the first holder reduces
+        clear_acc();
+        while (holders) {
+            const int k = __ffs(holders) - 1;
+            holders &= holders - 1u;
+            const float* src = red + k * FR;
+#pragma unroll
+            for (int b = 0; b < MT; ++b)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
+        }
+        store_rows(tag);
+    }
 }
 
 }  // namespace cb

@@ -129,6 +129,68 @@ int main() {
                 if (extract_code(st.data(), pos, bits) != want) ++fails;
             }
     }
+    // 5. decode8 on the raw `bits`-wide stream (no nibble re-pack), every mask byte, and the literal slow path
+    for (int bits = 2; bits <= 4; ++bits) {
+        const int top = (1 << bits) - 1;
+        for (int iter = 0; iter < 40000; ++iter) {
+            const uint32_t mb = (iter < 256) ? (uint32_t)iter : (rng() & 0xFFu);
+            int codes[8];
+            uint64_t stream = 0;
+            int r = 0;
+            for (int b = 0; b < 8; ++b) {
+                codes[b] = 0;
+                if ((mb >> b) & 1) { codes[b] = rng() % (top + 1); stream |= (uint64_t)codes[b] << (bits * r); ++r; }
+            }
+            stream |= ((uint64_t)rng() << 32 | rng()) << (bits * r);                 // garbage after the survivors
+            const float s = ((rng() % 10000) / 10000.0f) * 0.01f + 0.0007f;
+            const float z = (float)(rng() % (top + 1));
+            SegParams p = make_seg_params(float_to_half_bits((iter & 1) ? -s : s) | (float_to_half_bits(z) << 16), bits, false);
+            if (!p.fast) { ++fails; continue; }
+            const Lut4 e = make_lut4(lut1[mb], bits);
+            if (e.amt != (uint32_t)(bits * r)) ++fails;
+            uint32_t out[4];
+            const uint32_t w0 = (uint32_t)stream;
+            if (bits == 2) decode8<2>(w0, e.selA, e.selB, e.self, p, out);
+            else if (bits == 3) decode8<3>(w0, e.selA, e.selB, e.self, p, out);
+            else decode8<4>(w0, e.selA, e.selB, e.self, p, out);
+            for (int b = 0; b < 8; ++b) {
+                const uint32_t got = (out[b / 2] >> (16 * (b & 1))) & 0xFFFFu;
+                const float keepf = (float)((mb >> b) & 1);
+                const uint32_t want = float_to_bf16_bits(dequant_fp32((float)codes[b], p.z, p.s, 1.0f) * keepf);
+                const bool same = got == want || (((got | want) & 0x7FFFu) == 0);
+                if (!same) {
+                    if (fails < 10) printf("decode8 mismatch bits=%d mb=%02x b=%d got %04x want %04x\n", bits, mb, b, got, want);
+                    ++fails;
+                }
+            }
+        }
+        for (int iter = 0; iter < 4000; ++iter) {                                    // decode32_slow
+            uint32_t m = rng() & rng();
+            if (iter % 7 == 0) m = 0xFFFFFFFFu;
+            std::vector<uint32_t> st(8, 0);
+            const uint32_t start = rng() % 64;
+            int codes[32];
+            uint32_t bp = start;
+            for (int b = 0; b < 32; ++b) {
+                codes[b] = 0;
+                if ((m >> b) & 1) {
+                    codes[b] = rng() % (top + 1);
+                    for (int i = 0; i < bits; ++i) if ((codes[b] >> i) & 1) st[(bp + i) >> 5] |= 1u << ((bp + i) & 31);
+                    bp += bits;
+                }
+            }
+            const float s = 0.003f, z = (iter & 1) ? -3.0f : 2.5f;
+            SegParams p = make_seg_params(float_to_half_bits(s) | (float_to_half_bits(z) << 16), bits, false);
+            uint32_t out[16];
+            decode32_slow(m, [&](uint32_t i) { return st[i]; }, start, bits, p, nullptr, out);
+            for (int b = 0; b < 32; ++b) {
+                const uint32_t got = (out[b / 2] >> (16 * (b & 1))) & 0xFFFFu;
+                const float keepf = (float)((m >> b) & 1);
+                const uint32_t want = float_to_bf16_bits(dequant_fp32((float)codes[b], p.z, p.s, 1.0f) * keepf);
+                if (!(got == want || (((got | want) & 0x7FFFu) == 0))) ++fails;
+            }
+        }
+    }
     if (fails) { printf("FAILED: %d mismatches\n", fails); return 1; }
     printf("OK\n");
     return 0;
