@@ -9,7 +9,7 @@ import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("COBALT_B200_LIB") or os.path.join(HERE, "libcobalt_b200.so")   # override: experiments only
+LIB_PATH = os.path.join(HERE, "libcobalt_b200.so")
 
 
 class CobaltMat(Structure):
@@ -43,6 +43,8 @@ EXPORTS = {
     "cobalt_gemv_fused": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                   c_void_p]),
     "cobalt_gemv_fused_scratch_bytes": (c_size_t, [c_int, c_void_p, c_int]),
+    "cobalt_gemv_fused_prefetch": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                           c_size_t, c_int, c_void_p, c_void_p, c_void_p]),
     "cobalt_gemv_rowwalk": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                     c_void_p]),
     "cobalt_gemm": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p,
@@ -67,7 +69,6 @@ EXPORTS = {
     "cobalt_allreduce_peer": (c_int, [c_void_p, c_int, c_int, c_size_t, c_size_t, c_size_t, c_void_p, c_int, c_void_p,
                                       c_void_p]),
     "cobalt_device_status": (c_int, [c_void_p, c_void_p, POINTER(c_uint32)]),
-    "cobalt_set_tuning": (c_int, [c_int, c_int]),
 }
 
 _lib = None

@@ -20,10 +20,16 @@ constexpr int MAX_DEVICES = 64;
 int g_num_sms[MAX_DEVICES];
 int g_cc_major[MAX_DEVICES];
 bool g_dev_known[MAX_DEVICES];
+// Launch heuristics can be overridden for experiments when the library is built with -DCOBALT_TUNING_HOOKS
+// (cobalt_set_tuning is then exported); the product build has no such state.
+#ifdef COBALT_TUNING_HOOKS
 int g_tune_tiles_per_split = 0;     // 0 = heuristic
 int g_tune_gemv_stages = 0;
 int g_tune_gemm_stages = 0;
 int g_tune_gemv_mode = 0;           // 0 = heuristic, 1 = CTAs hold whole row blocks, 2 = balanced words
+#else
+constexpr int g_tune_tiles_per_split = 0, g_tune_gemv_stages = 0, g_tune_gemm_stages = 0, g_tune_gemv_mode = 0;
+#endif
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -100,12 +106,15 @@ int gemv_config(const GemvGeom& g, int N, int M, int num_sms, GemvCfg* c) {
     c->smem = fixed + c->xs_bytes + (size_t)GEMV_WARPS * stages * c->slot;
     // Persistent grid, at most one CTA per SM.  Preferred: every CTA holds whole row blocks, so that no partial sums
     // cross CTAs - the grid is the smallest one that reaches the minimal number of row blocks per CTA.  When that
-    // leaves more than 15 % of the machine idle (few, long row blocks), the words are balanced over all SMs instead
-    // and the blocks that straddle CTAs are exchanged through global scratch.
+    // leaves much of the machine idle (few, long row blocks), the words are balanced over all SMs instead and the
+    // blocks that straddle CTAs are exchanged through global scratch.
     const long tiles = (long)RB * CT;
     const long per_cta = (RB + num_sms - 1) / num_sms;                  // row blocks of the busiest CTA
     long grid = (RB + per_cta - 1) / per_cta;
-    bool aligned = (double)RB / ((double)per_cta * num_sms) >= 0.85;
+    // words per warp either way; the exchange of the straddling blocks costs about as much as five words
+    const double words_aligned = (double)per_cta * CT * TILE_WORDS / GEMV_WARPS;
+    const double words_balanced = (double)tiles * TILE_WORDS / ((double)num_sms * GEMV_WARPS) + 5.0;
+    bool aligned = words_aligned <= words_balanced;
     if (g_tune_gemv_mode == 1) aligned = true;
     if (g_tune_gemv_mode == 2) aligned = false;
     if (!aligned) grid = num_sms;
@@ -125,7 +134,7 @@ int gemv_config(const GemvGeom& g, int N, int M, int num_sms, GemvCfg* c) {
     // its counters to zero; neither ever sees the other's partial sums where it expects counters)
     c->partials_off = c->counters_off + round_up((size_t)RB * 4, 256);
     if (c->partials_off < SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES) c->partials_off = SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES;
-    c->total = c->partials_off + (size_t)c->total_warps * 2 * 4 * c->mt * 32 * sizeof(float);
+    c->total = c->partials_off + (size_t)grid * 2 * 4 * c->mt * 32 * sizeof(float);      // one subtotal per CTA and side
     return COBALT_OK;
 }
 
@@ -232,8 +241,10 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
 // shared body of every GEMV entry point: `n` matrices that share x, N and the bit width
 struct GemvOut { void* y; int64_t ldy; const void* bias; };
 
+struct GemvNext { int n; const void* const* ptr; const size_t* bytes; };
+
 int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void* x, int64_t ldx, int M, bool fp32_out,
-                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream) {
+                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, const GemvNext* next = nullptr) {
     if (n < 1 || n > GEMV_MAX_MATS || !w || !out) return COBALT_EINVAL;
     if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
     GemvGeom g = {};
@@ -285,6 +296,22 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.slot_bytes = c.slot; P.xs_bytes = c.xs_bytes;
     P.total_warps = c.total_warps;
     P.aligned = c.aligned ? 1 : 0;
+    if (next) {                                              // L2 prefetch hint: split every range evenly over the warps of the grid
+        if (next->n < 0 || next->n > GEMV_MAX_MATS || (next->n > 0 && (!next->ptr || !next->bytes))) return COBALT_EINVAL;
+        size_t budget = COBALT_PREFETCH_MAX_BYTES;
+        for (int k = 0; k < next->n; ++k) {
+            if (!next->ptr[k] || ((uintptr_t)next->ptr[k] & 15)) return COBALT_EINVAL;
+            size_t b = next->bytes[k] & ~(size_t)15;
+            if (b > budget) b = budget;
+            budget -= b;
+            if (b == 0) continue;
+            const size_t chunk = round_up((b + c.total_warps - 1) / c.total_warps, 128);
+            P.pf_ptr[P.n_pf] = (const uint8_t*)next->ptr[k];
+            P.pf_bytes[P.n_pf] = b;
+            P.pf_chunk[P.n_pf] = (uint32_t)chunk;
+            ++P.n_pf;
+        }
+    }
     P.part_q = c.part_q; P.part_r = c.part_r;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
@@ -335,8 +362,9 @@ const char* cobalt_strerror(int status) {
     }
 }
 
-// Tuning hook for benchmarks: key 0 = GEMV grid size, 1 = GEMV ring stages, 2 = GEMM split-K factor;
-// value 0 restores the heuristic.  Not part of the stable contract.
+#ifdef COBALT_TUNING_HOOKS
+// Experiment hook: key 0 = GEMV grid size, 1 = GEMV ring stages, 2 = GEMM split-K factor, 3 = GEMV partition
+// (1 = whole row blocks per CTA, 2 = balanced words); value 0 restores the heuristic.
 int cobalt_set_tuning(int key, int value) {
     if (value < 0) return COBALT_EINVAL;
     switch (key) {
@@ -347,6 +375,7 @@ int cobalt_set_tuning(int key, int value) {
         default: return COBALT_EINVAL;
     }
 }
+#endif
 
 size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M) {
     int sms = 0;
@@ -417,6 +446,16 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
     GemvOut o[GEMV_MAX_MATS];
     for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
     return gemv_launch(n_mats, w, o, x, ldx, M, false, scratch, scratch_bytes, false, stream);
+}
+
+int cobalt_gemv_fused_prefetch(int n_mats, const CobaltMat* const* w, const void* x, int64_t ldx, void* const* y,
+                               const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
+                               int n_next, const void* const* next_ptr, const size_t* next_bytes, void* stream) {
+    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !y || !ldy) return COBALT_EINVAL;
+    GemvOut o[GEMV_MAX_MATS];
+    for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
+    const GemvNext nx = {n_next, next_ptr, next_bytes};
+    return gemv_launch(n_mats, w, o, x, ldx, M, false, scratch, scratch_bytes, false, stream, &nx);
 }
 
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
@@ -656,7 +695,14 @@ int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int ac
 }
 
 int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out) {
-    if (!scratch || !status_out) return COBALT_EINVAL;
+    if (!status_out) return COBALT_EINVAL;
+    if (!scratch) {                                          // the status word of cobalt_gemv_static()'s private array
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return COBALT_ELAUNCH;
+        if (dev < 0 || dev >= MAX_DEVICES) return COBALT_EINVAL;
+        if (!g_static_scratch_ptr[dev]) { *status_out = 0; return COBALT_OK; }      // never used on this device: nothing to report
+        scratch = g_static_scratch_ptr[dev];
+    }
     cudaStream_t st = (cudaStream_t)stream;
     if (cudaMemcpyAsync(status_out, scratch, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
     if (cudaStreamSynchronize(st) != cudaSuccess) return COBALT_ELAUNCH;

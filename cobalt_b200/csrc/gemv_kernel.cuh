@@ -84,6 +84,12 @@ struct GemvParams {
     uint32_t total_warps;                // grid * GEMV_WARPS
     int aligned;                         // CTAs hold whole row blocks (no exchange between CTAs)
     uint32_t part_q, part_r;             // partition quotient and remainder, see cta_range_start()
+    // byte ranges the next kernel on the stream will read (a hint): every warp asks L2 for `pf_chunk[k]` bytes of
+    // range k at offset (global warp index) * pf_chunk[k] once it has requested its own last tile
+    const uint8_t* pf_ptr[GEMV_MAX_MATS];
+    uint64_t pf_bytes[GEMV_MAX_MATS];
+    uint32_t pf_chunk[GEMV_MAX_MATS];
+    int n_pf;
     float* partials;                     // [grid][2][4 * MT * 32]: CTA subtotals of straddling row blocks
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
@@ -134,6 +140,9 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     uint64_t p; asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p)); return p;
+}
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {      // p 16-byte aligned, bytes % 16 == 0
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ uint32_t ldg_hint(const uint32_t* p, uint64_t pol) {
     uint32_t v; asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol)); return v;
@@ -245,7 +254,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 
     uint8_t* ring_p = after_x + GEMV_BAR_BYTES + GEMV_REDCNT_BYTES + gemv_red_bytes(MT) + (size_t)warp * P.stages * P.slot_bytes;
     const uint32_t ring = smem_u32(ring_p);
-    const uint4* lut_lane = lut_s + (lane & (GEMV_LUT_COPIES - 1));
+    const uint32_t lut_lane = smem_u32(lut_s) + (uint32_t)(lane & (GEMV_LUT_COPIES - 1)) * 16u;      // this lane's replica
+    const uint32_t xs32 = smem_u32(xs);                               // 256-byte aligned: the swizzle is XORed into addresses
 
     auto issue = [&](int i, int slot_idx, bool drained) {              // all lanes call; lane 0 acts
         const uint8_t* base;
@@ -438,6 +448,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
+        if (i == n - 1 && P.n_pf > 0 && lane == 0) {                   // own stream fully requested: pull the next kernel's head into L2
+            const uint64_t gwarp = (uint64_t)blockIdx.x * GEMV_WARPS + (uint64_t)warp;
+#pragma unroll
+            for (int k = 0; k < GEMV_MAX_MATS; ++k) {
+                if (k >= P.n_pf) break;
+                const uint64_t off = gwarp * P.pf_chunk[k];
+                if (off < P.pf_bytes[k]) {
+                    const uint64_t left = P.pf_bytes[k] - off;
+                    l2_prefetch_bulk(P.pf_ptr[k] + off, left < P.pf_chunk[k] ? (uint32_t)left : P.pf_chunk[k]);
+                }
+            }
+        }
         if (rev) { if (--ct < 0) { ct = CT - 1; --rb; } }
         else if (++ct == CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {
@@ -452,15 +474,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         int w = P.G - TILE_GROUPS * ct;
         if (w > TILE_GROUPS) w = TILE_GROUPS;
         const bool active = t < w;
-        const uint8_t* slot = ring_p + (size_t)st * P.slot_bytes;
+        const uint32_t slot = ring + (uint32_t)st * P.slot_bytes;      // shared-window address of the tile
         const int segA = g * w + t, segB = (g + 8) * w + t;
         uint4 mA = make_uint4(0, 0, 0, 0), mB = make_uint4(0, 0, 0, 0);
         uint32_t szA = 0, szB = 0;
         if (active) {
-            mA = *reinterpret_cast<const uint4*>(slot + segA * 16);
-            mB = *reinterpret_cast<const uint4*>(slot + segB * 16);
-            szA = *reinterpret_cast<const uint32_t*>(slot + TILE_ROWS * w * 16 + segA * 4);
-            szB = *reinterpret_cast<const uint32_t*>(slot + TILE_ROWS * w * 16 + segB * 4);
+            mA = lds128(slot + segA * 16);
+            mB = lds128(slot + segB * 16);
+            szA = lds32(slot + TILE_ROWS * w * 16 + segA * 4);
+            szB = lds32(slot + TILE_ROWS * w * 16 + segB * 4);
         }
         const uint32_t cntA = __popc(mA.x) + __popc(mA.y) + __popc(mA.z) + __popc(mA.w);
         const uint32_t cntB = __popc(mB.x) + __popc(mB.y) + __popc(mB.z) + __popc(mB.w);
@@ -475,7 +497,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         const uint32_t exc = inc - v;
         uint32_t bitA = (exc & 0xFFFFu) * BITS;                        // bit offset of the lane's first code, row A / row B
         uint32_t bitB = ((tot & 0xFFFFu) + (exc >> 16)) * BITS;
-        const uint32_t* cw = reinterpret_cast<const uint32_t*>(slot + TILE_ROWS * w * 20);   // code stream of the tile
+        const uint32_t cw = slot + TILE_ROWS * w * 20;                 // code stream of the tile
         for (int r = 0; r < ja; ++r) {                                 // skip the words in front of the range
             bitA += BITS * __popc(mA.x); bitB += BITS * __popc(mB.x);
             mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
@@ -497,7 +519,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         const uint16_t* xrow[MT];
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
-            xs_lane[b] = (uint32_t)tok[b] * x_row_bytes + (uint32_t)col0 * 2u + ((uint32_t)((t & 3) | ((tok[b] & 1) << 2)) << 4);
+            xs_lane[b] = xs32 + (uint32_t)tok[b] * x_row_bytes + (uint32_t)col0 * 2u + ((uint32_t)((t & 3) | ((tok[b] & 1) << 2)) << 4);
             xrow[b] = P.x + (size_t)tok[b] * P.ldx + col0;
         }
 
@@ -505,20 +527,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             // ---- request everything unit `u` (16 columns: half h of mask word j) needs
             auto load_unit = [&](uint32_t m16A, uint32_t m16B, uint32_t bA, uint32_t bB, int j, int h) {
                 GemvUnit<MT> Un;
-                const uint32_t* pa = cw + (bA >> 5);
-                const uint32_t* pb = cw + (bB >> 5);
-                Un.ra0 = pa[0]; Un.ra1 = pa[1]; Un.ra2 = BITS == 2 ? 0u : pa[2];
-                Un.rb0 = pb[0]; Un.rb1 = pb[1]; Un.rb2 = BITS == 2 ? 0u : pb[2];
-                Un.ea0 = lut_lane[(m16A & 0xFFu) * GEMV_LUT_COPIES];
-                Un.ea1 = lut_lane[(m16A >> 8) * GEMV_LUT_COPIES];
-                Un.eb0 = lut_lane[(m16B & 0xFFu) * GEMV_LUT_COPIES];
-                Un.eb1 = lut_lane[(m16B >> 8) * GEMV_LUT_COPIES];
+                const uint32_t pa = cw + ((bA >> 5) << 2), pb = cw + ((bB >> 5) << 2);
+                Un.ra0 = lds32(pa); Un.ra1 = lds32(pa + 4); Un.ra2 = BITS == 2 ? 0u : lds32(pa + 8);
+                Un.rb0 = lds32(pb); Un.rb1 = lds32(pb + 4); Un.rb2 = BITS == 2 ? 0u : lds32(pb + 8);
+                Un.ea0 = lds128(lut_lane + (m16A & 0xFFu) * (GEMV_LUT_COPIES * 16u));
+                Un.ea1 = lds128(lut_lane + (m16A >> 8) * (GEMV_LUT_COPIES * 16u));
+                Un.eb0 = lds128(lut_lane + (m16B & 0xFFu) * (GEMV_LUT_COPIES * 16u));
+                Un.eb1 = lds128(lut_lane + (m16B >> 8) * (GEMV_LUT_COPIES * 16u));
 #pragma unroll
                 for (int b = 0; b < MT; ++b) {
                     if (XS) {
                         const uint32_t jo = (uint32_t)j << 6;
-                        Un.x[b][0] = *reinterpret_cast<const uint4*>(xs + (xs_lane[b] ^ (jo | (uint32_t)(32 * h))));
-                        Un.x[b][1] = *reinterpret_cast<const uint4*>(xs + (xs_lane[b] ^ (jo | (uint32_t)(32 * h + 16))));
+                        Un.x[b][0] = lds128(xs_lane[b] ^ (jo | (uint32_t)(32 * h)));
+                        Un.x[b][1] = lds128(xs_lane[b] ^ (jo | (uint32_t)(32 * h + 16)));
                     } else {
                         const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * (j & 3) + 16 * h);   // j == 4: the unused look-ahead
                         Un.x[b][0] = __ldg(xp);
@@ -547,24 +568,35 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                 }
             };
 
-            GemvUnit<MT> cur = load_unit(mA.x & 0xFFFFu, mB.x & 0xFFFFu, bitA, bitB, ja, 0);
-#pragma unroll 1
-            for (int j = ja; j < jb; ++j) {
-                const uint32_t mAj = mA.x, mBj = mB.x;                 // rotate instead of indexing registers
-                mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
-                mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
+            // one word (two units) of both rows; `cur` arrives requested, the first unit of the next word leaves requested
+            auto do_word = [&](GemvUnit<MT>& cur, uint32_t mAj, uint32_t mBj, uint32_t mAn, uint32_t mBn, int j) {
                 const uint32_t bitA1 = bitA + BITS * __popc(mAj & 0xFFFFu), bitB1 = bitB + BITS * __popc(mBj & 0xFFFFu);
                 const GemvUnit<MT> nxt = load_unit(mAj >> 16, mBj >> 16, bitA1, bitB1, j, 1);
                 compute_unit(cur, bitA, bitB);
                 const uint32_t bitA2 = bitA + BITS * __popc(mAj), bitB2 = bitB + BITS * __popc(mBj);
                 // after the last word this requests a unit that is never expanded (harmless in-bounds reads)
-                cur = load_unit(mA.x & 0xFFFFu, mB.x & 0xFFFFu, bitA2, bitB2, j + 1, 0);
+                cur = load_unit(mAn & 0xFFFFu, mBn & 0xFFFFu, bitA2, bitB2, j + 1, 0);
                 compute_unit(nxt, bitA1, bitB1);
                 bitA = bitA2; bitB = bitB2;
+            };
+            GemvUnit<MT> cur = load_unit(mA.x & 0xFFFFu, mB.x & 0xFFFFu, bitA, bitB, ja, 0);
+            if (ja == 0 && jb == TILE_WORDS) {                         // whole tile: straight-line code, no register rotation
+                do_word(cur, mA.x, mB.x, mA.y, mB.y, 0);
+                do_word(cur, mA.y, mB.y, mA.z, mB.z, 1);
+                do_word(cur, mA.z, mB.z, mA.w, mB.w, 2);
+                do_word(cur, mA.w, mB.w, mA.w, mB.w, 3);
+            } else {
+#pragma unroll 1
+                for (int j = ja; j < jb; ++j) {
+                    const uint32_t mAj = mA.x, mBj = mB.x;             // rotate instead of indexing registers
+                    mA.x = mA.y; mA.y = mA.z; mA.z = mA.w;
+                    mB.x = mB.y; mB.y = mB.z; mB.z = mB.w;
+                    do_word(cur, mAj, mBj, mA.x, mB.x, j);
+                }
             }
         } else {
             // ---- literal fp32 path (off-grid zero points, column scale): one 32-column word at a time
-            auto word_at = [&](uint32_t k) { return cw[k]; };
+            auto word_at = [&](uint32_t k) { return lds32(cw + 4u * k); };
 #pragma unroll 1
             for (int j = ja; j < jb; ++j) {
                 const uint32_t mAj = mA.x, mBj = mB.x;

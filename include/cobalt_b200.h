@@ -72,9 +72,11 @@ const char* cobalt_strerror(int status);
  * and, above it, SparseQuantLinear.forward for small batches (benchmarks/benchmark_suite.py:1200-1217).
  * `scratch` holds split-K partial sums and per-row-block arrival counters; it must be at least
  * cobalt_gemv_scratch_bytes() bytes, 256-byte aligned and ZERO before its first use (the kernel
- * leaves the counters zero again).  Calls sharing one scratch buffer must not overlap on the GPU,
- * and a buffer must not be shared between cobalt_gemv() and cobalt_gemm() without re-zeroing it
- * (their counters are laid out differently). */
+ * leaves the counters zero again).  Calls sharing one scratch buffer must not overlap on the GPU.
+ * One zeroed buffer may serve cobalt_gemv() and cobalt_gemm() calls in any order as long as the matrix has at most
+ * 16384 row blocks (K <= 262144): both kernels keep their arrival counters in the first 64 KB behind the status
+ * word and return them to zero, and neither reads partial sums it has not written.  Taller matrices need a
+ * buffer per kernel. */
 int cobalt_gemv(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy,
                 const void* bias, int M, void* scratch, size_t scratch_bytes, void* stream);
 size_t cobalt_gemv_scratch_bytes(const CobaltMat* w, int M);
@@ -89,6 +91,20 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
                       const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
                       void* stream);
 size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, int M);
+
+/* cobalt_gemv_fused() (n_mats = 1 gives cobalt_gemv()) with a hint for the memory system: up to 4 byte ranges that the
+ * NEXT kernel on the stream will stream, typically the tile images (tile_off table and tiles) of the next projection.
+ * Every warp, once it has requested the last tile of its own share, asks L2 for an equal slice of those ranges
+ * (cp.async.bulk.prefetch.L2), so that the next launch finds its offset tables and first tiles in L2 instead of paying a
+ * DRAM round trip with all warps at once.  The decode of a launch leaves most of the DRAM bandwidth unused, so the
+ * transfer costs this launch nothing.  Purely a hint: results do not depend on it, nothing waits for it, and at most
+ * COBALT_PREFETCH_MAX_BYTES are requested per launch (beyond that the ranges are cut short).  Pointers 16-byte aligned.
+ * No counterpart in the reference: its decode step is one persistent kernel whose phases follow each other without a
+ * launch boundary (src/cobaltkernel/csrc/megakernel.cu), so there is no cold start per projection to hide. */
+#define COBALT_PREFETCH_MAX_BYTES ((size_t)48 << 20)
+int cobalt_gemv_fused_prefetch(int n_mats, const CobaltMat* const* w, const void* x, int64_t ldx, void* const* y,
+                               const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
+                               int n_next, const void* const* next_ptr, const size_t* next_bytes, void* stream);
 
 /* cobalt_gemv() for callers that must not allocate device memory.
  *
@@ -105,6 +121,8 @@ size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, in
  *   - A matrix whose split-K bookkeeping does not fit the array is refused with
  *     COBALT_ETOOBIG; nothing is launched.  (The need grows with the number of row blocks;
  *     every 7B- and 27B-class projection, 262144-row heads included, fits.)
+ *   - A bounded wait that gave up leaves its code in the array's status word; cobalt_device_status(NULL, ...)
+ *     reads it.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on
  *     each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current) -- make that first call outside any stream capture.
@@ -214,13 +232,10 @@ int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t
                           size_t flags_off_bytes, void* out, int out_fp32, void* status, void* stream);
 
 /* Status word written by device code when a bounded wait gives up (0 = healthy).  Reads the
- * word at the start of `scratch` region reserved for it; synchronises `stream`. */
+ * word at the start of `scratch` region reserved for it; synchronises `stream`.  scratch = NULL reads the word of
+ * cobalt_gemv_static()'s private array on the current device (a copy from a cached address: nothing is allocated);
+ * that word is cleared by every cobalt_gemv_static() call, so ask before the next one. */
 int cobalt_device_status(const void* scratch, void* stream, uint32_t* status_out);
-
-/* Benchmark tuning hook (not part of the stable contract): key 0 = GEMV grid size
- * (CTAs), 1 = GEMV ring stages, 2 = GEMM split-K factor; value 0 restores the built-in heuristic.
- * No counterpart in the reference, whose knobs are compile-time macros (src/cobaltkernel/runner.py:52-206). */
-int cobalt_set_tuning(int key, int value);
 
 #ifdef __cplusplus
 }

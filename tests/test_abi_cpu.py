@@ -45,7 +45,6 @@ def test_argument_validation_without_gpu(lib):
     assert lib.cobalt_unpack(None, None, None, None) == -1
     m.tiles, m.tile_off, m.K, m.N, m.bits, m.group = 4096, 4096, 16, 100, 4, 128
     assert lib.cobalt_dequant(ctypes.byref(m), None, None) == -1      # N not a multiple of 128
-    assert lib.cobalt_set_tuning(9, 1) == -1
 
 
 def test_decoder_core_host_build(tmp_path):

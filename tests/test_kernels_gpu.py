@@ -22,6 +22,8 @@ pytestmark = pytest.mark.gpu
 
 MAX_ABS = 1e-2
 REL_L2 = 1e-3
+MAX_EXEMPT = 0.01          # largest share of elements that may differ by more than MAX_ABS as rounding-boundary cases
+EXEMPT = []                # (exempted, total) of every comparison that used the exemption, for the summary test
 
 
 def bf16_spacing(v: torch.Tensor) -> torch.Tensor:
@@ -44,6 +46,12 @@ def check_output(y: torch.Tensor, y_ref: torch.Tensor, y_exact: torch.Tensor):
             err = (val - ex).abs()
             lim = 0.52 * bf16_spacing(val)
             assert bool((err <= lim).all()), f"{name}: {int(bad.sum())} elements off by more than {MAX_ABS} and not a rounding-boundary case"
+        # the exemption is for isolated rounding-boundary flips, not for a result that is systematically one
+        # spacing off: at most MAX_EXEMPT of the elements may take it (a handful of elements for tiny outputs)
+        frac = float(bad.sum()) / bad.numel()
+        EXEMPT.append((int(bad.sum()), bad.numel()))
+        print(f"rounding-boundary exemptions: {int(bad.sum())} of {bad.numel()} ({100 * frac:.3f} %)")
+        assert int(bad.sum()) <= max(4, int(MAX_EXEMPT * bad.numel())), f"{int(bad.sum())} of {bad.numel()} elements exempted"
     return rel, float(d.max())
 
 
@@ -181,6 +189,39 @@ def test_gemv_reference_test_shapes(K, N):
     for M in (1, 2, 4, 8):
         x = O.seeded_activation(M, N, K + M)
         check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+
+
+@pytest.mark.parametrize("K,N,bits", [(512, 14336, 4), (1024, 28672, 3)])
+def test_gemv_balanced_partition_long_rows(K, N, bits):
+    """Few, long row blocks: the launch balances 32-column words over all SMs and the row blocks that straddle
+    CTAs are exchanged through global scratch (about 1.5 and 6 words per warp here)."""
+    raw = O.synth_raw(K, N, 0.5, bits, seed=K + N + bits)
+    mod = to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], bits)
+    Wb = O.dequantize(raw["q"], raw["scale"], raw["zero"], raw["keep"]).to(torch.bfloat16)
+    for M in (1, 3, 8, 16):
+        x = O.seeded_activation(M, N, K + M)
+        y = mod(x.cuda())
+        check_output(y, torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
+        assert torch.equal(y, mod(x.cuda()))              # the exchange order is fixed: same bits every run
+    assert mod.device_status() == 0
+
+
+def test_gemv_prefetch_hint_changes_nothing():
+    """cobalt_gemv_fused_prefetch: the L2 hint for the next launch leaves the results bit-identical."""
+    from cobalt_b200 import FusedProjections
+    raws = [O.synth_raw(K, 2048, 0.5, 4, seed=900 + K) for K in (512, 128, 128)]
+    mods = [to_module(r["keep"], r["q"], r["scale"], r["zero"], 4) for r in raws]
+    nxt = to_module(*[O.synth_raw(256, 1024, 0.5, 4, seed=77)[k] for k in ("keep", "q", "scale", "zero")], 4)
+    x = O.seeded_activation(2, 2048, 5).cuda()
+    fused = FusedProjections(mods)
+    plain = fused(x)
+    fused.prefetch_next = [nxt]
+    hinted = fused(x)
+    assert all(torch.equal(a, b) for a, b in zip(plain, hinted))
+    single = mods[0](x)
+    mods[0].prefetch_next = [nxt, mods[1]]
+    assert torch.equal(single, mods[0](x))
+    assert torch.equal(single, plain[0])
 
 
 # ----------------------------------------------------------------------------- benchmark configurations
@@ -498,3 +539,11 @@ def test_attn_decode_matches_torch(nh, nkv, D, ctx, pos, window):
     rel = float(d.norm() / ref.float().norm())
     assert rel <= 2e-3, rel
     assert float(d.abs().max()) <= 0.02 * float(ref.float().abs().max()), float(d.abs().max())
+
+
+def test_zz_exemption_summary():
+    """Collected after the other tests of this file: how often the rounding-boundary exemption was used."""
+    total = sum(t for _, t in EXEMPT)
+    used = sum(e for e, _ in EXEMPT)
+    print(f"rounding-boundary exemption used in {len(EXEMPT)} comparisons: {used} of {total} elements")
+    assert used <= max(16, int(MAX_EXEMPT * max(total, 1)))
