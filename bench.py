@@ -22,7 +22,13 @@ the 126 MB L2).
 With --gpus N > 1 (launched by torch.distributed.run) the run is tensor-parallel with the work
 per GPU held fixed (weak scaling): every rank streams one shard with the 7B block's shapes of
 a block N times as wide - q/k/v/gate/up split by output rows (no exchange), o/down split by
-input columns, their fp32 partial sums all-reduced over NCCL once per layer and rounded once.
+input columns, their fp32 partial sums all-reduced once per layer (the library's peer-memory kernel; NCCL with
+--nccl-allreduce or when the symmetric buffer cannot be set up) and rounded once.  The end-to-end leg of a
+multi-GPU run goes through the same tensor-parallel step, host copies included.
+
+The line also carries two short extra legs (single GPU, skipped with --no-extra): `prefill` - the tcgen05 GEMM on
+two 7B shapes at M = 128 and 2048 against the measured bf16 peak - and `model` - a reduced-depth (4-layer)
+Mistral-7B-shaped greedy decode with ms per layer and the 32-layer tokens/s extrapolated from it (labelled).
 """
 from __future__ import annotations
 
@@ -233,13 +239,20 @@ def run_ours(args):
         for b, f in zip(blocks, fuseds):                     # allocate scratch, configure kernels
             one_step(b, f)
         stream.synchronize()
-        graph = None
+        graph, step_graphs = None, []
         if not args.profile and not args.no_graph:
-            # the all-reduces of the tensor-parallel run are captured with the kernels (NCCL supports capture)
+            # the all-reduces of the tensor-parallel run are captured with the kernels (NCCL supports capture).
+            # One graph holds a step on every block copy; one more graph per copy serves step counts that are not a
+            # multiple of the number of copies, so that every timed (and warm-up) step is a replay.
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for b, f in zip(blocks, fuseds):
                     one_step(b, f)
+            for b, f in zip(blocks, fuseds):
+                gs = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gs, stream=stream):
+                    one_step(b, f)
+                step_graphs.append(gs)
 
         def run_steps(n):
             done = 0
@@ -247,6 +260,9 @@ def run_ours(args):
                 if graph is not None and n - done >= len(blocks):
                     graph.replay()
                     done += len(blocks)
+                elif step_graphs:
+                    step_graphs[done % len(blocks)].replay()
+                    done += 1
                 else:
                     one_step(blocks[done % len(blocks)], fuseds[done % len(blocks)])
                     done += 1
@@ -347,25 +363,55 @@ def run_ours(args):
     side = torch.cuda.Stream(dev)                            # the seven calls are independent: two streams let one
     e2e_streams = (stream, side)                             # call's copy-out overlap the next call's copy-in and kernel
 
-    def e2e_step(blk):
-        for i, (name, _, _) in enumerate(SHAPES_7B):
-            m = blk[name]
-            sp = (scr[name].data_ptr() + 255) // 256 * 256
-            rc = lib.cobalt_linear_host_async(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
-                                              xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
-                                              e2e_streams[i & 1].cuda_stream)
-            _lib.check("cobalt_linear_host_async", rc)
-        stream.synchronize()                                  # the caller reads the results: one wait per block
-        side.synchronize()
+    dx = {n: torch.empty_like(xs[n]) for n in xs}             # device staging of the tensor-parallel end-to-end step
+
+    def e2e_step(blk, fused):
+        if world == 1:
+            for i, (name, _, _) in enumerate(SHAPES_7B):
+                m = blk[name]
+                sp = (scr[name].data_ptr() + 255) // 256 * 256
+                rc = lib.cobalt_linear_host_async(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
+                                                  xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
+                                                  e2e_streams[i & 1].cuda_stream)
+                _lib.check("cobalt_linear_host_async", rc)
+            stream.synchronize()                              # the caller reads the results: one wait per block
+            side.synchronize()
+            return
+        # tensor parallel: the same step as the device-timed one (fused launches, fp32 partial sums of o and down
+        # all-reduced over the ranks), fed from pinned host activations and read back to pinned host outputs
+        with torch.cuda.stream(stream):
+            done = set()
+            for name in names:
+                if name in done:
+                    continue
+                dx[name].copy_(hx[name], non_blocking=True)
+                if name in fused_of:
+                    outs = fused[fused_of[name]](dx[name])
+                    for n2, o in zip(fused_of[name], outs):
+                        hy[n2].copy_(o, non_blocking=True)
+                    done.update(fused_of[name])
+                elif name in ROW_PARALLEL:
+                    if reducer is not None:
+                        n = M * info[name]["K"]
+                        blk[name](dx[name], out_fp32=True, out=reducer.slot_view(n))
+                        reducer.reduce(n, ys[name].view(-1))
+                    else:
+                        part = blk[name](dx[name], out_fp32=True)
+                        dist.all_reduce(part)
+                        ys[name].copy_(part)
+                    hy[name].copy_(ys[name], non_blocking=True)
+                else:
+                    hy[name].copy_(blk[name](dx[name]), non_blocking=True)
+        stream.synchronize()
 
     for i in range(3):
-        e2e_step(blocks[i % len(blocks)])
+        e2e_step(blocks[i % len(blocks)], fuseds[i % len(blocks)])
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        e2e_step(blocks[i % len(blocks)])
+        e2e_step(blocks[i % len(blocks)], fuseds[i % len(blocks)])
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     if dist is not None:
@@ -390,6 +436,8 @@ def run_ours(args):
                    "bytes_per_step": int(wbytes + abytes), "peak": peak_kind},
         "clocks": clocks,
         "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
+                "path": "cobalt_linear_host_async per projection, two streams, one wait per step" if world == 1 else
+                        "tensor-parallel step through the module API: pinned host x in, fused launches, all-reduce of o and down, pinned host y out",
                 "h2d_bytes_per_step": int(sum(M * v["N"] * 2 for v in info.values())),
                 "d2h_bytes_per_step": int(sum(M * v["K"] * 2 for v in info.values()))},
         "gpu_launches": int(args.steps * launches_per_step),
@@ -398,7 +446,7 @@ def run_ours(args):
                      # DRAM bytes per launch: 1.005 x algorithmic, from an ncu capture of the gate projection
                      # (24.03 MB read for 23.9 MB); traffic grows in proportion to the tiles streamed
                      "traffic": int(1.005 * (wbytes + abytes) / launches_per_step),
-                     "kernel": "gemv_mma_kernel<4,1>", "launches_per_step": launches_per_step,
+                     "kernel": f"gemv_mma_kernel<{BITS},{2 if M > 8 else 1},{'true' if M <= 8 else 'false'}>", "launches_per_step": launches_per_step,
                      "bytes_per_launch": int((wbytes + abytes) / launches_per_step)},
         "device_status": status,
         "per_shape": per_shape,
@@ -406,8 +454,84 @@ def run_ours(args):
     }
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(info, M, limit_s=15.0)
+        if not args.no_extra:
+            del blocks, fuseds, mods0
+            torch.cuda.empty_cache()
+            try:
+                out.update(extra_legs(dev))
+            except Exception as e:                            # noqa: BLE001 - the extra legs never take the headline line down
+                out["extra_legs_error"] = f"{type(e).__name__}: {e}"
     print(json.dumps(out), flush=True)
     _finish(dist)
+
+
+# ----------------------------------------------------------------------------- short extra legs of the default line
+def extra_legs(dev, steps=5):
+    """Two short single-GPU legs appended to the decode line: the tensor-bound prefill GEMM on two 7B shapes and a
+    reduced-depth model decode.  Both use seeded synthetic weights; every timed prefill launch follows an L2 flush."""
+    from cobalt_b200 import CobaltSparseLinear, SparseQuantConfig, compress_weight
+    from cobalt_b200.decoder import build_random_decoder
+    out = {}
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = json.load(open(p))["bf16_tflops"] if os.path.exists(p) else 1590.0
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    cases = []
+    for name, K, N in (("down", 4096, 14336), ("q", 4096, 4096)):
+        g = torch.Generator().manual_seed(4003)
+        W = (torch.randn(K, N, generator=g) * 0.02).half().float().to(dev)
+        norm = (torch.randn(N, generator=g).abs() + 0.1).to(dev)
+        keep, q, sc, zr = compress_weight(W, norm, SparseQuantConfig(3, 0.7, 0.5))
+        mod = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": 3})
+        del W, keep, q, sc, zr
+        for M in (2048, 128):
+            x = torch.randn(M, N, device=dev).to(torch.bfloat16)
+            for _ in range(3):
+                mod(x)
+            times = []
+            for _ in range(steps):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                mod(x)
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            ms = sorted(times)[len(times) // 2]
+            tf = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+            cases.append({"shape": name, "M": M, "bits": 3, "sparsity": 0.7, "ms": round(ms, 4), "tflops": round(tf, 1),
+                          "tensor_frac": round(tf / peak, 4), "status": mod.device_status()})
+        del mod
+    del flush
+    torch.cuda.empty_cache()
+    out["prefill"] = {"metric": "prefill GEMM TFLOP/s (dense-equivalent 2*M*K*N), 3-bit 70 % sparse", "peak_tflops": peak,
+                      "kernel": "gemm_tcgen05_kernel<3>", "l2": "256 MB flush before every timed launch", "cases": cases}
+    # reduced-depth model decode: 4 layers of the 7B shape (every layer its own copy of one set of seeded matrices)
+    layers, ctx, n_new = 4, 2048, 64
+    cfg = dict(model_type="mistral", hidden_size=4096, num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8,
+               head_dim=128, intermediate_size=14336, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=1e6, sliding_window=None)
+    dec = build_random_decoder(cfg, SparseQuantConfig(BITS, SPARSITY, BETA), ctx + n_new + 8, dev, clone_first_layer=True)
+    g = torch.Generator().manual_seed(2048)
+    prompt = torch.randint(0, cfg["vocab_size"], (ctx,), generator=g)
+    dec.generate(prompt, 4, use_graph=True)
+    torch.cuda.synchronize()
+    dec.pos.fill_(ctx)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_new):
+        dec._graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms4 = e0.elapsed_time(e1) / n_new
+    ms_head = dec.time_head_ms()
+    ms_layer = max(ms4 - ms_head, 0.0) / layers
+    out["model"] = {"metric": "Mistral-7B-shape greedy decode, batch 1, context 2048", "layers_run": layers,
+                    "ms_per_token_4_layers": round(ms4, 4), "ms_head_and_embedding": round(ms_head, 4), "ms_per_layer": round(ms_layer, 4),
+                    "tokens_per_s_32_layers_extrapolated": round(1e3 / (32 * ms_layer + ms_head), 1),
+                    "note": "extrapolated from 4 layers: 32 * ms_per_layer + head; the full-depth run is `--workload model`",
+                    "status": max(m.device_status() for m in dec.lin.values())}
+    del dec
+    torch.cuda.empty_cache()
+    return out
 
 
 # ----------------------------------------------------------------------------- CPU arm (reference path)
@@ -655,6 +779,7 @@ def main():
     ap.add_argument("--model", default="mistral7b", choices=["mistral7b", "gemma27b"], help="shape of --workload model")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: use NCCL instead of the peer-memory all-reduce kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
+    ap.add_argument("--no-extra", action="store_true", help="skip the short prefill and reduced-depth model legs of the default line")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")
     args = ap.parse_args()

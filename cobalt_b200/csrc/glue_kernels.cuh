@@ -90,11 +90,13 @@ __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v
         const float x1 = bf16_to_float(src[d]), x2 = bf16_to_float(src[d + half]);
         const float o1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * s));
         const float o2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
+        if (!is_q && (pos < 0 || pos >= max_ctx)) return;              // a position outside the cache is never stored
         uint16_t* dst = is_q ? q + ((size_t)t * nh + head) * D
                              : k_cache + ((size_t)(head - nh) * max_ctx + (size_t)pos) * D;
         dst[d] = float_to_bf16(o1);
         dst[d + half] = float_to_bf16(o2);
     } else {
+        if (pos < 0 || pos >= max_ctx) return;
         const int hv = head - nh - nkv;
         const uint16_t* src = v + ((size_t)t * nkv + hv) * D;
         uint16_t* dst = v_cache + ((size_t)hv * max_ctx + (size_t)pos) * D;
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(256) rope_kv_norm_kernel(uint16_t* q, const ui
     if (wid >= (long long)T * heads) return;
     const int t = (int)(wid / heads), head = (int)(wid - (long long)t * heads);
     const long long pos = positions[t];
+    if (head >= nh && (pos < 0 || pos >= max_ctx)) return;             // a position outside the cache is never stored
     if (head >= nh + nkv) {                                            // v: plain copy into the cache
         const int hv = head - nh - nkv;
         const uint16_t* src = v + ((size_t)t * nkv + hv) * D;

@@ -276,10 +276,36 @@ class CobaltDecoder:
         return F.linear(x, head).unsqueeze(0)                                          # [1, T, V]
 
     @torch.no_grad()
+    def time_head_ms(self, reps: int = 20) -> float:
+        """Device time of what a decode step spends outside the blocks: embedding lookup, final norm, head, argmax."""
+        x = torch.zeros(1, self.cfg["hidden_size"], dtype=torch.bfloat16, device=self.dev)
+        head = self.P["model.embed_tokens.weight"] if self.gemma else self.P["lm_head.weight"]
+
+        def once():
+            h = self.P["model.embed_tokens.weight"].index_select(0, self.tok)
+            _, y = self._add_rmsnorm(h, None, self.P["model.norm.weight"])
+            return torch.argmax(F.linear(y + x, head).float(), dim=-1)
+
+        for _ in range(3):
+            once()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            once()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def _check_room(self, n_tokens: int, start: int = 0):
+        if start < 0 or start + n_tokens > self.max_ctx:
+            raise ValueError(f"{n_tokens} tokens from position {start} do not fit the KV cache of {self.max_ctx} slots")
+
+    @torch.no_grad()
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
         """Run the prompt, fill the cache, return logits [T, V]."""
         ids = ids.to(self.dev)
         T = ids.shape[0]
+        self._check_room(T)
         logits = self._forward(ids, torch.arange(T, device=self.dev), T)[0]
         self.pos.fill_(T)
         return logits
@@ -298,6 +324,7 @@ class CobaltDecoder:
         """Greedy continuation.  Returns (tokens [n_new] on the CPU, logits of every step [n_new, V]).
         With ``teacher`` (token ids), the fed-back token of step i is ``teacher[i]`` instead of the argmax
         (teacher-forced run, src/cobaltkernel/verify_kernel.py:288-339)."""
+        self._check_room(int(prompt.shape[0]) + n_new)       # the captured step advances the position on the device
         logits = self.prefill(prompt)
         first = torch.argmax(logits[-1].float(), dim=-1, keepdim=True)
         self.tok.copy_(first if teacher is None else teacher[0:1].to(self.dev))

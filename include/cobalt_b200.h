@@ -195,7 +195,8 @@ int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_hos
  *                        NULL) delta is first normalised the same way with (1 + w_branch) - the norm Gemma-3 applies to a
  *                        branch before it joins the residual.
  *   cobalt_rope_kv     : rotates q [T, n_heads*D] in place; rotates k and copies v [T, n_kv_heads*D] into the caches
- *                        [n_kv_heads][max_ctx][D] at positions[t]; inv_freq fp32 [D/2]; cos/sin rounded to bf16.  With
+ *                        [n_kv_heads][max_ctx][D] at positions[t] (a position outside [0, max_ctx) is read on the device
+ *                        and simply not stored); inv_freq fp32 [D/2]; cos/sin rounded to bf16.  With
  *                        q_norm_w / k_norm_w (bf16 [D], both or neither) q and k first get Gemma-3's per-head norm
  *                        bf16(x * rsqrt(mean_D(x^2) + eps) * (1 + w)) (src/cobaltkernel/ref_gemma3.py:181-185).
  *   cobalt_swiglu      : out = act(gate) * up over n elements; act 0 = SiLU, act 1 = GELU (tanh approximation).

@@ -64,3 +64,16 @@ def test_forward_refuses_cpu_tensor():
     mod = CobaltSparseLinear(q, sc, sc, keep, None, None, {"nbits": 4, "group_size": 128})
     with pytest.raises(RuntimeError):
         mod(torch.zeros(1, 128, dtype=torch.bfloat16))
+
+
+def test_decoder_refuses_more_tokens_than_cache_slots():
+    """The captured decode step advances the position on the device, so running past the KV cache is refused on the
+    host before anything is launched."""
+    from types import SimpleNamespace
+    from cobalt_b200.decoder import CobaltDecoder
+    d = SimpleNamespace(max_ctx=32)
+    CobaltDecoder._check_room(d, 32)
+    with pytest.raises(ValueError):
+        CobaltDecoder._check_room(d, 33)
+    with pytest.raises(ValueError):
+        CobaltDecoder._check_room(d, 8, start=30)

@@ -206,6 +206,30 @@ def test_gemv_balanced_partition_long_rows(K, N, bits):
     assert mod.device_status() == 0
 
 
+def test_gemv_scratch_survives_graph_replay_after_a_larger_batch():
+    """A graph captured at M = 1 keeps the scratch address: a later 12-token call must not move or dirty the buffer."""
+    raw = O.synth_raw(640, 2048, 0.5, 4, seed=5150)
+    mod = to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)
+    x1 = O.seeded_activation(1, 2048, 1).cuda()
+    x12 = O.seeded_activation(12, 2048, 2).cuda()
+    want = mod(x1).clone()
+    addr = mod._scratch["gemv"].data_ptr()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        y_static = mod(x1)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            y_static = mod(x1)
+    torch.cuda.current_stream().wait_stream(s)
+    y12 = mod(x12)                                            # larger batch between capture and replay
+    assert mod._scratch["gemv"].data_ptr() == addr
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y_static, want)
+    assert torch.equal(y12[:1], mod(x12[:1]))
+
+
 def test_gemv_prefetch_hint_changes_nothing():
     """cobalt_gemv_fused_prefetch: the L2 hint for the next launch leaves the results bit-identical."""
     from cobalt_b200 import FusedProjections
