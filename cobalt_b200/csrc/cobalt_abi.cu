@@ -75,7 +75,7 @@ struct GemvCfg {
     bool xs;                           // activations staged in shared memory
     bool aligned;                      // every CTA holds whole row blocks
     uint32_t slot, xs_bytes, total_warps, part_q, part_r;
-    size_t smem, counters_off, partials_off, total;
+    size_t smem, counters_off, partials_off, xperm_off, total;
 };
 
 // geometry shared by the matrices of one (possibly fused) GEMV launch
@@ -98,7 +98,8 @@ int gemv_config(const GemvGeom& g, int N, int M, int num_sms, GemvCfg* c) {
     const size_t xs_want = c->mt == 1 ? round_up((size_t)M * N * 2 + 64, 256) : 0;
     c->xs = xs_want != 0 && fixed + xs_want + (size_t)GEMV_WARPS * 2 * c->slot <= SMEM_LIMIT;
     c->xs_bytes = c->xs ? (uint32_t)xs_want : 0u;
-    int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : 3;
+    // without the staged copy the activations come through L1: a shallower ring leaves it more room
+    int stages = g_tune_gemv_stages > 0 ? g_tune_gemv_stages : (c->xs ? 3 : 2);
     if (stages > GEMV_MAX_STAGES) stages = GEMV_MAX_STAGES;
     while (stages > 1 && fixed + c->xs_bytes + (size_t)GEMV_WARPS * stages * c->slot > SMEM_LIMIT) --stages;
     if (fixed + c->xs_bytes + (size_t)GEMV_WARPS * stages * c->slot > SMEM_LIMIT) return COBALT_EINVAL;
@@ -134,7 +135,9 @@ int gemv_config(const GemvGeom& g, int N, int M, int num_sms, GemvCfg* c) {
     // its counters to zero; neither ever sees the other's partial sums where it expects counters)
     c->partials_off = c->counters_off + round_up((size_t)RB * 4, 256);
     if (c->partials_off < SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES) c->partials_off = SCRATCH_STATUS_BYTES + SCRATCH_COUNTER_BYTES;
-    c->total = c->partials_off + (size_t)grid * 2 * 4 * c->mt * 32 * sizeof(float);      // one subtotal per CTA and side
+    c->xperm_off = c->partials_off + round_up((size_t)grid * 2 * 4 * c->mt * 32 * sizeof(float), 256);    // one subtotal per CTA and side
+    // fragment-ordered activations of launches that cannot stage x: [column tiles][16 chunks][mt][32 lanes] x 16 bytes
+    c->total = c->xperm_off + (c->xs ? 0 : (size_t)CT * 16 * c->mt * 32 * 16);
     return COBALT_OK;
 }
 
@@ -291,6 +294,7 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.N = w[0]->N; P.G = w[0]->N / GROUP; P.CT = g.CT; P.RB = g.RB;
     P.col_scale = (const uint16_t*)w[0]->col_scale;
     P.x = (const uint16_t*)x; P.ldx = ldx;
+    P.xperm = (const uint4*)((uint8_t*)scratch + c.xperm_off);
     P.M = M;
     P.stages = c.stages;
     P.slot_bytes = c.slot; P.xs_bytes = c.xs_bytes;
@@ -316,6 +320,20 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);
+    if (!c.xs) {                                             // fragment-ordered copy of x, read by every warp of the GEMV
+        const int chunks = g.CT * 16 * c.mt * 32;
+        cudaLaunchConfig_t pc = {};
+        pc.gridDim = dim3((unsigned)((chunks + 255) / 256 < 4 * sms ? (chunks + 255) / 256 : 4 * sms));
+        pc.blockDim = dim3(256);
+        pc.stream = st;
+        cudaLaunchAttribute pattr[1];
+        pattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pattr[0].val.programmaticStreamSerializationAllowed = 1;
+        pc.attrs = pattr;
+        pc.numAttrs = 1;
+        if (cudaLaunchKernelEx(&pc, x_permute_kernel, (const uint16_t*)x, ldx, M, w[0]->N, g.CT, c.mt, (uint4*)((uint8_t*)scratch + c.xperm_off)) != cudaSuccess)
+            return COBALT_ELAUNCH;
+    }
     if (c.mt == 1 && c.xs) {
         switch (g.bits) {
             case 2: return launch_gemv<2, 1, true>(P, c, st);

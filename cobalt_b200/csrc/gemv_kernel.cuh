@@ -77,6 +77,7 @@ struct GemvParams {
     int N, G, CT, RB;                    // shared geometry; RB = row blocks of all matrices together
     const uint16_t* col_scale;           // single-matrix launches only
     const uint16_t* x; int64_t ldx;
+    const uint4* xperm;                  // activations in fragment order (see x_permute_kernel), used when x is not staged
     int M;
     int stages;
     uint32_t slot_bytes;
@@ -166,6 +167,26 @@ __device__ __forceinline__ uint4 gemv_lut_entry(uint32_t mb, int bits) {
     }
     return make_uint4(s[0] | (s[2] << 4) | (s[1] << 8) | (s[3] << 12), s[4] | (s[6] << 4) | (s[5] << 8) | (s[7] << 12),
                       rank == 8u ? 0x3210u : 0x4210u, rank * (uint32_t)bits);
+}
+
+// Activations in fragment order, for launches whose x does not fit into shared memory: chunk (ct, c, b, lane) holds the
+// 8 columns [512*ct + 128*t + 8*c, +8) of token min(g + 8*b, M-1), lane = 4*g + t, so that the 32 lanes of a warp read
+// 512 contiguous bytes per fragment load instead of 32 separate lines (the read-only path serves one line per cycle).
+// One thread per 16-byte chunk; columns beyond N (partial last tile) are zero.
+__global__ void x_permute_kernel(const uint16_t* __restrict__ x, int64_t ldx, int M, int N, int CT, int MT, uint4* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int total = CT * 16 * MT * 32;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int lane = i & 31, b = (i >> 5) % MT, c = ((i >> 5) / MT) & 15, ct = (i >> 5) / MT / 16;
+        const int g = lane >> 2, t = lane & 3;
+        int tok = g + 8 * b;
+        if (tok > M - 1) tok = M - 1;
+        const int col = 512 * ct + 128 * t + 8 * c;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (col < N) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)tok * ldx + col));
+        out[i] = v;
+    }
 }
 
 // what one unit (16 columns of both rows of a lane) reads from memory; requested one unit ahead
@@ -517,6 +538,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         // activations of this lane's group: staged copy (byte offset with the swizzle folded in) or global rows
         uint32_t xs_lane[MT];
         const uint16_t* xrow[MT];
+        const uint4* xfrag = P.xperm + (size_t)ct * 16 * MT * 32 + lane;       // this lane's chunks of the tile's columns
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             xs_lane[b] = xs32 + (uint32_t)tok[b] * x_row_bytes + (uint32_t)col0 * 2u + ((uint32_t)((t & 3) | ((tok[b] & 1) << 2)) << 4);
@@ -541,9 +563,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
                         Un.x[b][0] = lds128(xs_lane[b] ^ (jo | (uint32_t)(32 * h)));
                         Un.x[b][1] = lds128(xs_lane[b] ^ (jo | (uint32_t)(32 * h + 16)));
                     } else {
-                        const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + 32 * (j & 3) + 16 * h);   // j == 4: the unused look-ahead
+                        // fragment-ordered copy: chunk index 4*(j & 3) + 2*h (j == 4 is the unused look-ahead)
+                        const uint4* xp = xfrag + ((size_t)(4 * (j & 3) + 2 * h) * MT + b) * 32;
                         Un.x[b][0] = __ldg(xp);
-                        Un.x[b][1] = __ldg(xp + 1);
+                        Un.x[b][1] = __ldg(xp + MT * 32);
                     }
                 }
                 return Un;
