@@ -640,7 +640,7 @@ int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t
     if (!peer_base || !out || world < 1 || world > PEER_MAX_RANKS || rank < 0 || rank >= world) return COBALT_EINVAL;
     if (n == 0 || (n & 3) || n * sizeof(float) > slot_stride_bytes || n > 0xFFFFFFFFull) return COBALT_EINVAL;
     if (((uintptr_t)out & 15)) return COBALT_EINVAL;
-    if ((slot_stride_bytes & 15) || (flags_off_bytes & 15) || flags_off_bytes < 3 * slot_stride_bytes) return COBALT_EINVAL;
+    if ((slot_stride_bytes & 15) || (flags_off_bytes & 15) || flags_off_bytes < (size_t)(1 + 2 * world) * slot_stride_bytes) return COBALT_EINVAL;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;

@@ -339,14 +339,15 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* part, co
 }
 
 // ----------------------------------------------------------------------------- all-reduce over peer memory
-// Sum of the fp32 partial outputs of a row-parallel layer, one [n]-vector per GPU, read straight from the peers'
-// memory (NVLink loads), added in rank order and rounded to bf16 once.  Every rank runs this kernel (one CTA) on its
-// own GPU: it moves its partial from the staging area (where the GEMV wrote it) into slot (epoch & 1), publishes
-// "my partial of epoch e is written" in each peer's flag array, waits (bounded) until all peers have published epoch
-// e in its own flag array, then reads.  The epoch counter lives on the device, so replaying a captured graph
-// advances it like eager calls do.  Two slots alternate, so that a rank that is ahead never overwrites a partial
-// that a peer is still reading (a rank can only finish epoch e after every peer has started it, i.e. has finished
-// reading epoch e-1).
+// Sum of the fp32 partial outputs of a row-parallel layer, one [n]-vector per GPU, added in rank order and rounded
+// to bf16 once.  Every rank runs this kernel (one CTA) on its own GPU.  It PUSHES: the partial goes from the local
+// staging area (where the GEMV wrote it) into row `rank` of slot (epoch & 1) in EVERY rank's buffer (posted NVLink
+// stores), then "my partial of epoch e is written" is published in each peer's flag array (release at system
+// scope); the kernel waits (bounded) until all peers have published epoch e in its own flag array and adds the
+// `world` rows of the slot from LOCAL memory - no load ever crosses NVLink.  The epoch counter lives on the device,
+// so replaying a captured graph advances it like eager calls do.  Two slots alternate, so that a rank that is ahead
+// never overwrites a row that a peer is still reading (a rank can only finish epoch e after every peer has started
+// it, i.e. has finished reading epoch e-1).
 constexpr int PEER_MAX_RANKS = 8;
 constexpr int PEER_EPOCH_INDEX = 16;       // u32 index of the local epoch counter behind the flags
 
@@ -354,7 +355,7 @@ struct PeerParams {
     unsigned long long base[PEER_MAX_RANKS];   // every rank's symmetric buffer, as mapped into this process
     int rank, world;
     unsigned int n;                            // floats to reduce
-    unsigned long long slot_stride, flags_off; // bytes; staging at 0, slots at slot_stride and 2 * slot_stride
+    unsigned long long slot_stride, flags_off; // bytes; staging at 0, slot s row r at (1 + s * world + r) * slot_stride
     uint16_t* out;                             // bf16 [n]
     float* out32;                              // or fp32 [n]
     uint32_t* status;
@@ -380,14 +381,19 @@ __global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P
     }
     __syncthreads();
     const uint32_t epoch = epoch_s;
-    const unsigned long long slot_off = (1ull + (epoch & 1u)) * P.slot_stride;
+    const unsigned long long slot_off = (1ull + (unsigned long long)(epoch & 1u) * P.world) * P.slot_stride;   // row 0 of this epoch's slot
     const unsigned int n4 = P.n >> 2;                                  // n is a multiple of 4 (checked on the host)
-    {   // staging -> this epoch's slot
+    {   // staging -> row `rank` of this epoch's slot on every rank (the own copy included)
         const float4* stage = reinterpret_cast<const float4*>(P.base[P.rank]);
-        float4* slot = reinterpret_cast<float4*>(P.base[P.rank] + slot_off);
-        for (unsigned int i = threadIdx.x; i < n4; i += 1024) slot[i] = stage[i];
+        const unsigned long long row_off = slot_off + (unsigned long long)P.rank * P.slot_stride;
+        for (unsigned int i = threadIdx.x; i < n4; i += 1024) {
+            const float4 v = stage[i];
+#pragma unroll
+            for (int q = 0; q < PEER_MAX_RANKS; ++q)
+                if (q < P.world) reinterpret_cast<float4*>(P.base[q] + row_off)[i] = v;
+        }
     }
-    __syncthreads();                                                   // the release below covers every thread's copy
+    __syncthreads();                                                   // the release below covers every thread's stores
     bool good = true;
     if ((int)threadIdx.x < P.world) {
         uint32_t* theirs = reinterpret_cast<uint32_t*>(P.base[threadIdx.x] + P.flags_off) + P.rank;
@@ -405,11 +411,12 @@ __global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P
         if (threadIdx.x == 0 && P.status) atomicCAS(P.status, 0u, (uint32_t)DEV_TIMEOUT_PEER);
         return;
     }
+    const unsigned long long mine_base = P.base[P.rank] + slot_off;
     for (unsigned int i = threadIdx.x; i < n4; i += 1024) {
         float4 v[PEER_MAX_RANKS];
 #pragma unroll
-        for (int q = 0; q < PEER_MAX_RANKS; ++q)                       // all peers' loads in flight before the first add
-            if (q < P.world) v[q] = ld_sys_f4(reinterpret_cast<const float*>(P.base[q] + slot_off) + 4 * i);
+        for (int q = 0; q < PEER_MAX_RANKS; ++q)                       // the rows the peers pushed, all loads in flight before the first add
+            if (q < P.world) v[q] = ld_sys_f4(reinterpret_cast<const float*>(mine_base + (unsigned long long)q * P.slot_stride) + 4 * i);
         float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int q = 0; q < PEER_MAX_RANKS; ++q)

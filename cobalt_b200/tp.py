@@ -78,8 +78,9 @@ class ColumnParallelLinear(nn.Module):
 
 class PeerReducer:
     """Sum of fp32 partials over peer memory (``cobalt_allreduce_peer``).  One symmetric buffer per rank: a
-    staging area the local GEMV writes to, two data slots of ``max_floats`` fp32 that the kernel alternates by a
-    device-side epoch counter (so captured graphs and eager calls can be mixed), and a flag block.  All ranks
+    staging area the local GEMV writes to, two data slots of ``world`` rows of ``max_floats`` fp32 (every rank pushes
+    its partial into its row of every rank's slot; the kernel alternates the slots by a device-side epoch counter,
+    so captured graphs and eager calls can be mixed), and a flag block.  All ranks
     must make the same sequence of calls.  Needs ``torch.distributed._symmetric_memory`` (NVLink peer
     mappings); construction raises if that is unavailable, and the caller keeps using NCCL."""
 
@@ -95,7 +96,7 @@ class PeerReducer:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.stride = (int(max_floats) * 4 + 255) // 256 * 256
-        self.flags_off = 3 * self.stride
+        self.flags_off = (1 + 2 * self.world) * self.stride      # staging + two slots of `world` rows
         total = self.flags_off + self.FLAG_BYTES
         self.buf = symm.empty(total // 4, dtype=torch.float32, device=device)
         self.buf.zero_()

@@ -219,16 +219,16 @@ int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
 
 /* All-reduce (sum) of the fp32 partial outputs of a row-parallel layer over peer memory, for tensor-parallel decode
  * (the reference has no distributed code; this replaces the NCCL all-reduce that would follow cobalt_linear_f32).
- * Every rank owns one symmetric buffer mapped into all processes: [staging: slot_stride bytes][slot 0][slot 1][flags at
- * flags_off >= 3 * slot_stride: 32 x u32], zero-initialised.  peer_base (host array, `world` entries) holds every
- * rank's buffer address as seen by THIS process.  The caller has its GEMV write the fp32 partial [n] into the staging
- * area of its own buffer, then calls this on every rank with the same n (all ranks make the same sequence of calls).
- * One CTA: copies the partial into the slot of this call's epoch (a counter kept on the device, so graph replays
- * advance it), publishes the epoch in every peer's flags, waits (bounded, about a second; on expiry the status word is
- * set and the output is not written) until all peers have published theirs, reads all partials with peer loads, adds
- * them in rank order (deterministic) and writes bf16 (out_fp32 = 0) or fp32.  n % 4 == 0, n <= slot_stride/4, out 16-byte
- * aligned, world <= 8.  Plain
- * peer loads and stores only (no multicast). */
+ * Every rank owns one symmetric buffer mapped into all processes: [staging: slot_stride bytes][slot 0: world rows of
+ * slot_stride bytes][slot 1: the same][flags at flags_off >= (1 + 2 * world) * slot_stride: 32 x u32], zero-initialised.
+ * peer_base (host array, `world` entries) holds every rank's buffer address as seen by THIS process.  The caller has its
+ * GEMV write the fp32 partial [n] into the staging area of its own buffer, then calls this on every rank with the same
+ * n (all ranks make the same sequence of calls).  One CTA: pushes the partial into row `rank` of the slot of this call's
+ * epoch (a counter kept on the device, so graph replays advance it) in EVERY rank's buffer (posted peer stores),
+ * publishes the epoch in every peer's flags, waits (bounded, about a second; on expiry the status word is set and the
+ * output is not written) until all peers have published theirs, adds the rows of its LOCAL slot in rank order
+ * (deterministic) and writes bf16 (out_fp32 = 0) or fp32.  n % 4 == 0, n <= slot_stride/4, out 16-byte aligned,
+ * world <= 8.  Plain peer stores only (no multicast, no load crosses NVLink). */
 int cobalt_allreduce_peer(const uint64_t* peer_base, int rank, int world, size_t n, size_t slot_stride_bytes,
                           size_t flags_off_bytes, void* out, int out_fp32, void* status, void* stream);
 

@@ -491,6 +491,31 @@ def test_one_scratch_serves_gemv_and_gemm_in_any_order():
 
 
 @pytest.mark.gpu
+def test_peer_allreduce_single_rank_and_layout_check():
+    """world = 1: the kernel pushes the partial into its own slot, sees its own flag and writes the sum; three calls
+    in a row alternate the slots.  A flag block that overlaps the slots is refused on the host."""
+    import ctypes
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    n, stride = 2048, 8192
+    flags_off = 3 * stride
+    buf = torch.zeros((flags_off + 256) // 4, dtype=torch.float32, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    ptrs = (ctypes.c_uint64 * 1)(buf.data_ptr())
+    st = torch.cuda.current_stream().cuda_stream
+    for call in range(3):
+        part = torch.randn(n, device=dev)
+        buf[:n] = part
+        out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        assert lib.cobalt_allreduce_peer(ptrs, 0, 1, n, stride, flags_off, out.data_ptr(), 0, status.data_ptr(), st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, part.to(torch.bfloat16)) and int(status[0]) == 0
+    two = (ctypes.c_uint64 * 2)(buf.data_ptr(), buf.data_ptr())
+    assert lib.cobalt_allreduce_peer(two, 0, 2, n, stride, flags_off, out.data_ptr(), 0, status.data_ptr(), st) == -1
+
+
+@pytest.mark.gpu
 def test_peer_allreduce_wait_expires_cleanly():
     """Failure detection without a fault: a peer that never publishes its flag (here: a second buffer in the same
     process that nothing writes to) makes the bounded wait of the all-reduce kernel run out; the kernel records the
@@ -501,7 +526,7 @@ def test_peer_allreduce_wait_expires_cleanly():
     lib = _lib.load()
     dev = torch.device("cuda")
     n, stride = 1024, 4096
-    flags_off = 3 * stride
+    flags_off = (1 + 2 * 2) * stride                      # staging + two slots of two rows
     mine = torch.zeros((flags_off + 256) // 4, dtype=torch.float32, device=dev)
     silent = torch.zeros_like(mine)                       # stands for a rank that never arrives
     mine[:n] = 1.0
