@@ -43,8 +43,6 @@ EXPORTS = {
     "cobalt_gemv_fused": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                   c_void_p]),
     "cobalt_gemv_fused_scratch_bytes": (c_size_t, [c_int, c_void_p, c_int]),
-    "cobalt_gemv_fused_prefetch": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                           c_size_t, c_int, c_void_p, c_void_p, c_void_p]),
     "cobalt_gemv_rowwalk": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                     c_void_p]),
     "cobalt_gemm": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p,

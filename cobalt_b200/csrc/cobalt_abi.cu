@@ -244,10 +244,8 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
 // shared body of every GEMV entry point: `n` matrices that share x, N and the bit width
 struct GemvOut { void* y; int64_t ldy; const void* bias; };
 
-struct GemvNext { int n; const void* const* ptr; const size_t* bytes; };
-
 int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void* x, int64_t ldx, int M, bool fp32_out,
-                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, const GemvNext* next = nullptr) {
+                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream) {
     if (n < 1 || n > GEMV_MAX_MATS || !w || !out) return COBALT_EINVAL;
     if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
     GemvGeom g = {};
@@ -300,22 +298,6 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.slot_bytes = c.slot; P.xs_bytes = c.xs_bytes;
     P.total_warps = c.total_warps;
     P.aligned = c.aligned ? 1 : 0;
-    if (next) {                                              // L2 prefetch hint: split every range evenly over the warps of the grid
-        if (next->n < 0 || next->n > GEMV_MAX_MATS || (next->n > 0 && (!next->ptr || !next->bytes))) return COBALT_EINVAL;
-        size_t budget = COBALT_PREFETCH_MAX_BYTES;
-        for (int k = 0; k < next->n; ++k) {
-            if (!next->ptr[k] || ((uintptr_t)next->ptr[k] & 15)) return COBALT_EINVAL;
-            size_t b = next->bytes[k] & ~(size_t)15;
-            if (b > budget) b = budget;
-            budget -= b;
-            if (b == 0) continue;
-            const size_t chunk = round_up((b + c.total_warps - 1) / c.total_warps, 128);
-            P.pf_ptr[P.n_pf] = (const uint8_t*)next->ptr[k];
-            P.pf_bytes[P.n_pf] = b;
-            P.pf_chunk[P.n_pf] = (uint32_t)chunk;
-            ++P.n_pf;
-        }
-    }
     P.part_q = c.part_q; P.part_r = c.part_r;
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
@@ -464,16 +446,6 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
     GemvOut o[GEMV_MAX_MATS];
     for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
     return gemv_launch(n_mats, w, o, x, ldx, M, false, scratch, scratch_bytes, false, stream);
-}
-
-int cobalt_gemv_fused_prefetch(int n_mats, const CobaltMat* const* w, const void* x, int64_t ldx, void* const* y,
-                               const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
-                               int n_next, const void* const* next_ptr, const size_t* next_bytes, void* stream) {
-    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !y || !ldy) return COBALT_EINVAL;
-    GemvOut o[GEMV_MAX_MATS];
-    for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
-    const GemvNext nx = {n_next, next_ptr, next_bytes};
-    return gemv_launch(n_mats, w, o, x, ldx, M, false, scratch, scratch_bytes, false, stream, &nx);
 }
 
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,

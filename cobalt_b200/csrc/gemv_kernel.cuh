@@ -85,12 +85,6 @@ struct GemvParams {
     uint32_t total_warps;                // grid * GEMV_WARPS
     int aligned;                         // CTAs hold whole row blocks (no exchange between CTAs)
     uint32_t part_q, part_r;             // partition quotient and remainder, see cta_range_start()
-    // byte ranges the next kernel on the stream will read (a hint): every warp asks L2 for `pf_chunk[k]` bytes of
-    // range k at offset (global warp index) * pf_chunk[k] once it has requested its own last tile
-    const uint8_t* pf_ptr[GEMV_MAX_MATS];
-    uint64_t pf_bytes[GEMV_MAX_MATS];
-    uint32_t pf_chunk[GEMV_MAX_MATS];
-    int n_pf;
     float* partials;                     // [grid][2][4 * MT * 32]: CTA subtotals of straddling row blocks
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
@@ -141,9 +135,6 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     uint64_t p; asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p)); return p;
-}
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {      // p 16-byte aligned, bytes % 16 == 0
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ uint32_t ldg_hint(const uint32_t* p, uint64_t pol) {
     uint32_t v; asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol)); return v;
@@ -469,18 +460,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         healthy = __all_sync(full, healthy && ok);
         if (!healthy) continue;                                        // drain what is in flight, decode nothing
 
-        if (i == n - 1 && P.n_pf > 0 && lane == 0) {                   // own stream fully requested: pull the next kernel's head into L2
-            const uint64_t gwarp = (uint64_t)blockIdx.x * GEMV_WARPS + (uint64_t)warp;
-#pragma unroll
-            for (int k = 0; k < GEMV_MAX_MATS; ++k) {
-                if (k >= P.n_pf) break;
-                const uint64_t off = gwarp * P.pf_chunk[k];
-                if (off < P.pf_bytes[k]) {
-                    const uint64_t left = P.pf_bytes[k] - off;
-                    l2_prefetch_bulk(P.pf_ptr[k] + off, left < P.pf_chunk[k] ? (uint32_t)left : P.pf_chunk[k]);
-                }
-            }
-        }
         if (rev) { if (--ct < 0) { ct = CT - 1; --rb; } }
         else if (++ct == CT) { ct = 0; ++rb; }
         if (rb != cur_rb) {

@@ -56,7 +56,6 @@ class CobaltSparseLinear(nn.Module):
         self.register_buffer("scale2", scale2.reshape(-1).to(torch.float16).to(img.blob.device) if has_scale2 else None)
         self.bias = nn.Parameter(bias.detach().clone(), requires_grad=False) if bias is not None else None
         self._scratch = None
-        self.prefetch_next = []          # modules the next launch will stream (L2 prefetch hint of cobalt_gemv_fused_prefetch)
         self._desc = None
         self._desc_key = None
 
@@ -169,13 +168,6 @@ class CobaltSparseLinear(nn.Module):
             rc = lib.cobalt_linear_f32(ctypes.byref(d), x2.data_ptr(), x2.stride(0), y.data_ptr(), y.stride(0), M, sp, sbytes,
                                        stream)
             _lib.check("cobalt_linear_f32", rc)
-        elif M <= GEMV_MAX_TOKENS and self.prefetch_next:
-            n_next, nptr, nbytes = _next_ranges(self.prefetch_next)
-            dp = (ctypes.POINTER(_lib.CobaltMat) * 1)(ctypes.pointer(d))
-            yp, ld, bp = (ctypes.c_void_p * 1)(y.data_ptr()), (ctypes.c_int64 * 1)(y.stride(0)), (ctypes.c_void_p * 1)(_ptr(bias))
-            rc = lib.cobalt_gemv_fused_prefetch(1, dp, x2.data_ptr(), x2.stride(0), yp, ld, bp, M, sp, sbytes, n_next, nptr, nbytes,
-                                                stream)
-            _lib.check("cobalt_gemv_fused_prefetch", rc)
         elif M <= GEMV_MAX_TOKENS:
             rc = lib.cobalt_gemv(ctypes.byref(d), x2.data_ptr(), x2.stride(0), y.data_ptr(), y.stride(0), _ptr(bias), M,
                                  sp, sbytes, stream)
@@ -270,15 +262,6 @@ class CobaltSparseLinear(nn.Module):
                 f"group_size={GROUP}, density={dens:.3f}, bias={self.bias is not None}")
 
 
-def _next_ranges(mods):
-    """ctypes arrays (count, pointers, byte counts) of the packed images of `mods`, for the L2 prefetch hint."""
-    mods = list(mods)[:FUSED_MAX]
-    n = len(mods)
-    ptrs = (ctypes.c_void_p * max(n, 1))(*[m.packed.data_ptr() for m in mods])
-    sizes = (ctypes.c_size_t * max(n, 1))(*[m.packed.numel() for m in mods])
-    return n, ptrs, sizes
-
-
 class FusedProjections:
     """Several ``CobaltSparseLinear`` that read the same activations (q|k|v, gate|up), evaluated with one
     GEMV launch for up to 16 tokens (``cobalt_gemv_fused``) and one call each above that.  The reference
@@ -292,7 +275,6 @@ class FusedProjections:
         if any(m.in_features != n0 or m.bits != mods[0].bits or m.scale2 is not None or m.bias is not None for m in mods):
             raise ValueError("fused projections need equal in_features and bit width, no column scale and no bias")
         self.mods = mods
-        self.prefetch_next = []          # modules the next launch will stream: their images are requested from L2 early
         self._scratch = None
         self._arrays = None
 
@@ -324,9 +306,8 @@ class FusedProjections:
         yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
         ld = (ctypes.c_int64 * n)(*[y.stride(0) for y in ys])
         sp = (self._scratch.data_ptr() + 255) // 256 * 256
-        n_next, nptr, nbytes = _next_ranges(self.prefetch_next)
-        rc = lib.cobalt_gemv_fused_prefetch(n, descs, x2.data_ptr(), x2.stride(0), yp, ld, None, M, sp,
-                                            self._scratch.numel() - (sp - self._scratch.data_ptr()), n_next, nptr, nbytes,
-                                            torch.cuda.current_stream(x.device).cuda_stream)
-        _lib.check("cobalt_gemv_fused_prefetch", rc)
+        rc = lib.cobalt_gemv_fused(n, descs, x2.data_ptr(), x2.stride(0), yp, ld, None, M, sp,
+                                   self._scratch.numel() - (sp - self._scratch.data_ptr()),
+                                   torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check("cobalt_gemv_fused", rc)
         return [y.reshape(*lead, m.out_features) for y, m in zip(ys, self.mods)]

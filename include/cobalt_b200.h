@@ -92,20 +92,6 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
                       void* stream);
 size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, int M);
 
-/* cobalt_gemv_fused() (n_mats = 1 gives cobalt_gemv()) with a hint for the memory system: up to 4 byte ranges that the
- * NEXT kernel on the stream will stream, typically the tile images (tile_off table and tiles) of the next projection.
- * Every warp, once it has requested the last tile of its own share, asks L2 for an equal slice of those ranges
- * (cp.async.bulk.prefetch.L2), so that the next launch finds its offset tables and first tiles in L2 instead of paying a
- * DRAM round trip with all warps at once.  The decode of a launch leaves most of the DRAM bandwidth unused, so the
- * transfer costs this launch nothing.  Purely a hint: results do not depend on it, nothing waits for it, and at most
- * COBALT_PREFETCH_MAX_BYTES are requested per launch (beyond that the ranges are cut short).  Pointers 16-byte aligned.
- * No counterpart in the reference: its decode step is one persistent kernel whose phases follow each other without a
- * launch boundary (src/cobaltkernel/csrc/megakernel.cu), so there is no cold start per projection to hide. */
-#define COBALT_PREFETCH_MAX_BYTES ((size_t)48 << 20)
-int cobalt_gemv_fused_prefetch(int n_mats, const CobaltMat* const* w, const void* x, int64_t ldx, void* const* y,
-                               const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
-                               int n_next, const void* const* next_ptr, const size_t* next_bytes, void* stream);
-
 /* cobalt_gemv() for callers that must not allocate device memory.
  *
  * Who needs it: code that runs where cudaMalloc is off limits -- a plug-in inside a serving

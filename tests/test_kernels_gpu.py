@@ -230,24 +230,6 @@ def test_gemv_scratch_survives_graph_replay_after_a_larger_batch():
     assert torch.equal(y12[:1], mod(x12[:1]))
 
 
-def test_gemv_prefetch_hint_changes_nothing():
-    """cobalt_gemv_fused_prefetch: the L2 hint for the next launch leaves the results bit-identical."""
-    from cobalt_b200 import FusedProjections
-    raws = [O.synth_raw(K, 2048, 0.5, 4, seed=900 + K) for K in (512, 128, 128)]
-    mods = [to_module(r["keep"], r["q"], r["scale"], r["zero"], 4) for r in raws]
-    nxt = to_module(*[O.synth_raw(256, 1024, 0.5, 4, seed=77)[k] for k in ("keep", "q", "scale", "zero")], 4)
-    x = O.seeded_activation(2, 2048, 5).cuda()
-    fused = FusedProjections(mods)
-    plain = fused(x)
-    fused.prefetch_next = [nxt]
-    hinted = fused(x)
-    assert all(torch.equal(a, b) for a, b in zip(plain, hinted))
-    single = mods[0](x)
-    mods[0].prefetch_next = [nxt, mods[1]]
-    assert torch.equal(single, mods[0](x))
-    assert torch.equal(single, plain[0])
-
-
 # ----------------------------------------------------------------------------- benchmark configurations
 def _compress_on_gpu(K, N, bits, sparsity, seed):
     """Seeded weights and norms from the oracle's generator; mask + RTN by the product
