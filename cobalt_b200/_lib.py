@@ -59,11 +59,11 @@ EXPORTS = {
     "cobalt_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p]),
     "cobalt_rope_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                               c_int, c_void_p, c_void_p, c_float, c_void_p]),
+                               c_int, c_void_p, c_void_p, c_float, c_int64, c_void_p]),
     "cobalt_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "cobalt_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "cobalt_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_int,
-                                   c_int, c_float, c_void_p]),
+                                   c_int, c_float, c_int, c_int64, c_void_p]),
     "cobalt_allreduce_peer": (c_int, [c_void_p, c_int, c_int, c_size_t, c_size_t, c_size_t, c_void_p, c_int, c_void_p,
                                       c_void_p]),
     "cobalt_device_status": (c_int, [c_void_p, c_void_p, POINTER(c_uint32)]),

@@ -100,11 +100,32 @@ def quantize_survivors(weight: torch.Tensor, keep: torch.Tensor, bits: int, grou
     has_any = kg.any(-1, keepdim=True)
     lo = lo * has_any
     hi = hi * has_any
-    scale = (hi - lo).clamp(min=1e-4) / top_code
+    scale = (hi - lo).clamp(min=1e-4) / torch.full_like(hi, float(top_code))     # tensor / tensor: see quantize_dense
     zero = -torch.round(lo / scale)
     q = torch.clamp(torch.round(wg / scale + zero), 0, top_code).view(K, N)
     q = (q * keep).to(torch.uint8)
     return q, scale.view(K, G).half(), zero.view(K, G).half()
+
+
+def quantize_dense(weight: torch.Tensor, bits: int, group_size: int = GROUP):
+    """Plain asymmetric min-max RTN per 128-wide group, no mask: the recipe the reference applies to the (tied)
+    embedding / head matrix, which is read as a lookup (src/cobaltkernel/pack_cobalt.py:375-386).  The hull always
+    contains 0, so the zero point is an integer code in ``[0, 2**bits)``.  Returns ``q uint8[K,N]``, ``scale f16[K,G]``,
+    ``zero f16[K,G]`` (the reference stores the zero point as uint8; fp16 holds the same integers)."""
+    K, N = weight.shape
+    if N % group_size:
+        raise ValueError(f"in_features {N} is not a multiple of group_size {group_size}")
+    G = N // group_size
+    top_code = (1 << bits) - 1
+    wg = weight.float().view(K, G, group_size)
+    lo = wg.amin(-1).clamp(max=0.0)
+    hi = wg.amax(-1).clamp(min=0.0)
+    # tensor / tensor is an IEEE division on every device; tensor / python-number is a multiplication by the rounded
+    # reciprocal on CUDA, which moves the scale by an ulp and with it 0.7 % of the codes
+    scale = ((hi - lo) / torch.full_like(hi, float(top_code))).clamp(min=1e-12)
+    zero = torch.round(-lo / scale).clamp(0, top_code)
+    q = torch.clamp(torch.round(wg / scale.unsqueeze(-1) + zero.unsqueeze(-1)), 0, top_code).view(K, N)
+    return q.to(torch.uint8), scale.half(), zero.half()
 
 
 def compress_weight(weight: torch.Tensor, act_norm: torch.Tensor, cfg: SparseQuantConfig):

@@ -586,10 +586,10 @@ int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_
 
 int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positions, const float* inv_freq, void* k_cache,
                    void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, const void* q_norm_w,
-                   const void* k_norm_w, float eps, void* stream) {
+                   const void* k_norm_w, float eps, int64_t cache_seq_stride, void* stream) {
     if (!q || !k || !v || !positions || !inv_freq || !k_cache || !v_cache) return COBALT_EINVAL;
     if (T <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || max_ctx <= 0) return COBALT_EINVAL;
-    if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return COBALT_EINVAL;
+    if ((q_norm_w == nullptr) != (k_norm_w == nullptr) || cache_seq_stride < 0) return COBALT_EINVAL;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
@@ -597,13 +597,14 @@ int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positio
         const long long warps = (long long)T * (n_heads + 2 * n_kv_heads);
         rope_kv_norm_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             (uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, (const long long*)positions, inv_freq, (uint16_t*)k_cache,
-            (uint16_t*)v_cache, T, n_heads, n_kv_heads, head_dim, max_ctx, (const uint16_t*)q_norm_w, (const uint16_t*)k_norm_w, eps);
+            (uint16_t*)v_cache, T, n_heads, n_kv_heads, head_dim, max_ctx, (const uint16_t*)q_norm_w, (const uint16_t*)k_norm_w, eps,
+            (long long)cache_seq_stride);
         return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
     }
     const long long n = (long long)T * (n_heads + 2 * n_kv_heads) * (head_dim / 2);
     rope_kv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         (uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, (const long long*)positions, inv_freq, (uint16_t*)k_cache,
-        (uint16_t*)v_cache, T, n_heads, n_kv_heads, head_dim, max_ctx);
+        (uint16_t*)v_cache, T, n_heads, n_kv_heads, head_dim, max_ctx, (long long)cache_seq_stride);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
@@ -647,30 +648,32 @@ size_t cobalt_attn_decode_scratch_bytes(int n_heads, int head_dim, int max_ctx) 
 
 int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions, void* scratch,
                        size_t scratch_bytes, void* out, int n_heads, int n_kv_heads, int head_dim, int max_ctx, int window,
-                       float scale, void* stream) {
+                       float scale, int n_seq, int64_t cache_seq_stride, void* stream) {
     if (!q || !k_cache || !v_cache || !positions || !scratch || !out) return COBALT_EINVAL;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads / n_kv_heads > ATTN_MAX_REP) return COBALT_EINVAL;
+    if (n_seq < 1 || n_seq > 65535 || cache_seq_stride < 0) return COBALT_EINVAL;
     if (head_dim < 64 || head_dim > 256 || head_dim % 64 != 0 || max_ctx <= 0) return COBALT_EINVAL;
     if (((uintptr_t)k_cache & 3) || ((uintptr_t)q & 3) || ((uintptr_t)scratch & 255)) return COBALT_EINVAL;
     const int chunks = (max_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
     if (chunks > ATTN_MAX_CHUNKS) return COBALT_ETOOBIG;
-    if (scratch_bytes < cobalt_attn_decode_scratch_bytes(n_heads, head_dim, max_ctx)) return COBALT_ESCRATCH;
+    if (scratch_bytes < (size_t)n_seq * cobalt_attn_decode_scratch_bytes(n_heads, head_dim, max_ctx)) return COBALT_ESCRATCH;
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
     const int rep = n_heads / n_kv_heads;
+    // scratch: scores [n_seq][n_heads][max_ctx], chunk statistics [n_seq][n_heads][chunks][2], partial contexts [n_seq][chunks][n_heads][D]
     float* att = (float*)scratch;
-    float* stat = (float*)((uint8_t*)scratch + round_up((size_t)n_heads * max_ctx * 4, 256));
-    float* part = (float*)((uint8_t*)stat + round_up((size_t)n_heads * chunks * 8, 256));
+    float* stat = (float*)((uint8_t*)scratch + round_up((size_t)n_seq * n_heads * max_ctx * 4, 256));
+    float* part = (float*)((uint8_t*)stat + round_up((size_t)n_seq * n_heads * chunks * 8, 256));
     cudaStream_t st = (cudaStream_t)stream;
-    const dim3 grid((unsigned)chunks, (unsigned)n_kv_heads);
+    const dim3 grid((unsigned)chunks, (unsigned)n_kv_heads, (unsigned)n_seq);
     attn_scores_kernel<<<grid, ATTN_THREADS, 0, st>>>((const uint16_t*)q, (const uint16_t*)k_cache, (const long long*)positions, att, stat,
-                                             rep, head_dim, max_ctx, window, scale);
+                                             rep, head_dim, max_ctx, window, scale, (long long)cache_seq_stride);
     attn_context_kernel<<<grid, ATTN_THREADS, 0, st>>>(att, stat, (const uint16_t*)v_cache, (const long long*)positions, part, rep,
-                                              head_dim, max_ctx, window, n_heads);
+                                              head_dim, max_ctx, window, n_heads, (long long)cache_seq_stride);
     const int n = n_heads * head_dim;
-    attn_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, (const long long*)positions, (uint16_t*)out, n, chunks,
-                                                                     window);
+    attn_combine_kernel<<<dim3((unsigned)((n + 255) / 256), (unsigned)n_seq), 256, 0, st>>>(part, (const long long*)positions, (uint16_t*)out, n,
+                                                                                          chunks, window);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 

@@ -70,9 +70,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, con
 }
 
 // q [T, nh*D] rotated in place; k rotated and v copied into the caches [kvh][max_ctx][D] at positions[t]
+// (token t writes at cache + t * seq_stride: 0 for the tokens of one sequence, the per-sequence cache size for a batch
+// of sequences that decode one token each)
 __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v, const long long* positions,
                                const float* inv_freq, uint16_t* k_cache, uint16_t* v_cache, int T, int nh, int nkv,
-                               int D, int max_ctx) {
+                               int D, int max_ctx, long long seq_stride) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int half = D / 2;
     const int per_tok = (nh + 2 * nkv) * half;
@@ -92,14 +94,14 @@ __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v
         const float o2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
         if (!is_q && (pos < 0 || pos >= max_ctx)) return;              // a position outside the cache is never stored
         uint16_t* dst = is_q ? q + ((size_t)t * nh + head) * D
-                             : k_cache + ((size_t)(head - nh) * max_ctx + (size_t)pos) * D;
+                             : k_cache + (size_t)t * seq_stride + ((size_t)(head - nh) * max_ctx + (size_t)pos) * D;
         dst[d] = float_to_bf16(o1);
         dst[d + half] = float_to_bf16(o2);
     } else {
         if (pos < 0 || pos >= max_ctx) return;
         const int hv = head - nh - nkv;
         const uint16_t* src = v + ((size_t)t * nkv + hv) * D;
-        uint16_t* dst = v_cache + ((size_t)hv * max_ctx + (size_t)pos) * D;
+        uint16_t* dst = v_cache + (size_t)t * seq_stride + ((size_t)hv * max_ctx + (size_t)pos) * D;
         dst[d] = src[d];
         dst[d + half] = src[d + half];
     }
@@ -110,7 +112,7 @@ __global__ void rope_kv_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v
 __global__ void __launch_bounds__(256) rope_kv_norm_kernel(uint16_t* q, const uint16_t* k, const uint16_t* v, const long long* positions,
                                                            const float* inv_freq, uint16_t* k_cache, uint16_t* v_cache, int T, int nh,
                                                            int nkv, int D, int max_ctx, const uint16_t* q_norm_w,
-                                                           const uint16_t* k_norm_w, float eps) {
+                                                           const uint16_t* k_norm_w, float eps, long long seq_stride) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int half = D / 2;
     const int heads = nh + 2 * nkv;
@@ -123,14 +125,14 @@ __global__ void __launch_bounds__(256) rope_kv_norm_kernel(uint16_t* q, const ui
     if (head >= nh + nkv) {                                            // v: plain copy into the cache
         const int hv = head - nh - nkv;
         const uint16_t* src = v + ((size_t)t * nkv + hv) * D;
-        uint16_t* dst = v_cache + ((size_t)hv * max_ctx + (size_t)pos) * D;
+        uint16_t* dst = v_cache + (size_t)t * seq_stride + ((size_t)hv * max_ctx + (size_t)pos) * D;
         for (int d = lane; d < D; d += 32) dst[d] = src[d];
         return;
     }
     const bool is_q = head < nh;
     const uint16_t* src = is_q ? q + ((size_t)t * nh + head) * D : k + ((size_t)t * nkv + (head - nh)) * D;
     const uint16_t* nw = is_q ? q_norm_w : k_norm_w;
-    uint16_t* dst = is_q ? q + ((size_t)t * nh + head) * D : k_cache + ((size_t)(head - nh) * max_ctx + (size_t)pos) * D;
+    uint16_t* dst = is_q ? q + ((size_t)t * nh + head) * D : k_cache + (size_t)t * seq_stride + ((size_t)(head - nh) * max_ctx + (size_t)pos) * D;
     float ss = 0.0f;
     for (int d = lane; d < D; d += 32) { const float x = bf16_to_float(src[d]); ss += x * x; }
 #pragma unroll
@@ -191,11 +193,17 @@ __device__ __forceinline__ bool attn_allowed(int s, long long pos, int window, i
 // grid (chunks, n_kv), block ATTN_THREADS: warp w takes slots s0 + w + ATTN_WARPS * i; lane holds D/32 contiguous dims (D % 64 == 0, D <= 256)
 __global__ void __launch_bounds__(ATTN_THREADS) attn_scores_kernel(const uint16_t* q, const uint16_t* k_cache, const long long* positions,
                                                           float* att, float* chunk_stat, int rep, int D, int max_ctx, int window,
-                                                          float scale) {
+                                                          float scale, long long seq_stride) {
     __shared__ float sc[ATTN_MAX_REP][ATTN_CHUNK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
-    const long long pos = positions[0];
+    const int n_heads_all = (int)gridDim.y * rep;
+    // blockIdx.z = sequence: its query, cache, position and scratch
+    q += (size_t)blockIdx.z * n_heads_all * D;
+    k_cache += (size_t)blockIdx.z * seq_stride;
+    att += (size_t)blockIdx.z * n_heads_all * max_ctx;
+    chunk_stat += (size_t)blockIdx.z * n_heads_all * nchunks * 2;
+    const long long pos = positions[blockIdx.z];
     const int s0 = chunk * ATTN_CHUNK;
     float* stat = chunk_stat + ((size_t)(kvh * rep) * nchunks + chunk) * 2;     // [head][chunk][max, sum]
     if (s0 > pos || (window > 0 && s0 + ATTN_CHUNK - 1 <= pos - window)) {      // nothing allowed in this chunk
@@ -267,13 +275,17 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_scores_kernel(const uint16_
 // partial context of the chunk -> part [chunk][n_heads][D]
 __global__ void __launch_bounds__(ATTN_THREADS) attn_context_kernel(const float* att, const float* chunk_stat, const uint16_t* v_cache,
                                                            const long long* positions, float* part, int rep, int D, int max_ctx,
-                                                           int window, int n_heads) {
+                                                           int window, int n_heads, long long seq_stride) {
     __shared__ float gm[ATTN_MAX_REP], gz[ATTN_MAX_REP];
     __shared__ float pr[ATTN_MAX_REP][ATTN_CHUNK];
     __shared__ float red[ATTN_WARPS][ATTN_MAX_REP][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
-    const long long pos = positions[0];
+    v_cache += (size_t)blockIdx.z * seq_stride;                         // blockIdx.z = sequence
+    att += (size_t)blockIdx.z * n_heads * max_ctx;
+    chunk_stat += (size_t)blockIdx.z * n_heads * nchunks * 2;
+    part += (size_t)blockIdx.z * nchunks * n_heads * D;
+    const long long pos = positions[blockIdx.z];
     const int s0 = chunk * ATTN_CHUNK;
     float* mine = part + ((size_t)chunk * n_heads + (size_t)kvh * rep) * D;
     if (s0 > pos || (window > 0 && s0 + ATTN_CHUNK - 1 <= pos - window)) return;   // the combine step skips chunks outside the range
@@ -328,7 +340,9 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* part, co
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
-    const long long pos = positions[0];
+    part += (size_t)blockIdx.y * nchunks * n;                           // blockIdx.y = sequence
+    out += (size_t)blockIdx.y * n;
+    const long long pos = positions[blockIdx.y];
     int c1 = (int)(pos / ATTN_CHUNK) + 1;
     if (c1 > nchunks) c1 = nchunks;
     int c0 = 0;

@@ -114,20 +114,28 @@ def random_dense_params(cfg: dict, device, seed: int = 7):
 
 
 class CobaltDecoder:
-    """Batch-1 decoder over compressed projections.  ``linears[(layer, proj)]`` are
-    ``CobaltSparseLinear`` modules; ``dense`` holds embedding / norms / lm_head."""
+    """Decoder over compressed projections for ``batch`` independent sequences (each with its own KV cache; up to 16,
+    the token limit of the decode GEMV).  ``linears[(layer, proj)]`` are ``CobaltSparseLinear`` modules; ``dense`` holds
+    embedding / norms / lm_head.  ``head`` (optional) is the head as a compressed module - group-128 RTN without a mask,
+    the reference's recipe for the tied embedding / head (src/cobaltkernel/pack_cobalt.py:375-386, 538-558); with tensor
+    parallelism it holds this rank's slice of the vocabulary and the logits are gathered over the ranks."""
 
     def __init__(self, cfg: dict, linears: Dict[tuple, CobaltSparseLinear], dense: Dict[str, torch.Tensor],
-                 max_ctx: int, device, tp_world: int = 1, reducer=None, group=None):
+                 max_ctx: int, device, tp_world: int = 1, reducer=None, group=None, batch: int = 1,
+                 head: Optional[CobaltSparseLinear] = None):
         self.cfg, self.lin, self.P, self.max_ctx, self.dev = cfg, linears, dense, max_ctx, device
         self.world, self.reducer, self.group = tp_world, reducer, group
+        self.head, self.B = head, int(batch)
+        if not 1 <= self.B <= 16:
+            raise ValueError("batch must be between 1 and 16 sequences")
         self.fused_prompt_attention = False
         if cfg["num_attention_heads"] % tp_world or cfg["num_key_value_heads"] % tp_world:
             raise ValueError("heads must split evenly over the tensor-parallel ranks")
         self.nh, self.nkv = cfg["num_attention_heads"] // tp_world, cfg["num_key_value_heads"] // tp_world   # local heads
         L, nkv, D = cfg["num_hidden_layers"], self.nkv, cfg["head_dim"]
-        self.k_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
-        self.v_cache = torch.zeros(L, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
+        self.k_cache = torch.zeros(L, self.B, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)     # [layer][sequence][kv head][slot][D]
+        self.v_cache = torch.zeros(L, self.B, nkv, max_ctx, D, dtype=torch.bfloat16, device=device)
+        self.seq_stride = nkv * max_ctx * D                                    # elements of one sequence's cache in a layer
         self.gemma = is_gemma(cfg)
         self.types = layer_types(cfg)
         self.inv_freq = {lt: rope_inv_freq(cfg, lt, device) for lt in set(self.types)}
@@ -135,11 +143,11 @@ class CobaltDecoder:
         if self.gemma:
             self.embed_scale = torch.tensor(float(cfg["hidden_size"]) ** 0.5, dtype=torch.bfloat16, device=device)
         self.kv_pos = torch.arange(max_ctx, device=device)
-        need = _lib.load().cobalt_attn_decode_scratch_bytes(self.nh, D, max_ctx)
+        need = _lib.load().cobalt_attn_decode_scratch_bytes(self.nh, D, max_ctx) * self.B
         self.att_scratch = torch.empty(need, dtype=torch.uint8, device=device) if self.nh // self.nkv <= 8 and D % 64 == 0 and D <= 256 \
             and max_ctx <= 65536 else None
-        self.tok = torch.zeros(1, dtype=torch.long, device=device)        # next token to feed
-        self.pos = torch.zeros(1, dtype=torch.long, device=device)        # its position
+        self.tok = torch.zeros(self.B, dtype=torch.long, device=device)   # next token of every sequence
+        self.pos = torch.zeros(self.B, dtype=torch.long, device=device)   # its position
         self.qkv = [FusedProjections([linears[(i, "self_attn.q_proj")], linears[(i, "self_attn.k_proj")],
                                       linears[(i, "self_attn.v_proj")]]) for i in range(L)]
         self.gate_up = [FusedProjections([linears[(i, "mlp.gate_proj")], linears[(i, "mlp.up_proj")]]) for i in range(L)]
@@ -161,27 +169,34 @@ class CobaltDecoder:
         _lib.check("cobalt_add_rmsnorm", rc)
         return h_out, y
 
-    def _rope_kv(self, q, k, v, positions, layer):
+    def _rope_kv(self, q, k, v, positions, layer, seq: Optional[int]):
+        """``seq`` = the sequence the T tokens belong to, or None: token t belongs to sequence t (batched decode)."""
         cfg = self.cfg
+        kc = self.k_cache[layer] if seq is None else self.k_cache[layer][seq]
+        vc = self.v_cache[layer] if seq is None else self.v_cache[layer][seq]
         qn = kn = None
         if self.gemma:                                                                 # per-head norm of q and k, fused in
             qn = self.P[f"model.layers.{layer}.self_attn.q_norm.weight"].data_ptr()
             kn = self.P[f"model.layers.{layer}.self_attn.k_norm.weight"].data_ptr()
         rc = self._lib.cobalt_rope_kv(q.data_ptr(), k.data_ptr(), v.data_ptr(), positions.data_ptr(),
                                       self.inv_freq[self.types[layer]].data_ptr(),
-                                      self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(), q.shape[0],
+                                      kc.data_ptr(), vc.data_ptr(), q.shape[0],
                                       self.nh, self.nkv, cfg["head_dim"], self.max_ctx, qn, kn, float(cfg["rms_norm_eps"]),
-                                      torch.cuda.current_stream(self.dev).cuda_stream)
+                                      self.seq_stride if seq is None else 0, torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_rope_kv", rc)
 
-    def _attn_one(self, q, positions, layer):
-        """Attention of one new token over cache slots 0..positions[0] (three small launches, length read on the device)."""
+    def _attn_one(self, q, positions, layer, seq: Optional[int]):
+        """Attention of one new token per sequence over cache slots 0..positions[b] (three small launches, lengths read on
+        the device).  ``seq`` = a single sequence (q [1, nh*D]) or None = all ``batch`` sequences (q [B, nh*D])."""
         cfg = self.cfg
         ctx = torch.empty_like(q)
         window = int(cfg.get("sliding_window") or 0) if self.types[layer] == "sliding_attention" else 0
-        rc = self._lib.cobalt_attn_decode(q.data_ptr(), self.k_cache[layer].data_ptr(), self.v_cache[layer].data_ptr(),
+        kc = self.k_cache[layer] if seq is None else self.k_cache[layer][seq]
+        vc = self.v_cache[layer] if seq is None else self.v_cache[layer][seq]
+        rc = self._lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                           positions.data_ptr(), self.att_scratch.data_ptr(), self.att_scratch.numel(), ctx.data_ptr(),
                                           self.nh, self.nkv, cfg["head_dim"], self.max_ctx, window, self.scale,
+                                          q.shape[0], self.seq_stride if seq is None else 0,
                                           torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check("cobalt_attn_decode", rc)
         return ctx
@@ -207,9 +222,24 @@ class CobaltDecoder:
         return out
 
     # ------------------------------------------------------------------ one forward over T tokens
-    def _forward(self, ids: torch.Tensor, positions: torch.Tensor, attend_len: int) -> torch.Tensor:
+    def _head_logits(self, x: torch.Tensor) -> torch.Tensor:
+        """Head: dense bf16 matmul, or the compressed head (GEMV up to 16 rows, tcgen05 GEMM above); with a vocabulary
+        split over the ranks the local logits are gathered in rank order."""
+        if self.head is None:
+            w = self.P["model.embed_tokens.weight"] if self.gemma else self.P["lm_head.weight"]   # Gemma ties the head
+            return F.linear(x, w)
+        lg = self.head(x)
+        if self.world > 1:
+            import torch.distributed as dist
+            parts = [torch.empty_like(lg) for _ in range(self.world)]
+            dist.all_gather(parts, lg.contiguous(), group=self.group)
+            lg = torch.cat(parts, dim=-1)
+        return lg
+
+    def _forward(self, ids: torch.Tensor, positions: torch.Tensor, attend_len: int, seq: Optional[int] = 0) -> torch.Tensor:
         """ids, positions: [T] device tensors.  Keys/values are written at ``positions``; attention
-        looks at cache slots [0, attend_len) under the causal mask ``slot <= position``."""
+        looks at cache slots [0, attend_len) under the causal mask ``slot <= position``.  ``seq`` names the sequence
+        whose cache is used; ``seq=None`` is the batched decode step: token t is the next token of sequence t."""
         cfg, P = self.cfg, self.P
         nh, nkv, D = self.nh, self.nkv, cfg["head_dim"]                                # heads of this rank
         T, rep, S = ids.shape[0], nh // nkv, attend_len
@@ -230,10 +260,15 @@ class CobaltDecoder:
             p = f"model.layers.{i}."
             h, x = self._add_rmsnorm(h, delta, P[p + "input_layernorm.weight"], delta_w)
             q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
-            self._rope_kv(q, k, v, positions, i)                                       # q in place, k/v into the caches
-            Kc, Vc = self.k_cache[i][:, :S], self.v_cache[i][:, :S]                    # [nkv, S, D]
-            if T == 1 and self.att_scratch is not None:
-                ctx = self._attn_one(q, positions, i)
+            self._rope_kv(q, k, v, positions, i, seq)                                  # q in place, k/v into the caches
+            if seq is not None:
+                Kc, Vc = self.k_cache[i][seq][:, :S], self.v_cache[i][seq][:, :S]      # [nkv, S, D]
+            if seq is None:                                                            # one new token per sequence
+                if self.att_scratch is None:
+                    raise NotImplementedError("batched decode needs the library's decode attention (head_dim % 64 == 0, <= 8 q heads per kv head)")
+                ctx = self._attn_one(q, positions, i, None)
+            elif T == 1 and self.att_scratch is not None:
+                ctx = self._attn_one(q, positions, i, seq)
             elif self.fused_prompt_attention and T > 16:
                 # opt-in for prompts: the library's fused attention (fp32 scores and softmax inside; no [T, S] score
                 # tensor in memory).  It skips the spec's bf16 rounding of scores and probabilities; on a small model the
@@ -272,19 +307,15 @@ class CobaltDecoder:
             if self.gemma:
                 delta_w = P[p + "post_feedforward_layernorm.weight"]
         h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"], delta_w)
-        head = P["model.embed_tokens.weight"] if self.gemma else P["lm_head.weight"]   # Gemma ties the head
-        return F.linear(x, head).unsqueeze(0)                                          # [1, T, V]
+        return self._head_logits(x).unsqueeze(0)                                            # [1, T, V]
 
     @torch.no_grad()
     def time_head_ms(self, reps: int = 20) -> float:
         """Device time of what a decode step spends outside the blocks: embedding lookup, final norm, head, argmax."""
-        x = torch.zeros(1, self.cfg["hidden_size"], dtype=torch.bfloat16, device=self.dev)
-        head = self.P["model.embed_tokens.weight"] if self.gemma else self.P["lm_head.weight"]
-
         def once():
             h = self.P["model.embed_tokens.weight"].index_select(0, self.tok)
             _, y = self._add_rmsnorm(h, None, self.P["model.norm.weight"])
-            return torch.argmax(F.linear(y + x, head).float(), dim=-1)
+            return torch.argmax(self._head_logits(y).float(), dim=-1)
 
         for _ in range(3):
             once()
@@ -302,34 +333,51 @@ class CobaltDecoder:
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
-        """Run the prompt, fill the cache, return logits [T, V]."""
+        """Run the prompt(s), fill the cache(s), return the logits: ``ids [T]`` -> ``[T, V]`` (sequence 0), or
+        ``ids [B, T]`` (one prompt per sequence, equal lengths) -> ``[B, T, V]``."""
         ids = ids.to(self.dev)
-        T = ids.shape[0]
+        single = ids.dim() == 1
+        ids2 = ids.view(1, -1) if single else ids
+        if ids2.shape[0] > self.B:
+            raise ValueError(f"{ids2.shape[0]} prompts for a decoder built for {self.B} sequences")
+        T = ids2.shape[1]
         self._check_room(T)
-        logits = self._forward(ids, torch.arange(T, device=self.dev), T)[0]
+        pos = torch.arange(T, device=self.dev)
+        logits = torch.stack([self._forward(ids2[b], pos, T, seq=b)[0] for b in range(ids2.shape[0])])
         self.pos.fill_(T)
-        return logits
+        return logits[0] if single else logits
 
     @torch.no_grad()
     def step(self) -> torch.Tensor:
-        """One decode step for the token in ``self.tok`` at ``self.pos``; returns logits [V] and
-        advances ``tok`` (greedy) and ``pos`` on the device."""
-        logits = self._forward(self.tok, self.pos, self.max_ctx)[0, 0]
-        self.tok.copy_(torch.argmax(logits.float(), dim=-1, keepdim=True))
+        """One decode step for the tokens in ``self.tok`` at ``self.pos`` (one per sequence); returns the logits
+        (``[V]`` for a single sequence, else ``[B, V]``) and advances ``tok`` (greedy) and ``pos`` on the device."""
+        if self.B == 1:
+            logits = self._forward(self.tok, self.pos, self.max_ctx, seq=0)[0, 0]
+            self.tok.copy_(torch.argmax(logits.float(), dim=-1, keepdim=True))
+        else:
+            logits = self._forward(self.tok, self.pos, self.max_ctx, seq=None)[0]
+            self.tok.copy_(torch.argmax(logits.float(), dim=-1))
         self.pos.add_(1)
         return logits
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True, teacher: Optional[torch.Tensor] = None):
-        """Greedy continuation.  Returns (tokens [n_new] on the CPU, logits of every step [n_new, V]).
-        With ``teacher`` (token ids), the fed-back token of step i is ``teacher[i]`` instead of the argmax
-        (teacher-forced run, src/cobaltkernel/verify_kernel.py:288-339)."""
-        self._check_room(int(prompt.shape[0]) + n_new)       # the captured step advances the position on the device
+        """Greedy continuation.  ``prompt [T]``: returns (tokens [n_new] on the CPU, logits of every step [n_new, V]);
+        ``prompt [B, T]``: (tokens [n_new, B], logits [n_new, B, V]).  With ``teacher`` (token ids, ``[n_new]`` or
+        ``[n_new, B]``), the fed-back token of step i is ``teacher[i]`` instead of the argmax (teacher-forced run,
+        src/cobaltkernel/verify_kernel.py:288-339)."""
+        single = prompt.dim() == 1
+        if not single and prompt.shape[0] != self.B:
+            raise ValueError(f"{prompt.shape[0]} prompts for a decoder built for {self.B} sequences")
+        if single and self.B != 1:
+            raise ValueError("a batched decoder needs one prompt per sequence: prompt [B, T]")
+        self._check_room(int(prompt.shape[-1]) + n_new)      # the captured step advances the position on the device
         logits = self.prefill(prompt)
-        first = torch.argmax(logits[-1].float(), dim=-1, keepdim=True)
-        self.tok.copy_(first if teacher is None else teacher[0:1].to(self.dev))
+        last = logits[-1] if single else logits[:, -1]       # [V] or [B, V]
+        first = torch.argmax(last.float(), dim=-1, keepdim=single)
+        self.tok.copy_(first if teacher is None else teacher[0].reshape(-1).to(self.dev))
         toks = [first.clone()]
-        all_logits = [logits[-1].clone()]
+        all_logits = [last.clone()]
         if use_graph and self._graph is None:
             s = torch.cuda.Stream(self.dev)
             s.wait_stream(torch.cuda.current_stream(self.dev))
@@ -348,20 +396,45 @@ class CobaltDecoder:
                 lg = self._logits
             else:
                 lg = self.step()
-            toks.append(torch.argmax(lg.float(), dim=-1, keepdim=True).clone())
+            toks.append(torch.argmax(lg.float(), dim=-1, keepdim=single).clone())
             all_logits.append(lg.clone())
             if teacher is not None:
-                self.tok.copy_(teacher[i:i + 1].to(self.dev))
-        return torch.cat(toks).cpu(), torch.stack(all_logits)
+                self.tok.copy_(teacher[i].reshape(-1).to(self.dev))
+        toks = torch.cat(toks).cpu() if single else torch.stack(toks).cpu()
+        return toks, torch.stack(all_logits)
+
+
+def compress_head(dense: Dict[str, torch.Tensor], cfg: dict, bits: int, tp_rank: int = 0, tp_world: int = 1):
+    """Replace the head (and, for a tied head, the embedding table) by its group-128 RTN version: returns the compressed
+    module holding this rank's slice of the vocabulary.  The bf16 tensor in ``dense`` becomes the dequantised matrix, so
+    that embedding lookups and any oracle see exactly the weights the compressed head multiplies by."""
+    from .compress import quantize_dense
+    key = "model.embed_tokens.weight" if is_gemma(cfg) else "lm_head.weight"
+    W = dense[key]
+    V = W.shape[0]
+    if V % (16 * tp_world):
+        raise ValueError("the vocabulary must split into multiples of 16 rows per rank")
+    lo, hi = tp_rank * (V // tp_world), (tp_rank + 1) * (V // tp_world)
+    head = CobaltSparseLinear.from_dense_rtn(W, bits, rows=slice(lo, hi))
+    step = max(16, (1 << 25) // W.shape[1])
+    for k0 in range(0, V, step):                              # dequantised copy, chunked: (q - z) * s in fp32, one rounding
+        q, sc, zr = quantize_dense(W[k0:k0 + step], bits)
+        G = sc.shape[1]
+        wd = (q.float().view(q.shape[0], G, -1) - zr.float().unsqueeze(-1)) * sc.float().unsqueeze(-1)
+        W[k0:k0 + step] = wd.view(q.shape[0], -1).to(torch.bfloat16)
+    return head
 
 
 def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, device, keep_raw: bool = False,
-                         tp_rank: int = 0, tp_world: int = 1, reducer=None, group=None, clone_first_layer: bool = False):
+                         tp_rank: int = 0, tp_world: int = 1, reducer=None, group=None, clone_first_layer: bool = False,
+                         batch: int = 1, head_bits: int = 0):
     """Random-init model of the given shape with every projection compressed.  Returns the decoder
     and, when ``keep_raw``, the RAW tensors per (layer, proj) for an oracle to dequantise.  With
     ``tp_world > 1`` every matrix is compressed whole (same seeds on every rank) and this rank keeps its shard.
     ``clone_first_layer`` compresses only layer 0 and gives every other layer its own copy of those packed bytes
-    (for timing very large shapes: the bytes streamed per token are the same, the compression time is not)."""
+    (for timing very large shapes: the bytes streamed per token are the same, the compression time is not).
+    ``batch`` sequences decode together; ``head_bits`` (2..4) compresses the head with group-128 RTN and, with
+    tensor parallelism, splits its vocabulary over the ranks."""
     from .format import TileImage
     from .tp import kind_of, shard_raw
     lin, raws = {}, {}
@@ -380,5 +453,7 @@ def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, devic
             if tp_world > 1:
                 keep, q, sc, zr = shard_raw(kind_of(name), keep, q, sc, zr, tp_rank, tp_world)
             lin[(i, name)] = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": qcfg.bits})
-    dec = CobaltDecoder(cfg, lin, random_dense_params(cfg, device), max_ctx, device, tp_world=tp_world, reducer=reducer, group=group)
+    dense = random_dense_params(cfg, device)
+    head = compress_head(dense, cfg, head_bits, tp_rank, tp_world) if head_bits else None
+    dec = CobaltDecoder(cfg, lin, dense, max_ctx, device, tp_world=tp_world, reducer=reducer, group=group, batch=batch, head=head)
     return (dec, raws) if keep_raw else dec

@@ -92,6 +92,27 @@ class CobaltSparseLinear(nn.Module):
                      dict(nbits=bits, group_size=group_size, shape=tuple(W.shape), sparsity=sparsity, beta=beta))
         return obj
 
+    @classmethod
+    def from_dense_rtn(cls, weight: torch.Tensor, bits: int = 4, rows: Optional[slice] = None):
+        """Plain group-128 RTN without a mask (``compress.quantize_dense``): the recipe of the reference's tied
+        embedding / head (src/cobaltkernel/pack_cobalt.py:375-386, 538-558), packed with an all-ones bitmask so that the
+        same kernels multiply by it.  ``rows`` keeps only that slice of output rows (vocab-parallel head).  The matrix is
+        quantised in row chunks so that a 262144 x 5376 head does not need an fp32 copy of itself."""
+        from .compress import quantize_dense
+        K, N = weight.shape
+        r0, r1 = (0, K) if rows is None else (rows.start or 0, K if rows.stop is None else rows.stop)
+        qs, scs, zrs = [], [], []
+        step = max(16, (1 << 25) // max(N, 1))
+        for k0 in range(r0, r1, step):
+            q, sc, zr = quantize_dense(weight[k0:min(k0 + step, r1)], bits)
+            qs.append(q); scs.append(sc); zrs.append(zr)
+        q, sc, zr = torch.cat(qs), torch.cat(scs), torch.cat(zrs)
+        keep = torch.ones_like(q, dtype=torch.bool)
+        obj = cls._blank()
+        obj._install(pack_tiles(keep, q, sc, zr, bits), None, None,
+                     dict(nbits=bits, group_size=GROUP, shape=(r1 - r0, N), sparsity=0.0, recipe="dense_rtn"))
+        return obj
+
     # ------------------------------------------------------------------ descriptors
     def _descriptor(self) -> _lib.CobaltMat:
         key = (self.packed.data_ptr(), None if self.scale2 is None else self.scale2.data_ptr())

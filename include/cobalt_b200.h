@@ -185,23 +185,28 @@ int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_hos
  *                        and simply not stored); inv_freq fp32 [D/2]; cos/sin rounded to bf16.  With
  *                        q_norm_w / k_norm_w (bf16 [D], both or neither) q and k first get Gemma-3's per-head norm
  *                        bf16(x * rsqrt(mean_D(x^2) + eps) * (1 + w)) (src/cobaltkernel/ref_gemma3.py:181-185).
+ *                        cache_seq_stride (elements): token t writes at cache + t * cache_seq_stride - 0 when the T tokens
+ *                        belong to one sequence, the size of one sequence's cache when T sequences decode one token each.
  *   cobalt_swiglu      : out = act(gate) * up over n elements; act 0 = SiLU, act 1 = GELU (tanh approximation).
  *   cobalt_attn_decode : grouped-query attention of one new token (q [n_heads*D], already rotated) over the caches
  *                        [n_kv_heads][max_ctx][D]; slots 0..positions[0] are attended (positions[0] is read on the device;
  *                        window > 0 keeps only the last `window` slots); out [n_heads*D].  Rounding points of
  *                        src/cobaltkernel/ref_llama.py:117-137: bf16 scores times `scale` rounded to bf16, fp32 softmax,
  *                        bf16 probabilities, bf16 context.  scratch: cobalt_attn_decode_scratch_bytes(), 256-byte aligned,
- *                        contents irrelevant.  n_heads/n_kv_heads <= 8, D in {64,128,192,256}, max_ctx <= 65536. */
+ *                        contents irrelevant.  n_heads/n_kv_heads <= 8, D in {64,128,192,256}, max_ctx <= 65536.
+ *                        n_seq > 1 runs that many sequences at once (one new token each): q and out [n_seq][n_heads*D],
+ *                        positions[n_seq], sequence b's caches at k_cache/v_cache + b * cache_seq_stride elements, scratch
+ *                        n_seq times as large. */
 int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_out, void* y, int T, int H, float eps,
                        int flavor, const void* w_branch, void* stream);
 int cobalt_rope_kv(void* q, const void* k, const void* v, const int64_t* positions, const float* inv_freq, void* k_cache,
                    void* v_cache, int T, int n_heads, int n_kv_heads, int head_dim, int max_ctx, const void* q_norm_w,
-                   const void* k_norm_w, float eps, void* stream);
+                   const void* k_norm_w, float eps, int64_t cache_seq_stride, void* stream);
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream);
 size_t cobalt_attn_decode_scratch_bytes(int n_heads, int head_dim, int max_ctx);
 int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions, void* scratch,
                        size_t scratch_bytes, void* out, int n_heads, int n_kv_heads, int head_dim, int max_ctx, int window,
-                       float scale, void* stream);
+                       float scale, int n_seq, int64_t cache_seq_stride, void* stream);
 
 /* All-reduce (sum) of the fp32 partial outputs of a row-parallel layer over peer memory, for tensor-parallel decode
  * (the reference has no distributed code; this replaces the NCCL all-reduce that would follow cobalt_linear_f32).

@@ -102,6 +102,21 @@ def group_rtn_survivor(W: torch.Tensor, keep: torch.Tensor, nbits: int, gsize: i
     return q.view(K, N), scale.view(K, ng), zero.view(K, ng)
 
 
+def rtn_dense(W: torch.Tensor, nbits: int, gsize: int = GROUP):
+    """Restatement of ``rtn_dense`` (src/cobaltkernel/pack_cobalt.py:375-386): asymmetric group min-max RTN with a
+    0-inclusive hull, no mask - the recipe of the tied embedding / head.  Returns fp32 codes, fp16 scale, uint8 zero."""
+    K, N = W.shape
+    G = N // gsize
+    nl = (1 << nbits) - 1
+    Wg = W.float().view(K, G, gsize)
+    wmin = Wg.amin(-1).clamp(max=0.0)
+    wmax = Wg.amax(-1).clamp(min=0.0)
+    scale = ((wmax - wmin) / nl).clamp(min=1e-12)
+    zero = torch.round(-wmin / scale).clamp(0, nl)
+    q = torch.clamp(torch.round(Wg / scale.unsqueeze(-1) + zero.unsqueeze(-1)), 0, nl).view(K, N)
+    return q, scale.half(), zero.to(torch.uint8)
+
+
 def compress(W: torch.Tensor, act_norm: torch.Tensor, nbits: int, sparsity: float,
              beta: float = 0.5, gsize: int = GROUP):
     """The whole recipe of the benchmark configurations for one matrix.

@@ -23,3 +23,9 @@ def digests():
     import json
     with open(os.path.join(ROOT, "tests", "golden", "golden_digests.json")) as f:
         return json.load(f)
+
+
+@pytest.fixture(scope="session")
+def golden_head():
+    import numpy as np
+    return np.load(os.path.join(ROOT, "tests", "golden", "golden_head.npz"))

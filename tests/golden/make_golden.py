@@ -234,6 +234,28 @@ def main():
     np.savez_compressed(os.path.join(HERE, "golden_model_gemma3.npz"), **gout)
     dig["gemma3_cfg"] = gcfg
 
+    # plain group-128 RTN of the tied embedding / head matrix (src/cobaltkernel/pack_cobalt.py:375-386): small case in full
+    g = torch.Generator().manual_seed(606)
+    Wh = (torch.randn(96, 384, generator=g) * 0.02).to(torch.bfloat16)
+    Wh[7, 128:256] = Wh[7, 128:256].abs() + 0.004             # a group without negative values: the hull still contains 0
+    hq, hsc, hzr = pc.rtn_dense(Wh, 4)
+    np.savez_compressed(os.path.join(HERE, "golden_head.npz"), W=bf16_bits(Wh), q=hq.to(torch.uint8).numpy(),
+                        scale=hsc.numpy(), zero=hzr.numpy())
+
+    # matrices above 32 M elements: the global threshold of the mask comes from the reference's bisection branch
+    # (src/cobaltkernel/cobalt_math.py:79-101).  Digests only (the tensors are hundreds of megabytes).
+    dig["large"] = []
+    for (K, N, bits, sp, seed) in [(14336, 4096, 4, 0.5, 1004), (21504, 5376, 3, 0.6, 1005)]:
+        g = torch.Generator().manual_seed(seed)
+        W = (torch.randn(K, N, generator=g) * 0.02).half().float()
+        norm = torch.randn(N, generator=g).abs() + 0.1
+        keep = cm.balanced_keepmask(W.abs() * norm.view(1, -1), sp, 0.5)
+        q, sc, zr = cm.group_rtn(W, keep, bits, 128, "survivor")
+        q = q * keep
+        dig["large"].append(dict(K=K, N=N, bits=bits, sparsity=sp, beta=0.5, seed=seed, nnz=int(keep.bool().sum()),   # bool: an fp32 sum of 0/1 rounds above 2**24
+                                 keep=sha(keep.bool()), q=sha(q.to(torch.uint8)), scale=sha(sc.half()), zero=sha(zr.half())))
+        del W, keep, q, sc, zr
+
     with open(os.path.join(HERE, "golden_digests.json"), "w") as f:
         json.dump(dig, f, indent=1)
     print("wrote", len(out), "arrays")

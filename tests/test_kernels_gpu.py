@@ -373,17 +373,25 @@ def test_fused_projections_equal_separate_calls():
         FusedProjections([mods[0], to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
 
 
-@pytest.mark.parametrize("name,K,N", [("q_shard", 512, 5376), ("kv_shard", 256, 5376), ("o_shard", 5376, 512),
-                                        ("gate_up_shard", 2688, 5376), ("down_shard", 5376, 2688)])
-def test_config5_gemma27b_shard_shapes(name, K, N):
-    """Gemma-3-27B projection shapes as one rank of an 8-way tensor-parallel split sees them (hidden 5376,
-    intermediate 21504, 32 q / 16 kv heads of 128): 3 bit, 60 % sparse.  in_features of 5376, 2688 and 512
-    exercise partial column tiles (2, 1 and 4 groups in the last tile).  Decode batch 1 and 8, prefill 2048."""
+GEMMA27B = {"q": (4096, 5376, "column"), "kv": (2048, 5376, "column"), "o": (5376, 4096, "row"),
+            "gate_up": (21504, 5376, "column"), "down": (5376, 21504, "row")}
+
+
+@pytest.mark.parametrize("T", [1, 2, 4, 8])
+@pytest.mark.parametrize("name", list(GEMMA27B))
+def test_config5_gemma27b_shard_shapes(name, T):
+    """Gemma-3-27B projection shapes (hidden 5376, intermediate 21504, 32 q / 16 kv heads of 128) as one rank of a
+    T-way tensor-parallel split sees them, T = 1 (whole matrix), 2, 4, 8: 3 bit, 60 % sparse.  in_features of 5376,
+    10752, 2688 and 512 exercise partial column tiles.  Decode batch 1 and 8, prefill (2048 tokens at T = 8, 128 for the
+    larger shards, whose CPU oracle would otherwise run for minutes)."""
+    K, N, kind = GEMMA27B[name]
+    K, N = (K // T, N) if kind == "column" else (K, N // T)
+    prefill = 2048 if T == 8 else 128
     keep, q, sc, zr = _compress_on_gpu(K, N, 3, 0.6, 5000 + K % 101 + N % 103)
     mod = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": 3})
     Wb = O.dequantize(q.cpu(), sc.cpu(), zr.cpu(), keep.cpu()).to(torch.bfloat16)
     assert torch.equal(mod.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
-    for M in (1, 8, 2048):
+    for M in (1, 8, prefill):
         x = O.seeded_activation(M, N, 5100 + M)
         check_output(mod(x.cuda()), torch.matmul(x, Wb.t()), exact_fp64(x, Wb))
     # fp32 partial sums of a row-parallel shard: within fp32 accumulation noise of the exact product
@@ -553,7 +561,7 @@ def test_attn_decode_matches_torch(nh, nkv, D, ctx, pos, window):
     out = torch.empty_like(q)
     scale = float(D) ** -0.5
     rc = lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), positions.data_ptr(), scratch.data_ptr(), need, out.data_ptr(),
-                                nh, nkv, D, ctx, window, scale, torch.cuda.current_stream().cuda_stream)
+                                nh, nkv, D, ctx, window, scale, 1, 0, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     rep = nh // nkv
     qg = q.view(1, nkv, rep, D).permute(1, 0, 2, 3).reshape(nkv, rep, D)
@@ -570,6 +578,62 @@ def test_attn_decode_matches_torch(nh, nkv, D, ctx, pos, window):
     rel = float(d.norm() / ref.float().norm())
     assert rel <= 2e-3, rel
     assert float(d.abs().max()) <= 0.02 * float(ref.float().abs().max()), float(d.abs().max())
+
+
+@pytest.mark.gpu
+def test_attn_decode_batch_equals_single_sequences():
+    """n_seq sequences in one call (own caches, own positions) give the bits of n_seq single-sequence calls."""
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    B, nh, nkv, D, ctx, window = 3, 16, 4, 128, 700, 300
+    g = torch.Generator(device="cpu").manual_seed(77)
+    q = torch.randn(B, nh * D, generator=g).to(torch.bfloat16).to(dev)
+    kc = torch.randn(B, nkv, ctx, D, generator=g).to(torch.bfloat16).to(dev)
+    vc = torch.randn(B, nkv, ctx, D, generator=g).to(torch.bfloat16).to(dev)
+    positions = torch.tensor([699, 5, 412], dtype=torch.long, device=dev)
+    need = lib.cobalt_attn_decode_scratch_bytes(nh, D, ctx)
+    scratch = torch.empty(need * B, dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    out = torch.empty_like(q)
+    assert lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), positions.data_ptr(), scratch.data_ptr(), need * B,
+                                  out.data_ptr(), nh, nkv, D, ctx, window, 0.1, B, nkv * ctx * D, st) == 0
+    assert lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), positions.data_ptr(), scratch.data_ptr(), need,
+                                  out.data_ptr(), nh, nkv, D, ctx, window, 0.1, B, nkv * ctx * D, st) == -2     # scratch too small
+    for b in range(B):
+        one = torch.empty(1, nh * D, dtype=torch.bfloat16, device=dev)
+        assert lib.cobalt_attn_decode(q[b].data_ptr(), kc[b].data_ptr(), vc[b].data_ptr(), positions[b:b + 1].data_ptr(),
+                                      scratch.data_ptr(), need, one.data_ptr(), nh, nkv, D, ctx, window, 0.1, 1, 0, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(one[0], out[b]), b
+
+
+@pytest.mark.gpu
+def test_compressed_head_matches_oracle(golden_head):
+    """Group-128 RTN head (no mask): codes from the product quantiser equal the reference's, the packed all-ones-mask
+    image dequantises bit-exactly, logits and arg-max agree with the oracle's dequantise + matmul."""
+    from cobalt_b200 import quantize_dense
+    W = torch.from_numpy(golden_head["W"].copy()).view(torch.bfloat16)
+    # codes as the reference produced them (on the CPU: a GPU may round a tie in the division differently, which is
+    # why both sides of a parity check always share one set of RAW tensors)
+    q, sc, zr = quantize_dense(W, 4)
+    assert torch.equal(q, torch.from_numpy(golden_head["q"]))
+    assert torch.equal(sc, torch.from_numpy(golden_head["scale"]))
+    assert torch.equal(zr.to(torch.uint8), torch.from_numpy(golden_head["zero"]))
+    head = CobaltSparseLinear.from_dense_rtn(W, 4).cuda()
+    keep = torch.ones(W.shape, dtype=torch.bool)
+    Wb = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)
+    assert torch.equal(head.dequantize().cpu().view(torch.int16), Wb.view(torch.int16))
+    qg, scg, zrg = quantize_dense(W.cuda(), 4)                 # quantised on the GPU: at most a few ties differ
+    assert float((qg.cpu() != q).float().mean()) < 1e-3
+    for M in (1, 8, 40):                                       # GEMV and tcgen05 GEMM
+        x = O.seeded_activation(M, W.shape[1], 600 + M)
+        y = head(x.cuda())
+        y_ref = torch.matmul(x, Wb.t())
+        check_output(y, y_ref, exact_fp64(x, Wb))
+    part = CobaltSparseLinear.from_dense_rtn(W, 4, rows=slice(32, 64)).cuda()     # a vocabulary slice of a parallel head
+    x = O.seeded_activation(2, W.shape[1], 9)
+    assert torch.equal(part(x.cuda()), head(x.cuda())[:, 32:64])
 
 
 def test_zz_exemption_summary():

@@ -18,15 +18,16 @@ import pytest
 import torch
 
 from cobalt_b200 import CobaltSparseLinear, SparseQuantConfig
-from cobalt_b200.decoder import CobaltDecoder, random_dense_params, random_raw_layer
+from cobalt_b200.decoder import CobaltDecoder, compress_head, random_dense_params, random_raw_layer
 from oracle import cobalt_oracle as O
 from oracle import model_oracle as MO
 
 pytestmark = pytest.mark.gpu
 
 
-def build(cfg, qcfg, max_ctx, oracle_device):
-    """Decoder on the GPU plus the oracle's dense weights (on `oracle_device`) from the same RAW tensors."""
+def build(cfg, qcfg, max_ctx, oracle_device, batch=1, head_bits=0):
+    """Decoder on the GPU plus the oracle's dense weights (on `oracle_device`) from the same RAW tensors.  With
+    ``head_bits`` the head (tied embedding for Gemma) is group-128 RTN compressed; the oracle gets its dequantised matrix."""
     dev = torch.device("cuda")
     lin, W = {}, {}
     for i in range(cfg["num_hidden_layers"]):
@@ -35,9 +36,10 @@ def build(cfg, qcfg, max_ctx, oracle_device):
             Wd = O.dequantize(q, sc, zr, keep).to(torch.bfloat16)          # torch ops, same on any device
             W[f"model.layers.{i}.{name}.weight"] = Wd.to(oracle_device)
     dense = random_dense_params(cfg, dev)
+    head = compress_head(dense, cfg, head_bits) if head_bits else None     # rewrites the matrix in `dense` to what the codes mean
     for k, v in dense.items():
         W[k] = v.to(oracle_device)
-    return CobaltDecoder(cfg, lin, dense, max_ctx, dev), W
+    return CobaltDecoder(cfg, lin, dense, max_ctx, dev, batch=batch, head=head), W
 
 
 def compare(dec, W, cfg, prompt, n_new, oracle_device):
@@ -60,7 +62,8 @@ def compare(dec, W, cfg, prompt, n_new, oracle_device):
     agree = sum(a == b for a, b in zip(tf_toks.tolist(), toks_ref)) / n_new
     first_diff = next((i for i, (a, b) in enumerate(zip(toks, toks_ref)) if a != b), None)
     same = n_new if first_diff is None else first_diff
-    print(f"greedy identical for {same}/{n_new} tokens (first fork {first_diff}); teacher-forced agreement ours {agree:.4f} "
+    fork = "" if first_diff is None else f" [oracle top-2 margin at the fork {margins[first_diff]:.4f}]"
+    print(f"greedy identical for {same}/{n_new} tokens (first fork {first_diff}){fork}; teacher-forced agreement ours {agree:.4f} "
           f"control {ctl_agree:.4f}; max |dlogit| ours {our_noise:.4f} control {ctl_noise:.4f}")
     band = 2.0 * max(our_noise, ctl_noise, 2.0 ** -7)
     # (2) our logits are as close to the oracle as the oracle is to its own control (x2 head-room)
@@ -104,8 +107,8 @@ def test_small_model_other_bit_widths(bits, sparsity):
     compare(dec, W, cfg, torch.randint(0, 1000, (17,), generator=g), 12, "cpu")
 
 
-def gemma_small(layers=4, window=16):
-    return MO.gemma3_config(hidden=512, layers=layers, heads=8, kv_heads=2, head_dim=64, inter=1024, vocab=1000,
+def gemma_small(layers=4, window=16, vocab=1000):
+    return MO.gemma3_config(hidden=512, layers=layers, heads=8, kv_heads=2, head_dim=64, inter=1024, vocab=vocab,
                             sliding_window=window, pattern=2, query_pre_attn_scalar=96,
                             rope_scaling={"rope_type": "linear", "factor": 8.0})
 
@@ -137,6 +140,58 @@ def test_small_gemma3_three_bit_sixty_percent():
     dec, W = build(cfg, SparseQuantConfig(3, 0.6, 0.5), max_ctx=64, oracle_device="cpu")
     g = torch.Generator().manual_seed(9)
     compare(dec, W, cfg, torch.randint(0, 1000, (17,), generator=g), 12, "cpu")
+
+
+@pytest.mark.parametrize("family", ["llama", "gemma"])
+def test_compressed_head_decoder_against_cpu_oracle(family):
+    """The head as a compressed matrix (group-128 RTN, all-ones mask; tied to the embedding for Gemma) through the GEMV
+    and the GEMM: same gates as the dense head, the oracle multiplying by the dequantised matrix."""
+    cfg = gemma_small(layers=2, vocab=1008) if family == "gemma" else \
+        MO.llama_config(hidden=512, layers=2, heads=8, kv_heads=2, head_dim=64, inter=1024, vocab=1008)
+    dec, W = build(cfg, SparseQuantConfig(4, 0.5, 0.5), max_ctx=64, oracle_device="cpu", head_bits=4)
+    assert dec.head is not None and dec.head.out_features == cfg["vocab_size"]
+    g = torch.Generator().manual_seed(10)
+    compare(dec, W, cfg, torch.randint(0, 1000, (17,), generator=g), 12, "cpu")
+
+
+def test_batched_decoder_equals_single_sequences():
+    """Three sequences decoded together (one GEMV at M = 3 per projection, attention over three caches in one launch)
+    against the same three prompts run one at a time: identical tokens, identical logits."""
+    cfg = MO.llama_config(hidden=512, layers=2, heads=8, kv_heads=2, head_dim=64, inter=1024, vocab=1000)
+    qcfg = SparseQuantConfig(4, 0.5, 0.5)
+    many, _ = build(cfg, qcfg, 64, "cpu", batch=3)
+    one, _ = build(cfg, qcfg, 64, "cpu")
+    g = torch.Generator().manual_seed(11)
+    prompts = torch.randint(0, 1000, (3, 19), generator=g)
+    toks, logits = many.generate(prompts, 10, use_graph=True)                 # [10, 3], [10, 3, V]
+    for b in range(3):
+        t1, l1 = one.generate(prompts[b], 10, use_graph=True)
+        d = float((logits[:, b].float() - l1.float()).abs().max())
+        print(f"sequence {b}: max |dlogit| batched vs alone {d:.4g}")
+        assert torch.equal(toks[:, b], t1), b
+        assert torch.equal(logits[:, b], l1), b
+
+
+def test_config3_one_layer_at_7b_width_against_cpu_oracle():
+    """One block at the 7B widths (hidden 4096, 32/8 heads of 128, intermediate 14336, vocabulary 32000; 4-bit, 50 %)
+    against the oracle on the CPU -- another device, another matmul library: a 64-token prefill within twice the
+    control's rel-L2, then decode steps under the gates of `compare`."""
+    cfg = MO.llama_config(layers=1)
+    dec, W = build(cfg, SparseQuantConfig(4, 0.5, 0.5), max_ctx=96, oracle_device="cpu")
+    g = torch.Generator().manual_seed(64)
+    prompt = torch.randint(0, cfg["vocab_size"], (64,), generator=g)
+    ref_logits, _ = MO.prefill(cfg, W, prompt)
+    MO.EXACT_LINEAR = True
+    try:
+        ctl_logits, _ = MO.prefill(cfg, W, prompt)
+    finally:
+        MO.EXACT_LINEAR = False
+    got = dec.prefill(prompt).cpu()
+    rel = float((got.double() - ref_logits[0].double()).norm() / ref_logits.double().norm())
+    ctl = float((ctl_logits.double() - ref_logits.double()).norm() / ref_logits.double().norm())
+    print(f"7B-width layer, CPU oracle: prefill rel-L2 ours {rel:.2e} control {ctl:.2e}")
+    assert rel <= max(2.0 * ctl, 5e-3), (rel, ctl)
+    compare(dec, W, cfg, prompt, 6, "cpu")
 
 
 def test_config3_full_7b_shape():

@@ -99,3 +99,38 @@ def test_config1_recipe_matches_reference(digests):
     assert _sha(q) == d["q"]
     assert _sha(sc) == d["scale"]
     assert _sha(zr) == d["zero"]
+
+
+def test_head_rtn_matches_reference(golden_head):
+    """Plain group-128 RTN of the embedding / head (reference: rtn_dense, src/cobaltkernel/pack_cobalt.py:375-386): the
+    oracle's restatement and the product's quantiser both reproduce the reference's codes, scales and zero points."""
+    from cobalt_b200 import quantize_dense
+    W = torch.from_numpy(golden_head["W"].copy()).view(torch.bfloat16)
+    q, sc, zr = O.rtn_dense(W, 4)
+    assert np.array_equal(q.to(torch.uint8).numpy(), golden_head["q"])
+    assert np.array_equal(sc.numpy(), golden_head["scale"])
+    assert np.array_equal(zr.numpy(), golden_head["zero"])
+    q2, sc2, zr2 = quantize_dense(W, 4)
+    assert np.array_equal(q2.numpy(), golden_head["q"])
+    assert np.array_equal(sc2.numpy(), golden_head["scale"])
+    assert np.array_equal(zr2.to(torch.uint8).numpy(), golden_head["zero"])
+
+
+@pytest.mark.parametrize("idx", [0, 1])
+def test_large_matrix_mask_takes_the_bisection_branch(digests, idx):
+    """Above 32 M elements the global threshold of the keep mask comes from the reference's bisection
+    (src/cobaltkernel/cobalt_math.py:79-101): 14336 x 4096 (4 bit, 50 %) and 21504 x 5376 (3 bit, 60 %), seeded as
+    tests/golden/make_golden.py seeds them.  The oracle and the product compressor both reproduce the digests of the
+    reference's mask, codes, scales and zero points."""
+    from cobalt_b200 import SparseQuantConfig, compress_weight
+    d = digests["large"][idx]
+    g = torch.Generator().manual_seed(d["seed"])
+    W = (torch.randn(d["K"], d["N"], generator=g) * 0.02).half().float()
+    norm = torch.randn(d["N"], generator=g).abs() + 0.1
+    assert W.numel() > 32_000_000
+    keep, q, sc, zr = O.compress(W, norm, d["bits"], d["sparsity"], d["beta"])
+    assert int(keep.sum()) == d["nnz"]
+    assert (_sha(keep.bool()), _sha(q.to(torch.uint8)), _sha(sc.half()), _sha(zr.half())) == (d["keep"], d["q"], d["scale"], d["zero"])
+    del keep, q, sc, zr
+    k2, q2, s2, z2 = compress_weight(W, norm, SparseQuantConfig(d["bits"], d["sparsity"], d["beta"]))
+    assert (_sha(k2.bool()), _sha(q2), _sha(s2), _sha(z2)) == (d["keep"], d["q"], d["scale"], d["zero"])
