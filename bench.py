@@ -694,12 +694,13 @@ def run_model(args):
             except Exception as e:                           # noqa: BLE001 - any failure means "use NCCL"
                 if rank == 0:
                     print(f"peer all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
-    ctx, n_new = args.context, args.new_tokens
+    ctx, n_new, B = args.context, args.new_tokens, args.batch
     dec = build_random_decoder(cfg, SparseQuantConfig(bits, sparsity, BETA), ctx + n_new, dev, tp_rank=rank, tp_world=world,
-                               reducer=reducer, clone_first_layer=args.model == "gemma27b")
+                               reducer=reducer, clone_first_layer=args.model == "gemma27b", batch=B, head_bits=args.head_bits)
     dec.fused_prompt_attention = bool(args.fused_prompt_attention)
     g = torch.Generator().manual_seed(2048)
-    prompt = torch.randint(0, cfg["vocab_size"], (ctx,), generator=g)
+    prompt = torch.randint(0, cfg["vocab_size"], (ctx,) if B == 1 else (B, ctx), generator=g)
+    n_pre = min(args.prefill_tokens or ctx, ctx)
     t0 = time.perf_counter()
     dec.generate(prompt, 4, use_graph=True)                     # prefill + graph capture + a few steps (warm-up)
     torch.cuda.synchronize()
@@ -710,10 +711,14 @@ def run_model(args):
         dist.barrier()
     torch.cuda.synchronize()
     p0.record()
-    dec.prefill(prompt)
+    dec.prefill(prompt[..., :n_pre] if B == 1 else prompt[:1, :n_pre])   # one sequence; a prefix rewrites the same cache slots
     p1.record()
     torch.cuda.synchronize()
     prefill_ms = p0.elapsed_time(p1)
+    if dist is not None:
+        t = torch.tensor([prefill_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        prefill_ms = float(t.item())
     # timed: replay the captured step n_new times (token and position advance on the device)
     dec.pos.fill_(ctx)
     sampler = ClockSampler(local)
@@ -741,17 +746,21 @@ def run_model(args):
     if rank != 0:
         _finish(dist)
         return
-    head_bytes = cfg["vocab_size"] * cfg["hidden_size"] * 2
-    print(json.dumps({"metric": f"{label}-shape decode tokens/s (batch 1)", "value": round(1e3 / ms, 2), "unit": "tokens/s",
-                      "ms_per_token": round(ms, 4), "n_gpus": world, "dtype": "bf16", "data": "synthetic",
+    head_bytes = dec.head.compressed_bytes() * world if dec.head is not None else cfg["vocab_size"] * cfg["hidden_size"] * 2
+    head_txt = f"{args.head_bits}-bit group-128 RTN head" + (" split over the vocabulary" if world > 1 else "") \
+        if dec.head is not None else "dense bf16 lm_head"
+    print(json.dumps({"metric": f"{label}-shape decode tokens/s (batch {B})", "value": round(B * 1e3 / ms, 2), "unit": "tokens/s",
+                      "ms_per_step": round(ms, 4), "batch": B, "n_gpus": world, "dtype": "bf16", "data": "synthetic",
+                      "scaling": "strong",
                       "config": {"workload": f"{label} shape, {cfg['num_hidden_layers']} layers, {bits}-bit {int(sparsity*100)}% sparse, "
-                                             f"context {ctx}, {n_new} greedy tokens, CUDA graph; dense bf16 lm_head"
+                                             f"batch {B}, context {ctx}, {n_new} greedy tokens, CUDA graph; {head_txt}"
                                              + ("; every layer holds its own copy of the first layer's seeded matrices" if args.model == "gemma27b" else "")
                                              + (f"; tensor-parallel x{world} ({'peer-memory' if reducer is not None else 'NCCL'} all-reduce)" if world > 1 else ""),
                                  "compressed_bytes_per_token": int(wbytes), "lm_head_bytes": head_bytes},
                       "linear_GBps": round(wbytes / (ms * 1e-3) / 1e9, 1), "clocks": clocks, "device_status": status,
                       "prefill_attention": "fused library kernel (not the spec's rounding points)" if args.fused_prompt_attention else "spec arithmetic",
-                      "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(ctx / (prefill_ms * 1e-3), 1),
+                      "prefill_tokens": n_pre, "prefill_ms": round(prefill_ms, 2),
+                      "prefill_tokens_per_s": round(n_pre / (prefill_ms * 1e-3), 1),
                       "warmup_s": round(warm_s, 1)}), flush=True)
     _finish(dist)
 
@@ -769,6 +778,9 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--batch", type=int, default=1, help="--workload model: sequences decoded together (1..16)")
+    ap.add_argument("--head-bits", type=int, default=0, help="--workload model: compress the head with group-128 RTN at this width (0 = dense bf16)")
+    ap.add_argument("--prefill-tokens", type=int, default=0, help="--workload model: tokens of the timed prefill (0 = the whole context)")
     ap.add_argument("--prefill-m", default="128,512,2048")
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")

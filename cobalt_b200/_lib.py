@@ -26,6 +26,21 @@ class CobaltMat(Structure):
     ]
 
 
+class CobaltStagedInput(Structure):
+    """Mirror of ``struct CobaltStagedInput``."""
+    _fields_ = [
+        ("kind", c_int32), ("flavor", c_int32),
+        ("a", c_void_p), ("b", c_void_p),
+        ("ld", c_int64),
+        ("w", c_void_p), ("w_branch", c_void_p), ("h_out", c_void_p),
+        ("eps", c_float),
+    ]
+
+
+IN_GLU, IN_ADDNORM = 1, 2
+EUNSUPPORTED = -7
+
+
 class CobaltError(RuntimeError):
     def __init__(self, fn: str, status: int, text: str):
         super().__init__(f"{fn} failed with status {status}: {text}")
@@ -43,6 +58,8 @@ EXPORTS = {
     "cobalt_gemv_fused": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                   c_void_p]),
     "cobalt_gemv_fused_scratch_bytes": (c_size_t, [c_int, c_void_p, c_int]),
+    "cobalt_gemv_fused_staged": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                         c_size_t, c_void_p]),
     "cobalt_gemv_rowwalk": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                     c_void_p]),
     "cobalt_gemm": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p,

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcobalt_b200.so")
 SOURCES = ["cobalt_abi.cu"]
-HEADERS = ["common.cuh", "decode_core.cuh", "walk_kernels.cuh", "gemv_kernel.cuh", "gemm_kernel.cuh", "glue_kernels.cuh",
+HEADERS = ["common.cuh", "decode_core.cuh", "walk_kernels.cuh", "gemv_kernel.cuh", "gemm_kernel.cuh", "glue_kernels.cuh", "staged_input.cuh",
            os.path.join("..", "..", "include", "cobalt_b200.h")]
 
 

@@ -245,9 +245,21 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
 struct GemvOut { void* y; int64_t ldy; const void* bias; };
 
 int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void* x, int64_t ldx, int M, bool fp32_out,
-                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream) {
+                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, const CobaltStagedInput* in = nullptr) {
     if (n < 1 || n > GEMV_MAX_MATS || !w || !out) return COBALT_EINVAL;
     if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
+    if (in) {                                                // activations computed while staged: `a` stands in for x in the checks
+        if (in->kind != COBALT_IN_GLU && in->kind != COBALT_IN_ADDNORM) return COBALT_EINVAL;
+        if (in->flavor < 0 || in->flavor > 1 || !in->a) return COBALT_EINVAL;
+        if (((uintptr_t)in->b | (uintptr_t)in->w | (uintptr_t)in->w_branch | (uintptr_t)in->h_out) & 15) return COBALT_EINVAL;
+        if (in->kind == COBALT_IN_GLU && !in->b) return COBALT_EINVAL;
+        if (in->kind == COBALT_IN_ADDNORM) {
+            if (!in->w || in->h_out == in->a) return COBALT_EINVAL;
+            if (in->w_branch && (in->flavor != 1 || !in->b)) return COBALT_EINVAL;
+        }
+        x = in->a;
+        ldx = in->ld;
+    }
     GemvGeom g = {};
     for (int i = 0; i < n; ++i) {
         int rc = check_mat(w[i]);
@@ -268,6 +280,7 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     GemvCfg c;
     rc = gemv_config(g, w[0]->N, M, sms, &c);
     if (rc) return rc;
+    if (in && (!c.xs || w[0]->col_scale || (in->kind == COBALT_IN_ADDNORM && w[0]->N % 256 != 0))) return COBALT_EUNSUPPORTED;
     if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
     cudaStream_t st = (cudaStream_t)stream;
     if (clear_counters) {
@@ -302,6 +315,13 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);
+    if (in) {
+        P.in_kind = in->kind == COBALT_IN_GLU ? GEMV_IN_GLU : GEMV_IN_ADDNORM;
+        P.in_flavor = in->flavor;
+        P.in_a = (const uint16_t*)in->a; P.in_b = (const uint16_t*)in->b; P.in_ld = in->ld;
+        P.in_w = (const uint16_t*)in->w; P.in_wb = (const uint16_t*)in->w_branch; P.in_hout = (uint16_t*)in->h_out;
+        P.in_eps = in->eps;
+    }
     if (!c.xs) {                                             // fragment-ordered copy of x, read by every warp of the GEMV
         const int chunks = g.CT * 16 * c.mt * 32;
         cudaLaunchConfig_t pc = {};
@@ -358,6 +378,7 @@ const char* cobalt_strerror(int status) {
         case COBALT_EARCH: return "device is not compute capability 10.x (B200)";
         case COBALT_ETIMEOUT: return "a bounded device-side wait expired";
         case COBALT_ETOOBIG: return "size exceeds the stated maximum of this entry point";
+        case COBALT_EUNSUPPORTED: return "this shape cannot take the fused path; use the separate entry points";
         default: return "unknown status";
     }
 }
@@ -446,6 +467,16 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
     GemvOut o[GEMV_MAX_MATS];
     for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
     return gemv_launch(n_mats, w, o, x, ldx, M, false, scratch, scratch_bytes, false, stream);
+}
+
+int cobalt_gemv_fused_staged(int n_mats, const CobaltMat* const* w, const CobaltStagedInput* in, void* const* y,
+                             const int64_t* ldy, const void* const* bias, int M, int out_fp32, void* scratch,
+                             size_t scratch_bytes, void* stream) {
+    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !y || !ldy || !in) return COBALT_EINVAL;
+    if (out_fp32 && bias) return COBALT_EINVAL;
+    GemvOut o[GEMV_MAX_MATS];
+    for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
+    return gemv_launch(n_mats, w, o, nullptr, 0, M, out_fp32 != 0, scratch, scratch_bytes, false, stream, in);
 }
 
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,
@@ -579,8 +610,14 @@ int cobalt_add_rmsnorm(const void* h, const void* delta, const void* w, void* h_
     int sms = 0;
     int rc = device_info(&sms);
     if (rc) return rc;
-    add_rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)h, (const uint16_t*)delta, (const uint16_t*)w,
-                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps, flavor, (const uint16_t*)w_branch);
+    const bool vec = H % 256 == 0 && H <= 256 * ADDNORM_MAX_ITERS * (ADDNORM_THREADS / 32) && !(((uintptr_t)h | (uintptr_t)delta | (uintptr_t)w |
+                     (uintptr_t)h_out | (uintptr_t)y | (uintptr_t)w_branch) & 15);
+    if (vec)
+        add_rmsnorm_kernel<<<T, ADDNORM_THREADS, 0, (cudaStream_t)stream>>>((const uint16_t*)h, (const uint16_t*)delta, (const uint16_t*)w,
+                                                                           (uint16_t*)h_out, (uint16_t*)y, H, eps, flavor, (const uint16_t*)w_branch);
+    else
+        add_rmsnorm_generic_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)h, (const uint16_t*)delta, (const uint16_t*)w,
+                                                                       (uint16_t*)h_out, (uint16_t*)y, H, eps, flavor, (const uint16_t*)w_branch);
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 

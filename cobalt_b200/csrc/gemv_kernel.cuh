@@ -38,6 +38,7 @@
 // prefix scan per 1024-column window (src/cobaltkernel/csrc/cobalt_gemv.cuh:216-393).
 #pragma once
 #include "common.cuh"
+#include "staged_input.cuh"
 
 namespace cb {
 
@@ -88,7 +89,15 @@ struct GemvParams {
     float* partials;                     // [grid][2][4 * MT * 32]: CTA subtotals of straddling row blocks
     uint32_t* counters;                  // [row blocks]
     uint32_t* status;
+    // Activations computed while they are staged (staged launches only; 0: x is read as it is).
+    //   GEMV_IN_GLU:     x = bf16( bf16(act(in_a)) * in_b ), in_flavor 0 SiLU / 1 tanh-GELU
+    //   GEMV_IN_ADDNORM: h' = bf16(in_a + delta'), x = RMSNorm(h') * in_w; in_b = delta or null, in_wb = Gemma's
+    //                    branch-norm weight or null, in_flavor 0 Llama / 1 Gemma; CTA 0 writes h' to in_hout
+    int in_kind, in_flavor;
+    const uint16_t* in_a; const uint16_t* in_b; int64_t in_ld;
+    const uint16_t* in_w; const uint16_t* in_wb; uint16_t* in_hout; float in_eps;
 };
+constexpr int GEMV_IN_GLU = 1, GEMV_IN_ADDNORM = 2;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -298,40 +307,158 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     constexpr int XPRE = 2;
     const int chunks_per_row = P.N / 8;
     const int x_total = XS ? chunks_per_row * M : 0;
-    uint4 xpre[XPRE];
-#pragma unroll
-    for (int q = 0; q < XPRE; ++q) {
-        const int i = threadIdx.x + q * GEMV_THREADS;
-        if (i < x_total) {
-            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-            xpre[q] = __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c);
-        }
-    }
     static_assert(GEMV_THREADS == 2 * LUT_ENTRIES && GEMV_LUT_COPIES == 8, "table fill: one entry and four replicas per thread");
-    {
+    auto fill_table = [&]() {
         const uint32_t mb = threadIdx.x & (LUT_ENTRIES - 1), half = threadIdx.x / LUT_ENTRIES;
         const uint4 e = gemv_lut_entry(mb, BITS);
         uint4* dst = lut_s + mb * GEMV_LUT_COPIES + half * (GEMV_LUT_COPIES / 2);
 #pragma unroll
         for (int c = 0; c < GEMV_LUT_COPIES / 2; ++c) dst[c] = e;
-    }
-    {
-        auto stage_chunk = [&](int i, const uint4& v) {
+    };
+    auto stage_chunk = [&](int m, int c, const uint4& v) {
+        const int pc = c ^ (((c >> 4) & 3) | ((m & 1) << 2));
+        *reinterpret_cast<uint4*>(xs + ((size_t)m * chunks_per_row + pc) * 16) = v;
+    };
+    if (!XS || P.in_kind == 0) {
+        uint4 xpre[XPRE];
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+            if (i < x_total) {
+                const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+                xpre[q] = __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c);
+            }
+        }
+        fill_table();
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+            if (i < x_total) { const int m = i / chunks_per_row; stage_chunk(m, i - m * chunks_per_row, xpre[q]); }
+        }
+        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
             const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-            const int pc = c ^ (((c >> 4) & 3) | ((m & 1) << 2));
-            *reinterpret_cast<uint4*>(xs + ((size_t)m * chunks_per_row + pc) * 16) = v;
+            stage_chunk(m, c, __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c));
+        }
+    } else if (P.in_kind == GEMV_IN_GLU) {
+        // gated activation of the two halves of the previous projection, applied while staging
+        // (the reference closes it in the gate|up epilogue: src/cobaltkernel/csrc/megakernel.cu:1805-1892)
+        auto ld_a = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_a + (size_t)m * P.in_ld) + c); };
+        auto ld_b = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_b + (size_t)m * P.in_ld) + c); };
+        uint4 ga[XPRE], ub[XPRE];
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+            if (i < x_total) { const int m = i / chunks_per_row, c = i - m * chunks_per_row; ga[q] = ld_a(m, c); ub[q] = ld_b(m, c); }
+        }
+        fill_table();
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+            if (i < x_total) { const int m = i / chunks_per_row; stage_chunk(m, i - m * chunks_per_row, glu_chunk(ga[q], ub[q], P.in_flavor)); }
+        }
+        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            stage_chunk(m, c, glu_chunk(ld_a(m, c), ld_b(m, c), P.in_flavor));
+        }
+    } else {
+        // residual add + RMSNorm applied while staging (the reference normalises while it writes its activation
+        // copy: write_xprime, src/cobaltkernel/csrc/megakernel.cu:270-288); rows are multiples of 256 values, so the
+        // 32 chunks a warp handles in one step belong to one row.  Warp totals live in the (still unused) fragment area.
+        float* tot_branch = red;
+        float* tot_joined = red + 1024;
+        const int groups = chunks_per_row >> 5;
+        const bool has_delta = P.in_b != nullptr, norm_branch = has_delta && P.in_wb != nullptr;
+        auto ld_h = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_a + (size_t)m * P.in_ld) + c); };
+        auto ld_d = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_b + (size_t)m * P.in_ld) + c); };
+        uint4 hq[XPRE], dq[XPRE];
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+            dq[q] = make_uint4(0, 0, 0, 0);
+            if (i < x_total) {
+                const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+                hq[q] = ld_h(m, c);
+                if (has_delta) dq[q] = ld_d(m, c);
+            }
+        }
+        fill_table();
+        if (norm_branch) {                                             // sums of delta^2 per row
+            auto branch_total = [&](int i, const uint4& dd) {          // i < x_total is the same for all lanes of a warp
+                float d[8];
+                chunk_to_floats(dd, d);
+                const float s = warp_butterfly_sum(i < x_total ? chunk_sumsq(d) : 0.0f);
+                if (lane == 0 && i < x_total) tot_branch[i >> 5] = s;
+            };
+#pragma unroll
+            for (int q = 0; q < XPRE; ++q) branch_total(threadIdx.x + q * GEMV_THREADS, dq[q]);
+            for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+                const int m = i / chunks_per_row;
+                branch_total(i, ld_d(m, i - m * chunks_per_row));
+            }
+            __syncthreads();
+        }
+        auto joined_chunk = [&](int m, int c, const uint4& hh, const uint4& dd, float (&v)[8]) {      // h' of one chunk
+            chunk_to_floats(hh, v);
+            if (has_delta) {
+                float d[8];
+                chunk_to_floats(dd, d);
+                if (norm_branch) {
+                    const float rb = row_rsqrt(tot_branch + m * groups, groups, P.N, P.in_eps);
+                    float wb[8];
+                    chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(P.in_wb) + c), wb);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) d[k] = branch_value(d[k], rb, wb[k]);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = joined_value(v[k], d[k]);
+            }
+        };
+        const bool writes_h = blockIdx.x == 0 && P.in_hout != nullptr;
+        auto joined_total = [&](int i, const float (&v)[8]) {
+            const float s = warp_butterfly_sum(i < x_total ? chunk_sumsq(v) : 0.0f);
+            if (lane == 0 && i < x_total) tot_joined[i >> 5] = s;
+            if (writes_h && i < x_total) {
+                const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+                reinterpret_cast<uint4*>(P.in_hout + (size_t)m * P.in_ld)[c] = floats_to_chunk(v);
+            }
+        };
+        float vk[XPRE][8];
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) {
+            const int i = threadIdx.x + q * GEMV_THREADS;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) vk[q][k] = 0.0f;
+            if (i < x_total) { const int m = i / chunks_per_row; joined_chunk(m, i - m * chunks_per_row, hq[q], dq[q], vk[q]); }
+            joined_total(i, vk[q]);
+        }
+        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            float v[8];
+            joined_chunk(m, c, ld_h(m, c), has_delta ? ld_d(m, c) : make_uint4(0, 0, 0, 0), v);
+            joined_total(i, v);
+        }
+        __syncthreads();
+        auto normed_chunk = [&](int m, int c, const float (&v)[8]) {
+            const float r = row_rsqrt(tot_joined + m * groups, groups, P.N, P.in_eps);
+            float wn[8], o[8];
+            chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(P.in_w) + c), wn);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = normed_value(v[k], r, wn[k], P.in_flavor);
+            stage_chunk(m, c, floats_to_chunk(o));
         };
 #pragma unroll
         for (int q = 0; q < XPRE; ++q) {
             const int i = threadIdx.x + q * GEMV_THREADS;
-            if (i < x_total) stage_chunk(i, xpre[q]);
+            if (i < x_total) { const int m = i / chunks_per_row; normed_chunk(m, i - m * chunks_per_row, vk[q]); }
         }
-        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {         // the rest is recomputed, not kept
             const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-            stage_chunk(i, __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c));
+            float v[8];
+            joined_chunk(m, c, ld_h(m, c), has_delta ? ld_d(m, c) : make_uint4(0, 0, 0, 0), v);
+            normed_chunk(m, c, v);
         }
-        mbar_arrive(xbar);                                             // releases this thread's table and x stores
     }
+    mbar_arrive(xbar);                                                 // releases this thread's table and x stores
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = 1; i < issued; ++i) issue(i, i, false);               // the rest of the ring, off the path to the first decode
 

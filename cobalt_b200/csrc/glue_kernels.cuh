@@ -5,18 +5,17 @@
 // well, so that results agree with the spec up to the summation order of the mean.
 #pragma once
 #include "common.cuh"
+#include "staged_input.cuh"
 
 namespace cb {
-
-__device__ __forceinline__ float bf16_round(float f) { return bf16_to_float(float_to_bf16(f)); }
 
 // h_out = bf16(h + delta') (delta may be null);
 // flavor 0 (Llama):  y = w * bf16( h_out * rsqrt(mean(h_out^2) + eps) ),  delta' = delta
 // flavor 1 (Gemma):  y = bf16( h_out * rsqrt(mean(h_out^2) + eps) * (1 + w) ), all in fp32 before the one rounding;
 //                    with w_branch the branch is normalised first: delta' = bf16( delta * rsqrt(mean(delta^2) + eps) * (1 + w_branch) )
 //                    (the post-attention / post-feedforward norm of src/cobaltkernel/ref_gemma3.py:262-270)
-// one block per row
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, const uint16_t* delta, const uint16_t* w,
+// one block per row; any H (the fast kernel below takes rows of a multiple of 256 values)
+__global__ void __launch_bounds__(256) add_rmsnorm_generic_kernel(const uint16_t* h, const uint16_t* delta, const uint16_t* w,
                                                           uint16_t* h_out, uint16_t* y, int H, float eps, int flavor,
                                                           const uint16_t* w_branch) {
     __shared__ float red[8];
@@ -65,6 +64,75 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* h, con
             y[base + i] = float_to_bf16(bf16_to_float(w[i]) * n);
         } else {
             y[base + i] = float_to_bf16(__fmul_rn(__fmul_rn(v, r), __fadd_rn(1.0f, bf16_to_float(w[i]))));
+        }
+    }
+}
+
+// The same for rows of H = 256 * k values, H <= 256 * ADDNORM_MAX_GROUPS: one block of 512 threads per row, every
+// value read once with 16-byte loads and kept in registers between the two sums and the output.  Sums of squares in
+// the order staged_input.cuh defines, which the decode GEMV reproduces when it applies this step while staging.
+constexpr int ADDNORM_THREADS = 512;
+constexpr int ADDNORM_MAX_ITERS = 4;                                   // chunks per thread: rows up to 16384 values
+__global__ void __launch_bounds__(ADDNORM_THREADS) add_rmsnorm_kernel(const uint16_t* h, const uint16_t* delta, const uint16_t* w,
+                                                                      uint16_t* h_out, uint16_t* y, int H, float eps, int flavor,
+                                                                      const uint16_t* w_branch) {
+    __shared__ float tot_branch[ADDNORM_MAX_ITERS * ADDNORM_THREADS / 32], tot_joined[ADDNORM_MAX_ITERS * ADDNORM_THREADS / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const size_t base = (size_t)blockIdx.x * H;
+    const int cpr = H / 8, groups = cpr / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool norm_branch = delta != nullptr && w_branch != nullptr;
+    float v[ADDNORM_MAX_ITERS][8], d[ADDNORM_MAX_ITERS][8];
+#pragma unroll
+    for (int q = 0; q < ADDNORM_MAX_ITERS; ++q) {
+        const int c = threadIdx.x + q * ADDNORM_THREADS;
+        if (c < cpr) {
+            chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(h + base) + c), v[q]);
+            if (delta) chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(delta + base) + c), d[q]);
+        }
+    }
+    if (norm_branch) {
+#pragma unroll
+        for (int q = 0; q < ADDNORM_MAX_ITERS; ++q) {
+            const int c = threadIdx.x + q * ADDNORM_THREADS;
+            const float s = warp_butterfly_sum(c < cpr ? chunk_sumsq(d[q]) : 0.0f);
+            if (lane == 0 && c < cpr) tot_branch[q * (ADDNORM_THREADS / 32) + warp] = s;
+        }
+        __syncthreads();
+        const float rb = row_rsqrt(tot_branch, groups, H, eps);
+#pragma unroll
+        for (int q = 0; q < ADDNORM_MAX_ITERS; ++q) {
+            const int c = threadIdx.x + q * ADDNORM_THREADS;
+            if (c < cpr) {
+                float wb[8];
+                chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(w_branch) + c), wb);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) d[q][k] = branch_value(d[q][k], rb, wb[k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < ADDNORM_MAX_ITERS; ++q) {
+        const int c = threadIdx.x + q * ADDNORM_THREADS;
+        if (c < cpr && delta) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[q][k] = joined_value(v[q][k], d[q][k]);
+            if (h_out) reinterpret_cast<uint4*>(h_out + base)[c] = floats_to_chunk(v[q]);
+        }
+        const float s = warp_butterfly_sum(c < cpr ? chunk_sumsq(v[q]) : 0.0f);
+        if (lane == 0 && c < cpr) tot_joined[q * (ADDNORM_THREADS / 32) + warp] = s;
+    }
+    __syncthreads();
+    const float r = row_rsqrt(tot_joined, groups, H, eps);
+#pragma unroll
+    for (int q = 0; q < ADDNORM_MAX_ITERS; ++q) {
+        const int c = threadIdx.x + q * ADDNORM_THREADS;
+        if (c < cpr) {
+            float wn[8], o[8];
+            chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(w) + c), wn);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = normed_value(v[q][k], r, wn[k], flavor);
+            reinterpret_cast<uint4*>(y + base)[c] = floats_to_chunk(o);
         }
     }
 }
@@ -155,16 +223,7 @@ __global__ void swiglu_kernel(const uint16_t* g, const uint16_t* u, uint16_t* ou
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float x = bf16_to_float(g[i]);
-    float a;
-    if (act == 0) {
-        a = x / (1.0f + expf(-x));
-    } else {
-        const float kBeta = 0.7978845608028654f, kKappa = 0.044715f;   // sqrt(2/pi)
-        const float inner = kBeta * (x + kKappa * (x * x * x));
-        a = 0.5f * x * (1.0f + tanhf(inner));
-    }
-    out[i] = float_to_bf16(bf16_round(a) * bf16_to_float(u[i]));
+    out[i] = float_to_bf16(glu_value(bf16_to_float(g[i]), bf16_to_float(u[i]), act));
 }
 
 // ----------------------------------------------------------------------------- single-token attention

@@ -122,7 +122,7 @@ class CobaltDecoder:
 
     def __init__(self, cfg: dict, linears: Dict[tuple, CobaltSparseLinear], dense: Dict[str, torch.Tensor],
                  max_ctx: int, device, tp_world: int = 1, reducer=None, group=None, batch: int = 1,
-                 head: Optional[CobaltSparseLinear] = None):
+                 head: Optional[CobaltSparseLinear] = None, fuse_steps: bool = True):
         self.cfg, self.lin, self.P, self.max_ctx, self.dev = cfg, linears, dense, max_ctx, device
         self.world, self.reducer, self.group = tp_world, reducer, group
         self.head, self.B = head, int(batch)
@@ -151,6 +151,12 @@ class CobaltDecoder:
         self.qkv = [FusedProjections([linears[(i, "self_attn.q_proj")], linears[(i, "self_attn.k_proj")],
                                       linears[(i, "self_attn.v_proj")]]) for i in range(L)]
         self.gate_up = [FusedProjections([linears[(i, "mlp.gate_proj")], linears[(i, "mlp.up_proj")]]) for i in range(L)]
+        # Element-wise steps folded into the next projection's activation staging for up to 8 tokens (residual add +
+        # RMSNorm in front of q|k|v, gate|up and a compressed head; the gated activation in front of down): same results
+        # bit for bit as the separate kernels, three launches fewer per layer.
+        self.fuse_steps = bool(fuse_steps)
+        self.down = [FusedProjections([linears[(i, "mlp.down_proj")]]) for i in range(L)]
+        self.head_f = FusedProjections([head]) if head is not None else None
         self._lib = _lib.load()
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._logits = None
@@ -221,6 +227,37 @@ class CobaltDecoder:
         _lib.check("cobalt_swiglu", rc)
         return out
 
+    def _norm_then(self, fused: FusedProjections, h, delta, w, w_branch=None):
+        """``(h + delta', outputs of the projections applied to RMSNorm(h + delta') * w)``: one launch when the kernel can
+        normalise while it stages its activations, else the norm kernel followed by the projections."""
+        if delta is None:
+            w_branch = None
+        if self.fuse_steps and h.shape[0] <= 8:
+            h_out = torch.empty_like(h) if delta is not None else None
+            ys = fused.staged(_lib.IN_ADDNORM, h, delta, 1 if self.gemma else 0, w=w, w_branch=w_branch, h_out=h_out,
+                              eps=float(self.cfg["rms_norm_eps"]))
+            if ys is not None:
+                return (h if delta is None else h_out), ys
+        h, x = self._add_rmsnorm(h, delta, w, w_branch)
+        return h, fused(x)
+
+    def _glu_down(self, layer: int, g, u):
+        """down(act(g) * u), summed over the ranks with tensor parallelism; the activation is applied while the kernel
+        stages its input when the shape allows, else by its own kernel."""
+        lin = self.lin[(layer, "mlp.down_proj")]
+        T, K = g.shape[0], lin.out_features
+        if self.fuse_steps and T <= 8:
+            act = 1 if self.gemma else 0
+            if self.world == 1:
+                ys = self.down[layer].staged(_lib.IN_GLU, g, u, act)
+                if ys is not None:
+                    return ys[0]
+            elif self.reducer is not None and T * K * 4 <= self.reducer.stride:
+                ys = self.down[layer].staged(_lib.IN_GLU, g, u, act, out_fp32=True, outs=[self.reducer.slot_view(T * K)])
+                if ys is not None:
+                    return self.reducer.reduce(T * K, torch.empty(T * K, dtype=g.dtype, device=g.device)).view(T, K)
+        return self._row_parallel(lin, self._swiglu(g, u))
+
     # ------------------------------------------------------------------ one forward over T tokens
     def _head_logits(self, x: torch.Tensor) -> torch.Tensor:
         """Head: dense bf16 matmul, or the compressed head (GEMV up to 16 rows, tcgen05 GEMM above); with a vocabulary
@@ -258,8 +295,7 @@ class CobaltDecoder:
         delta, delta_w = None, None                                                    # pending branch and (Gemma) its norm weight
         for i in range(cfg["num_hidden_layers"]):
             p = f"model.layers.{i}."
-            h, x = self._add_rmsnorm(h, delta, P[p + "input_layernorm.weight"], delta_w)
-            q, k, v = self.qkv[i](x)                                                   # one launch for up to 16 tokens
+            h, (q, k, v) = self._norm_then(self.qkv[i], h, delta, P[p + "input_layernorm.weight"], delta_w)   # one launch for up to 8 tokens
             self._rope_kv(q, k, v, positions, i, seq)                                  # q in place, k/v into the caches
             if seq is not None:
                 Kc, Vc = self.k_cache[i][seq][:, :S], self.v_cache[i][seq][:, :S]      # [nkv, S, D]
@@ -299,13 +335,16 @@ class CobaltDecoder:
                 ctx = torch.bmm(att, Vc).view(nkv, T, rep, D).permute(1, 0, 2, 3).reshape(T, nh * D)
             o = self._row_parallel(self.lin[(i, "self_attn.o_proj")], ctx)
             if self.gemma:                                                             # the branch is normalised before it joins
-                h, x = self._add_rmsnorm(h, o, P[p + "pre_feedforward_layernorm.weight"], P[p + "post_attention_layernorm.weight"])
+                h, (g, u) = self._norm_then(self.gate_up[i], h, o, P[p + "pre_feedforward_layernorm.weight"],
+                                            P[p + "post_attention_layernorm.weight"])
             else:
-                h, x = self._add_rmsnorm(h, o, P[p + "post_attention_layernorm.weight"])
-            g, u = self.gate_up[i](x)
-            delta = self._row_parallel(self.lin[(i, "mlp.down_proj")], self._swiglu(g, u))
+                h, (g, u) = self._norm_then(self.gate_up[i], h, o, P[p + "post_attention_layernorm.weight"])
+            delta = self._glu_down(i, g, u)
             if self.gemma:
                 delta_w = P[p + "post_feedforward_layernorm.weight"]
+        if self.head_f is not None and self.world == 1:                                # final norm folded into the compressed head
+            h, (lg,) = self._norm_then(self.head_f, h, delta, P["model.norm.weight"], delta_w)
+            return lg.unsqueeze(0)
         h, x = self._add_rmsnorm(h, delta, P["model.norm.weight"], delta_w)
         return self._head_logits(x).unsqueeze(0)                                            # [1, T, V]
 
@@ -427,7 +466,7 @@ def compress_head(dense: Dict[str, torch.Tensor], cfg: dict, bits: int, tp_rank:
 
 def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, device, keep_raw: bool = False,
                          tp_rank: int = 0, tp_world: int = 1, reducer=None, group=None, clone_first_layer: bool = False,
-                         batch: int = 1, head_bits: int = 0):
+                         batch: int = 1, head_bits: int = 0, fuse_steps: bool = True):
     """Random-init model of the given shape with every projection compressed.  Returns the decoder
     and, when ``keep_raw``, the RAW tensors per (layer, proj) for an oracle to dequantise.  With
     ``tp_world > 1`` every matrix is compressed whole (same seeds on every rank) and this rank keeps its shard.
@@ -455,5 +494,6 @@ def build_random_decoder(cfg: dict, qcfg: SparseQuantConfig, max_ctx: int, devic
             lin[(i, name)] = CobaltSparseLinear(q, sc, zr, keep, None, None, {"nbits": qcfg.bits})
     dense = random_dense_params(cfg, device)
     head = compress_head(dense, cfg, head_bits, tp_rank, tp_world) if head_bits else None
-    dec = CobaltDecoder(cfg, lin, dense, max_ctx, device, tp_world=tp_world, reducer=reducer, group=group, batch=batch, head=head)
+    dec = CobaltDecoder(cfg, lin, dense, max_ctx, device, tp_world=tp_world, reducer=reducer, group=group, batch=batch, head=head,
+                        fuse_steps=fuse_steps)
     return (dec, raws) if keep_raw else dec

@@ -42,6 +42,7 @@ extern "C" {
 #define COBALT_EARCH        (-4)   /* device is not compute capability 10.x */
 #define COBALT_ETIMEOUT     (-5)   /* a bounded device-side wait gave up (see cobalt_device_status) */
 #define COBALT_ETOOBIG      (-6)   /* size exceeds a stated maximum of the entry point */
+#define COBALT_EUNSUPPORTED (-7)   /* this shape cannot take the fused path asked for; nothing was launched, use the separate entry points */
 
 /* Descriptor of one packed matrix.  Replaces the reference's 9 x int64 MatDesc
  * {data,row_off,scale,zero,col_scale,K,N,G,layout}
@@ -91,6 +92,37 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
                       const int64_t* ldy, const void* const* bias, int M, void* scratch, size_t scratch_bytes,
                       void* stream);
 size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, int M);
+
+/* cobalt_gemv_fused() whose activation rows are COMPUTED while the kernel copies them into shared memory, so
+ * that the element-wise step in front of a projection costs no launch and no round trip through memory:
+ *   COBALT_IN_GLU      x = bf16( bf16(act(a)) * b ), act = SiLU (flavor 0) or tanh-GELU (flavor 1): what
+ *                      cobalt_swiglu() computes.  The reference closes the gate in its gate|up epilogue
+ *                      (docs/FORMAT.md:126-151, src/cobaltkernel/csrc/megakernel.cu:1805-1892).
+ *   COBALT_IN_ADDNORM  h' = bf16(a + delta'), x = RMSNorm(h') * w: what cobalt_add_rmsnorm() computes, with
+ *                      b = delta (or NULL), w_branch = Gemma's branch-norm weight (or NULL), flavor 0 Llama / 1 Gemma;
+ *                      h' is written to h_out (may be NULL; must not alias a).  The reference normalises while it
+ *                      writes its activation copy and adds the residual in the o/down epilogue
+ *                      (src/cobaltkernel/csrc/megakernel.cu:270-288, 1904-1915).
+ * a, b, h_out are [M, in_features] bf16 with row stride ld (elements), 16-byte aligned; results are bit-identical
+ * to the separate entry points followed by cobalt_gemv_fused().  Only launches that stage their activations can
+ * take this path (M <= 8 and M * in_features * 2 bytes beside the weight ring; COBALT_IN_ADDNORM also needs
+ * in_features % 256 == 0): otherwise COBALT_EUNSUPPORTED is returned and nothing is launched. */
+#define COBALT_IN_GLU      1
+#define COBALT_IN_ADDNORM  2
+typedef struct CobaltStagedInput {
+    int kind;                       /* COBALT_IN_GLU or COBALT_IN_ADDNORM */
+    int flavor;
+    const void* a;                  /* gate, or the residual stream h */
+    const void* b;                  /* up, or delta (NULL: h' = h) */
+    int64_t ld;
+    const void* w;                  /* COBALT_IN_ADDNORM: norm weight [in_features] bf16 */
+    const void* w_branch;           /* COBALT_IN_ADDNORM, flavor 1: weight of the norm applied to delta first, or NULL */
+    void* h_out;                    /* COBALT_IN_ADDNORM: h' [M, in_features], or NULL */
+    float eps;
+} CobaltStagedInput;
+int cobalt_gemv_fused_staged(int n_mats, const CobaltMat* const* w, const CobaltStagedInput* in, void* const* y,
+                             const int64_t* ldy, const void* const* bias, int M, int out_fp32, void* scratch,
+                             size_t scratch_bytes, void* stream);
 
 /* cobalt_gemv() for callers that must not allocate device memory.
  *

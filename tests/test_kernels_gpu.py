@@ -636,6 +636,92 @@ def test_compressed_head_matches_oracle(golden_head):
     assert torch.equal(part(x.cuda()), head(x.cuda())[:, 32:64])
 
 
+def _separate_addnorm(h, delta, w, w_branch, flavor, eps):
+    """cobalt_add_rmsnorm through the C ABI: (h + delta', normalised rows)."""
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    y = torch.empty_like(h)
+    h_out = torch.empty_like(h) if delta is not None else None
+    ptr = lambda t: None if t is None else t.data_ptr()
+    rc = lib.cobalt_add_rmsnorm(h.data_ptr(), ptr(delta), w.data_ptr(), ptr(h_out), y.data_ptr(), h.shape[0], h.shape[1], eps,
+                                flavor, ptr(w_branch), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    return (h if delta is None else h_out), y
+
+
+@pytest.mark.parametrize("N,M", [(4096, 1), (4096, 3), (4096, 8), (5376, 1), (5376, 4), (512, 2)])
+@pytest.mark.parametrize("mode", ["llama", "llama_first", "gemma", "gemma_branch"])
+def test_norm_folded_into_staging_equals_separate_kernels(N, M, mode):
+    """Residual add + RMSNorm computed by the GEMV while it stages its activations (cobalt_gemv_fused_staged) against
+    cobalt_add_rmsnorm followed by cobalt_gemv_fused: identical h + delta and identical projections, bit for bit."""
+    from cobalt_b200 import _lib
+    from cobalt_b200.linear import FusedProjections
+    mods = []
+    for j, K in enumerate((256, 64)):
+        raw = O.synth_raw(K, N, 0.5, 4, seed=700 + j)
+        mods.append(to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4))
+    fused = FusedProjections(mods)
+    g = torch.Generator().manual_seed(N + M)
+    h = torch.randn(M, N, generator=g).bfloat16().cuda()
+    delta = None if mode == "llama_first" else (torch.randn(M, N, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(N, generator=g) * 0.1 + (1.0 if mode.startswith("llama") else 0.0)).bfloat16().cuda()
+    wb = (torch.randn(N, generator=g) * 0.1).bfloat16().cuda() if mode == "gemma_branch" else None
+    flavor, eps = (0, 1e-5) if mode.startswith("llama") else (1, 1e-6)
+    h_ref, x_ref = _separate_addnorm(h, delta, w, wb, flavor, eps)
+    want = fused(x_ref)
+    h_out = torch.empty_like(h) if delta is not None else None
+    got = fused.staged(_lib.IN_ADDNORM, h, delta, flavor, w=w, w_branch=wb, h_out=h_out, eps=eps)
+    assert got is not None
+    torch.cuda.synchronize()
+    if delta is not None:
+        assert torch.equal(h_out, h_ref)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    # the normalised rows themselves against torch in fp32 (the kernels' own arithmetic is pinned by the model tests)
+    hf = h_ref.float()
+    r = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)
+    xt = (w.float() * (hf * r).bfloat16().float()) if flavor == 0 else (hf * r * (1.0 + w.float()))
+    assert float((x_ref.float() - xt).abs().max()) <= 2.0 ** -6 * float(xt.abs().max())
+
+
+@pytest.mark.parametrize("N,M,act", [(14336, 1, 0), (14336, 2, 0), (21504, 1, 1), (4096, 8, 1), (1024, 5, 0)])
+def test_gated_activation_folded_into_staging_equals_separate_kernels(N, M, act):
+    """act(gate) * up computed by the GEMV while it stages (cobalt_gemv_fused_staged, COBALT_IN_GLU) against cobalt_swiglu
+    followed by cobalt_gemv: identical outputs, bf16 and raw fp32 sums."""
+    from cobalt_b200 import _lib
+    from cobalt_b200.linear import FusedProjections
+    raw = O.synth_raw(192, N, 0.5, 4, seed=800 + M)
+    mod = to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)
+    fused = FusedProjections([mod])
+    g = torch.Generator().manual_seed(N + M)
+    gate = torch.randn(M, N, generator=g).bfloat16().cuda()
+    up = torch.randn(M, N, generator=g).bfloat16().cuda()
+    x = torch.empty_like(gate)
+    rc = _lib.load().cobalt_swiglu(gate.data_ptr(), up.data_ptr(), x.data_ptr(), gate.numel(), act, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    got = fused.staged(_lib.IN_GLU, gate, up, act)
+    assert got is not None and torch.equal(got[0], mod(x))
+    got32 = fused.staged(_lib.IN_GLU, gate, up, act, out_fp32=True)
+    assert torch.equal(got32[0], mod(x, out_fp32=True))
+    xf = gate.float()
+    a = torch.nn.functional.silu(xf) if act == 0 else torch.nn.functional.gelu(xf, approximate="tanh")
+    assert float((x.float() - a.bfloat16().float() * up.float()).abs().max()) <= 2.0 ** -6 * float(x.float().abs().max())
+
+
+def test_staging_refuses_shapes_it_cannot_hold():
+    """Eight tokens of 14336 values do not fit beside the weight ring: the fused entry point launches nothing and says so."""
+    from cobalt_b200 import _lib
+    from cobalt_b200.linear import FusedProjections
+    raw = O.synth_raw(64, 14336, 0.5, 4, seed=3)
+    fused = FusedProjections([to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
+    gate = torch.zeros(8, 14336, dtype=torch.bfloat16, device="cuda")
+    assert fused.staged(_lib.IN_GLU, gate, gate, 0) is None
+    raw = O.synth_raw(64, 1152, 0.5, 4, seed=4)                   # 1152 = 4.5 * 256: rows the norm's sum order does not cover
+    fused = FusedProjections([to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
+    h = torch.zeros(1, 1152, dtype=torch.bfloat16, device="cuda")
+    assert fused.staged(_lib.IN_ADDNORM, h, None, 0, w=h[0], eps=1e-5) is None
+
+
 def test_zz_exemption_summary():
     """Collected after the other tests of this file: how often the rounding-boundary exemption was used."""
     total = sum(t for _, t in EXEMPT)

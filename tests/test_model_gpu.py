@@ -172,6 +172,25 @@ def test_batched_decoder_equals_single_sequences():
         assert torch.equal(logits[:, b], l1), b
 
 
+@pytest.mark.parametrize("family,batch", [("llama", 1), ("gemma", 1), ("llama", 3)])
+def test_folded_steps_equal_separate_kernels(family, batch):
+    """The decode step with residual + RMSNorm and the gated activation folded into the projections' activation staging
+    (three launches fewer per layer) against the same decoder running them as separate kernels: identical logits."""
+    from cobalt_b200.decoder import build_random_decoder
+    cfg = gemma_small(layers=2, vocab=1008) if family == "gemma" else \
+        MO.llama_config(hidden=512, layers=2, heads=8, kv_heads=2, head_dim=64, inter=1024, vocab=1008)
+    qcfg = SparseQuantConfig(4, 0.5, 0.5)
+    dev = torch.device("cuda")
+    a = build_random_decoder(cfg, qcfg, 64, dev, batch=batch, head_bits=4, fuse_steps=True)
+    b = build_random_decoder(cfg, qcfg, 64, dev, batch=batch, head_bits=4, fuse_steps=False)
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, 1000, (17,) if batch == 1 else (batch, 17), generator=g)
+    ta, la = a.generate(prompt, 8, use_graph=True)
+    tb, lb = b.generate(prompt, 8, use_graph=True)
+    assert torch.equal(ta, tb)
+    assert torch.equal(la, lb)
+
+
 def test_config3_one_layer_at_7b_width_against_cpu_oracle():
     """One block at the 7B widths (hidden 4096, 32/8 heads of 128, intermediate 14336, vocabulary 32000; 4-bit, 50 %)
     against the oracle on the CPU -- another device, another matmul library: a 64-token prefill within twice the
