@@ -698,6 +698,7 @@ def run_model(args):
     dec = build_random_decoder(cfg, SparseQuantConfig(bits, sparsity, BETA), ctx + n_new, dev, tp_rank=rank, tp_world=world,
                                reducer=reducer, clone_first_layer=args.model == "gemma27b", batch=B, head_bits=args.head_bits)
     dec.fused_prompt_attention = bool(args.fused_prompt_attention)
+    dec.push_partials = bool(args.push)
     g = torch.Generator().manual_seed(2048)
     prompt = torch.randint(0, cfg["vocab_size"], (ctx,) if B == 1 else (B, ctx), generator=g)
     n_pre = min(args.prefill_tokens or ctx, ctx)
@@ -791,6 +792,9 @@ def main():
     ap.add_argument("--model", default="mistral7b", choices=["mistral7b", "gemma27b"], help="shape of --workload model")
     ap.add_argument("--nccl-allreduce", action="store_true", help="multi-GPU: use NCCL instead of the peer-memory all-reduce kernel")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection instead of fused q|k|v and gate|up")
+    ap.add_argument("--push", action="store_true",
+                    help="--workload model, multi-GPU: partial sums pushed by the GEMV and added by the next projection's staging "
+                         "instead of the copy-based peer all-reduce kernel")
     ap.add_argument("--no-extra", action="store_true", help="skip the short prefill and reduced-depth model legs of the default line")
     ap.add_argument("--profile", action="store_true",
                     help="plain launches only: no CUDA graph, no end-to-end leg, no CPU baseline (for ncu captures)")

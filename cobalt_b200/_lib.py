@@ -26,6 +26,15 @@ class CobaltMat(Structure):
     ]
 
 
+class CobaltPeerSlots(Structure):
+    """Mirror of ``struct CobaltPeerSlots``."""
+    _fields_ = [
+        ("peer_base", c_void_p),
+        ("rank", c_int32), ("world", c_int32),
+        ("slot_stride_bytes", c_size_t), ("flags_off_bytes", c_size_t),
+    ]
+
+
 class CobaltStagedInput(Structure):
     """Mirror of ``struct CobaltStagedInput``."""
     _fields_ = [
@@ -34,10 +43,11 @@ class CobaltStagedInput(Structure):
         ("ld", c_int64),
         ("w", c_void_p), ("w_branch", c_void_p), ("h_out", c_void_p),
         ("eps", c_float),
+        ("b_slots", POINTER(CobaltPeerSlots)),
     ]
 
 
-IN_GLU, IN_ADDNORM = 1, 2
+IN_PLAIN, IN_GLU, IN_ADDNORM = 0, 1, 2
 EUNSUPPORTED = -7
 
 
@@ -59,7 +69,8 @@ EXPORTS = {
                                   c_void_p]),
     "cobalt_gemv_fused_scratch_bytes": (c_size_t, [c_int, c_void_p, c_int]),
     "cobalt_gemv_fused_staged": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-                                         c_size_t, c_void_p]),
+                                         c_void_p, c_size_t, c_void_p]),
+    "cobalt_peer_sum": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p]),
     "cobalt_gemv_rowwalk": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                     c_void_p]),
     "cobalt_gemm": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p,

@@ -241,30 +241,53 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
+constexpr size_t SCRATCH_PUSH_DONE_OFF = 128;            // CTA arrival counter of pushing launches, inside the status block
+
+int check_slots(const CobaltPeerSlots* s, size_t floats) {
+    if (!s->peer_base || s->world < 1 || s->world > PEER_MAX_RANKS || s->rank < 0 || s->rank >= s->world) return COBALT_EINVAL;
+    if (floats == 0 || floats * sizeof(float) > s->slot_stride_bytes) return COBALT_EINVAL;
+    if ((s->slot_stride_bytes & 15) || (s->flags_off_bytes & 15) ||
+        s->flags_off_bytes < (size_t)(1 + 2 * s->world) * s->slot_stride_bytes) return COBALT_EINVAL;
+    for (int q = 0; q < s->world; ++q)
+        if (!s->peer_base[q] || (s->peer_base[q] & 15)) return COBALT_EINVAL;
+    return COBALT_OK;
+}
+
 // shared body of every GEMV entry point: `n` matrices that share x, N and the bit width
 struct GemvOut { void* y; int64_t ldy; const void* bias; };
 
 int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void* x, int64_t ldx, int M, bool fp32_out,
-                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, const CobaltStagedInput* in = nullptr) {
+                void* scratch, size_t scratch_bytes, bool clear_counters, void* stream, const CobaltStagedInput* in = nullptr,
+                const CobaltPeerSlots* push = nullptr) {
     if (n < 1 || n > GEMV_MAX_MATS || !w || !out) return COBALT_EINVAL;
     if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
     if (in) {                                                // activations computed while staged: `a` stands in for x in the checks
-        if (in->kind != COBALT_IN_GLU && in->kind != COBALT_IN_ADDNORM) return COBALT_EINVAL;
+        if (in->kind != COBALT_IN_PLAIN && in->kind != COBALT_IN_GLU && in->kind != COBALT_IN_ADDNORM) return COBALT_EINVAL;
         if (in->flavor < 0 || in->flavor > 1 || !in->a) return COBALT_EINVAL;
         if (((uintptr_t)in->b | (uintptr_t)in->w | (uintptr_t)in->w_branch | (uintptr_t)in->h_out) & 15) return COBALT_EINVAL;
         if (in->kind == COBALT_IN_GLU && !in->b) return COBALT_EINVAL;
+        if (in->b_slots && (in->kind != COBALT_IN_ADDNORM || in->b)) return COBALT_EINVAL;
         if (in->kind == COBALT_IN_ADDNORM) {
             if (!in->w || in->h_out == in->a) return COBALT_EINVAL;
-            if (in->w_branch && (in->flavor != 1 || !in->b)) return COBALT_EINVAL;
+            if (in->w_branch && (in->flavor != 1 || !(in->b || in->b_slots))) return COBALT_EINVAL;
+        }
+        if (in->b_slots) {
+            int rc = check_slots(in->b_slots, (size_t)M * w[0]->N);
+            if (rc) return rc;
         }
         x = in->a;
         ldx = in->ld;
+    }
+    if (push) {
+        if (n != 1 || !fp32_out) return COBALT_EINVAL;
+        int rc = check_slots(push, (size_t)M * w[0]->K);
+        if (rc) return rc;
     }
     GemvGeom g = {};
     for (int i = 0; i < n; ++i) {
         int rc = check_mat(w[i]);
         if (rc) return rc;
-        rc = check_io(x, ldx, out[i].y, out[i].ldy, M, w[i]->K, w[i]->N);
+        rc = check_io(x, ldx, push ? x : out[i].y, push ? (int64_t)w[i]->K : out[i].ldy, M, w[i]->K, w[i]->N);
         if (rc) return rc;
         if (i == 0) g = geom_of(w[0]);
         else {
@@ -280,7 +303,8 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     GemvCfg c;
     rc = gemv_config(g, w[0]->N, M, sms, &c);
     if (rc) return rc;
-    if (in && (!c.xs || w[0]->col_scale || (in->kind == COBALT_IN_ADDNORM && w[0]->N % 256 != 0))) return COBALT_EUNSUPPORTED;
+    if (in && in->kind != COBALT_IN_PLAIN &&
+        (!c.xs || w[0]->col_scale || (in->kind == COBALT_IN_ADDNORM && w[0]->N % 256 != 0))) return COBALT_EUNSUPPORTED;
     if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
     cudaStream_t st = (cudaStream_t)stream;
     if (clear_counters) {
@@ -315,8 +339,26 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     P.status = (uint32_t*)scratch;
     P.counters = (uint32_t*)((uint8_t*)scratch + c.counters_off);
     P.partials = (float*)((uint8_t*)scratch + c.partials_off);
-    if (in) {
+    if (push) {
+        P.mode |= GEMV_MODE_PUSH;
+        P.push_world = push->world; P.push_rank = push->rank;
+        for (int q = 0; q < push->world; ++q) P.push_base[q] = push->peer_base[q];
+        P.push_stride = push->slot_stride_bytes; P.push_flags_off = push->flags_off_bytes;
+        P.push_flags = (uint32_t*)(push->peer_base[push->rank] + push->flags_off_bytes);
+        P.push_done = (uint32_t*)((uint8_t*)scratch + SCRATCH_PUSH_DONE_OFF);
+        P.mat[0].ldy = w[0]->K;                              // rows of the slot are [M, K] fp32, dense
+    }
+    if (in && in->kind != COBALT_IN_PLAIN) {
+        if (in->b_slots) {
+            const CobaltPeerSlots* sl = in->b_slots;
+            P.mode |= GEMV_MODE_SUMMED;
+            P.in_world = sl->world;
+            P.in_slots = (const uint8_t*)sl->peer_base[sl->rank];
+            P.in_stride = sl->slot_stride_bytes;
+            P.in_flags = (const uint32_t*)(sl->peer_base[sl->rank] + sl->flags_off_bytes);
+        }
         P.in_kind = in->kind == COBALT_IN_GLU ? GEMV_IN_GLU : GEMV_IN_ADDNORM;
+        P.mode |= P.in_kind;
         P.in_flavor = in->flavor;
         P.in_a = (const uint16_t*)in->a; P.in_b = (const uint16_t*)in->b; P.in_ld = in->ld;
         P.in_w = (const uint16_t*)in->w; P.in_wb = (const uint16_t*)in->w_branch; P.in_hout = (uint16_t*)in->h_out;
@@ -470,13 +512,44 @@ int cobalt_gemv_fused(int n_mats, const CobaltMat* const* w, const void* x, int6
 }
 
 int cobalt_gemv_fused_staged(int n_mats, const CobaltMat* const* w, const CobaltStagedInput* in, void* const* y,
-                             const int64_t* ldy, const void* const* bias, int M, int out_fp32, void* scratch,
-                             size_t scratch_bytes, void* stream) {
-    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !y || !ldy || !in) return COBALT_EINVAL;
+                             const int64_t* ldy, const void* const* bias, int M, int out_fp32,
+                             const CobaltPeerSlots* push, void* scratch, size_t scratch_bytes, void* stream) {
+    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !in) return COBALT_EINVAL;
+    if (!push && (!y || !ldy)) return COBALT_EINVAL;
     if (out_fp32 && bias) return COBALT_EINVAL;
     GemvOut o[GEMV_MAX_MATS];
-    for (int i = 0; i < n_mats; ++i) { o[i].y = y[i]; o[i].ldy = ldy[i]; o[i].bias = bias ? bias[i] : nullptr; }
-    return gemv_launch(n_mats, w, o, nullptr, 0, M, out_fp32 != 0, scratch, scratch_bytes, false, stream, in);
+    for (int i = 0; i < n_mats; ++i) {
+        o[i].y = push ? nullptr : y[i];
+        o[i].ldy = push ? 0 : ldy[i];
+        o[i].bias = bias ? bias[i] : nullptr;
+    }
+    return gemv_launch(n_mats, w, o, nullptr, 0, M, out_fp32 != 0, scratch, scratch_bytes, false, stream, in, push);
+}
+
+int cobalt_peer_sum(const CobaltPeerSlots* slots, size_t n, void* out, int out_fp32, void* status, void* stream) {
+    if (!slots || !out || ((uintptr_t)out & 15) || (n & 7) || n > 0xFFFFFFFFull) return COBALT_EINVAL;
+    int rc = check_slots(slots, n);
+    if (rc) return rc;
+    int sms = 0;
+    rc = device_info(&sms);
+    if (rc) return rc;
+    PeerParams P = {};
+    for (int q = 0; q < slots->world; ++q) P.base[q] = slots->peer_base[q];
+    P.rank = slots->rank; P.world = slots->world; P.n = (unsigned int)n;
+    P.slot_stride = slots->slot_stride_bytes; P.flags_off = slots->flags_off_bytes;
+    P.out = out_fp32 ? nullptr : (uint16_t*)out;
+    P.out32 = out_fp32 ? (float*)out : nullptr;
+    P.status = (uint32_t*)status;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, peer_sum_kernel, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 int cobalt_gemv_rowwalk(const CobaltMat* w, const void* x, int64_t ldx, void* y, int64_t ldy, const void* bias, int M,

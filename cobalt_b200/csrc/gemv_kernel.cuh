@@ -80,6 +80,8 @@ struct GemvParams {
     const uint16_t* x; int64_t ldx;
     const uint4* xperm;                  // activations in fragment order (see x_permute_kernel), used when x is not staged
     int M;
+    int mode;                            // in_kind | GEMV_MODE_PUSH | GEMV_MODE_SUMMED: the one word the common path tests; the
+                                         // fields of the special modes sit at the end, in parameter lines it never touches
     int stages;
     uint32_t slot_bytes;
     uint32_t xs_bytes;                   // shared-memory bytes reserved for staged activations (0: read x from global)
@@ -96,8 +98,19 @@ struct GemvParams {
     int in_kind, in_flavor;
     const uint16_t* in_a; const uint16_t* in_b; int64_t in_ld;
     const uint16_t* in_w; const uint16_t* in_wb; uint16_t* in_hout; float in_eps;
+    // GEMV_IN_ADDNORM whose delta is the sum over ranks of the partials pushed into this rank's peer buffer
+    // (in_world > 0; in_b unused): the staging waits for every rank's flag of the current epoch, then adds the rows
+    int in_world;
+    const uint8_t* in_slots; unsigned long long in_stride; const uint32_t* in_flags;
+    // Row-parallel output (raw fp32 sums) pushed into row `push_rank` of the epoch's slot in EVERY rank's peer buffer
+    // instead of y32 (push_world > 0; single-matrix launches); the last CTA to finish publishes the epoch to all ranks
+    int push_world, push_rank;
+    unsigned long long push_base[PEER_MAX_RANKS];
+    unsigned long long push_stride, push_flags_off;
+    uint32_t* push_flags;                // this rank's flag block (local address)
+    uint32_t* push_done;                 // CTA arrival counter in the launch's scratch, zero between launches
 };
-constexpr int GEMV_IN_GLU = 1, GEMV_IN_ADDNORM = 2;
+constexpr int GEMV_IN_GLU = 1, GEMV_IN_ADDNORM = 2, GEMV_MODE_IN_MASK = 3, GEMV_MODE_PUSH = 4, GEMV_MODE_SUMMED = 8;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -189,6 +202,195 @@ __global__ void x_permute_kernel(const uint16_t* __restrict__ x, int64_t ldx, in
     }
 }
 
+// ---- activations computed while they are staged (out of line: these are the less common launches)
+__device__ __forceinline__ void gemv_stage_chunk(uint8_t* xs, int chunks_per_row, int m, int c, const uint4& v) {
+    const int pc = c ^ (((c >> 4) & 3) | ((m & 1) << 2));
+    *reinterpret_cast<uint4*>(xs + ((size_t)m * chunks_per_row + pc) * 16) = v;
+}
+
+__device__ __noinline__ void gemv_stage_glu(const GemvParams& P, uint8_t* xs) {
+    constexpr int XPRE = 2;
+    const int chunks_per_row = P.N / 8, x_total = chunks_per_row * P.M;
+    auto stage_chunk = [&](int m, int c, const uint4& v) { gemv_stage_chunk(xs, chunks_per_row, m, c, v); };
+    // gated activation of the two halves of the previous projection, applied while staging
+    // (the reference closes it in the gate|up epilogue: src/cobaltkernel/csrc/megakernel.cu:1805-1892)
+    auto ld_a = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_a + (size_t)m * P.in_ld) + c); };
+    auto ld_b = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_b + (size_t)m * P.in_ld) + c); };
+    uint4 ga[XPRE], ub[XPRE];
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+        if (i < x_total) { const int m = i / chunks_per_row, c = i - m * chunks_per_row; ga[q] = ld_a(m, c); ub[q] = ld_b(m, c); }
+    }
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+        if (i < x_total) { const int m = i / chunks_per_row; stage_chunk(m, i - m * chunks_per_row, glu_chunk(ga[q], ub[q], P.in_flavor)); }
+    }
+    for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+        const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+        stage_chunk(m, c, glu_chunk(ld_a(m, c), ld_b(m, c), P.in_flavor));
+    }
+}
+
+__device__ __noinline__ void gemv_stage_addnorm(const GemvParams& P, uint8_t* xs, float* red) {
+    constexpr int XPRE = 2;
+    const int lane = threadIdx.x & 31;
+    const int chunks_per_row = P.N / 8, x_total = chunks_per_row * P.M;
+    auto stage_chunk = [&](int m, int c, const uint4& v) { gemv_stage_chunk(xs, chunks_per_row, m, c, v); };
+    // residual add + RMSNorm applied while staging (the reference normalises while it writes its activation
+    // copy: write_xprime, src/cobaltkernel/csrc/megakernel.cu:270-288); rows are multiples of 256 values, so the
+    // 32 chunks a warp handles in one step belong to one row.  Warp totals live in the (still unused) fragment area.
+    float* tot_branch = red;
+    float* tot_joined = red + 1024;
+    const int groups = chunks_per_row >> 5;
+    const bool has_delta = P.in_b != nullptr, norm_branch = (has_delta || (P.mode & GEMV_MODE_SUMMED)) && P.in_wb != nullptr;
+    const bool summed = (P.mode & GEMV_MODE_SUMMED) != 0;                            // delta = sum of the ranks' pushed partials
+    const bool has_delta2 = has_delta || summed;
+    const uint8_t* slot_row0 = nullptr;
+    auto ld_h = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_a + (size_t)m * P.in_ld) + c); };
+    auto ld_d = [&](int m, int c) {
+        if (summed) return peer_sum_chunk(slot_row0, P.in_stride, P.in_world, (size_t)m * P.N + (size_t)c * 8);
+        return __ldg(reinterpret_cast<const uint4*>(P.in_b + (size_t)m * P.in_ld) + c);
+    };
+    uint4 hq[XPRE], dq[XPRE];
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+        if (i < x_total) { const int m = i / chunks_per_row; hq[q] = ld_h(m, i - m * chunks_per_row); }
+    }
+    if (summed) {                                                  // bounded wait for every rank's partial of this epoch
+        const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(P.in_flags + PEER_EPOCH_INDEX);
+        slot_row0 = P.in_slots + (1ull + (unsigned long long)(e & 1u) * P.in_world) * P.in_stride;
+        if (!peer_wait_epoch(P.in_flags, P.in_world, e) && threadIdx.x == 0) atomicCAS(P.status, 0u, (uint32_t)DEV_TIMEOUT_PEER);
+    }
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+        dq[q] = make_uint4(0, 0, 0, 0);
+        if (i < x_total && has_delta2) { const int m = i / chunks_per_row; dq[q] = ld_d(m, i - m * chunks_per_row); }
+    }
+    if (norm_branch) {                                             // sums of delta^2 per row
+        auto branch_total = [&](int i, const uint4& dd) {          // i < x_total is the same for all lanes of a warp
+            float d[8];
+            chunk_to_floats(dd, d);
+            const float s = warp_butterfly_sum(i < x_total ? chunk_sumsq(d) : 0.0f);
+            if (lane == 0 && i < x_total) tot_branch[i >> 5] = s;
+        };
+#pragma unroll
+        for (int q = 0; q < XPRE; ++q) branch_total(threadIdx.x + q * GEMV_THREADS, dq[q]);
+        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+            const int m = i / chunks_per_row;
+            branch_total(i, ld_d(m, i - m * chunks_per_row));
+        }
+        __syncthreads();
+    }
+    auto joined_chunk = [&](int m, int c, const uint4& hh, const uint4& dd, float (&v)[8]) {      // h' of one chunk
+        chunk_to_floats(hh, v);
+        if (has_delta2) {
+            float d[8];
+            chunk_to_floats(dd, d);
+            if (norm_branch) {
+                const float rb = row_rsqrt(tot_branch + m * groups, groups, P.N, P.in_eps);
+                float wb[8];
+                chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(P.in_wb) + c), wb);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) d[k] = branch_value(d[k], rb, wb[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = joined_value(v[k], d[k]);
+        }
+    };
+    const bool writes_h = blockIdx.x == 0 && P.in_hout != nullptr;
+    auto joined_total = [&](int i, const float (&v)[8]) {
+        const float s = warp_butterfly_sum(i < x_total ? chunk_sumsq(v) : 0.0f);
+        if (lane == 0 && i < x_total) tot_joined[i >> 5] = s;
+        if (writes_h && i < x_total) {
+            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+            reinterpret_cast<uint4*>(P.in_hout + (size_t)m * P.in_ld)[c] = floats_to_chunk(v);
+        }
+    };
+    float vk[XPRE][8];
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vk[q][k] = 0.0f;
+        if (i < x_total) { const int m = i / chunks_per_row; joined_chunk(m, i - m * chunks_per_row, hq[q], dq[q], vk[q]); }
+        joined_total(i, vk[q]);
+    }
+    for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
+        const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+        float v[8];
+        joined_chunk(m, c, ld_h(m, c), has_delta2 ? ld_d(m, c) : make_uint4(0, 0, 0, 0), v);
+        joined_total(i, v);
+    }
+    __syncthreads();
+    auto normed_chunk = [&](int m, int c, const float (&v)[8]) {
+        const float r = row_rsqrt(tot_joined + m * groups, groups, P.N, P.in_eps);
+        float wn[8], o[8];
+        chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(P.in_w) + c), wn);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = normed_value(v[k], r, wn[k], P.in_flavor);
+        stage_chunk(m, c, floats_to_chunk(o));
+    };
+#pragma unroll
+    for (int q = 0; q < XPRE; ++q) {
+        const int i = threadIdx.x + q * GEMV_THREADS;
+        if (i < x_total) { const int m = i / chunks_per_row; normed_chunk(m, i - m * chunks_per_row, vk[q]); }
+    }
+    for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {         // the rest is recomputed, not kept
+        const int m = i / chunks_per_row, c = i - m * chunks_per_row;
+        float v[8];
+        joined_chunk(m, c, ld_h(m, c), has_delta2 ? ld_d(m, c) : make_uint4(0, 0, 0, 0), v);
+        normed_chunk(m, c, v);
+    }
+}
+
+// rows of one finished row block of a pushing launch -> row `push_rank` of the epoch's slot in every rank's buffer
+template <int MT>
+__device__ __noinline__ void gemv_push_rows(const GemvParams& P, uint32_t epoch, int ldy, int K, int row0, const float (&acc)[MT][4]) {
+    const int t = threadIdx.x & 3, row1 = row0 + 8;
+    const unsigned long long row_off = (1ull + (unsigned long long)(epoch & 1u) * P.push_world + P.push_rank) * P.push_stride;
+#pragma unroll
+    for (int q = 0; q < PEER_MAX_RANKS; ++q) {
+        if (q >= P.push_world) break;
+        float* dst = reinterpret_cast<float*>(P.push_base[q] + row_off);
+#pragma unroll
+        for (int b = 0; b < MT; ++b) {
+            const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
+            if (row0 < K) {
+                if (tok0 < P.M) dst[(size_t)tok0 * ldy + row0] = acc[b][0];
+                if (tok1 < P.M) dst[(size_t)tok1 * ldy + row0] = acc[b][1];
+            }
+            if (row1 < K) {
+                if (tok0 < P.M) dst[(size_t)tok0 * ldy + row1] = acc[b][2];
+                if (tok1 < P.M) dst[(size_t)tok1 * ldy + row1] = acc[b][3];
+            }
+        }
+    }
+}
+
+// Every row this CTA pushed is on its way; the last CTA of the launch to get here tells every rank that this rank's
+// partial of the epoch is complete (the consumer - the next projection's staging or the summing kernel - waits for
+// these flags).  A launch that gave up (status word set) still publishes: its peers then read rows it did not finish,
+// which the status word reports, instead of running into their own time-out.
+__device__ __noinline__ void gemv_push_publish(const GemvParams& P, uint32_t epoch) {
+    __syncthreads();                                                   // the CTA's stores are ordered before thread 0's fence
+    if (threadIdx.x == 0) {
+        __threadfence_system();                                        // one system-scope fence per CTA, cumulative over the barrier
+        const uint32_t old = atom_add_acq_rel_gpu(P.push_done, 1u);
+        if (old == gridDim.x - 1u) {
+            *P.push_done = 0u;
+            P.push_flags[PEER_EPOCH_INDEX] = epoch;
+#pragma unroll
+            for (int q = 0; q < PEER_MAX_RANKS; ++q)
+                if (q < P.push_world)
+                    st_release_sys_u32(reinterpret_cast<uint32_t*>(P.push_base[q] + P.push_flags_off) + P.push_rank, epoch);
+        }
+    }
+}
+
 // what one unit (16 columns of both rows of a lane) reads from memory; requested one unit ahead
 template <int MT>
 struct GemvUnit {
@@ -198,7 +400,7 @@ struct GemvUnit {
 };
 
 template <int BITS, int MT, bool XS>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvParams P) {
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -302,6 +504,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
     // Programmatic dependent launch: everything above touched only the weights and this CTA's shared
     // memory.  From here on the activations and the scratch of the previous kernel in the stream are used.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // pushing launches: the epoch of this all-reduce (the last CTA to finish advances the counter, after every CTA read it)
+    // (kept in shared memory, word 2 of the counter block: it is needed only when rows are stored)
+    volatile uint32_t* push_epoch_s = red_cnt + 2;
+    if ((P.mode & GEMV_MODE_PUSH) && threadIdx.x == 0) *push_epoch_s = *reinterpret_cast<volatile uint32_t*>(P.push_flags + PEER_EPOCH_INDEX) + 1u;
     // x -> shared memory, rows of N bf16, 16-byte chunk c of token m stored at chunk c ^ swizzle(group, m).  The
     // first chunks of every thread are requested before the table is built, so that their latency hides behind it.
     constexpr int XPRE = 2;
@@ -319,7 +525,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         const int pc = c ^ (((c >> 4) & 3) | ((m & 1) << 2));
         *reinterpret_cast<uint4*>(xs + ((size_t)m * chunks_per_row + pc) * 16) = v;
     };
-    if (!XS || P.in_kind == 0) {
+    if (!XS || (P.mode & GEMV_MODE_IN_MASK) == 0) {
         uint4 xpre[XPRE];
 #pragma unroll
         for (int q = 0; q < XPRE; ++q) {
@@ -339,124 +545,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
             const int m = i / chunks_per_row, c = i - m * chunks_per_row;
             stage_chunk(m, c, __ldg(reinterpret_cast<const uint4*>(P.x + (size_t)m * P.ldx) + c));
         }
-    } else if (P.in_kind == GEMV_IN_GLU) {
-        // gated activation of the two halves of the previous projection, applied while staging
-        // (the reference closes it in the gate|up epilogue: src/cobaltkernel/csrc/megakernel.cu:1805-1892)
-        auto ld_a = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_a + (size_t)m * P.in_ld) + c); };
-        auto ld_b = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_b + (size_t)m * P.in_ld) + c); };
-        uint4 ga[XPRE], ub[XPRE];
-#pragma unroll
-        for (int q = 0; q < XPRE; ++q) {
-            const int i = threadIdx.x + q * GEMV_THREADS;
-            if (i < x_total) { const int m = i / chunks_per_row, c = i - m * chunks_per_row; ga[q] = ld_a(m, c); ub[q] = ld_b(m, c); }
-        }
-        fill_table();
-#pragma unroll
-        for (int q = 0; q < XPRE; ++q) {
-            const int i = threadIdx.x + q * GEMV_THREADS;
-            if (i < x_total) { const int m = i / chunks_per_row; stage_chunk(m, i - m * chunks_per_row, glu_chunk(ga[q], ub[q], P.in_flavor)); }
-        }
-        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
-            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-            stage_chunk(m, c, glu_chunk(ld_a(m, c), ld_b(m, c), P.in_flavor));
-        }
     } else {
-        // residual add + RMSNorm applied while staging (the reference normalises while it writes its activation
-        // copy: write_xprime, src/cobaltkernel/csrc/megakernel.cu:270-288); rows are multiples of 256 values, so the
-        // 32 chunks a warp handles in one step belong to one row.  Warp totals live in the (still unused) fragment area.
-        float* tot_branch = red;
-        float* tot_joined = red + 1024;
-        const int groups = chunks_per_row >> 5;
-        const bool has_delta = P.in_b != nullptr, norm_branch = has_delta && P.in_wb != nullptr;
-        auto ld_h = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_a + (size_t)m * P.in_ld) + c); };
-        auto ld_d = [&](int m, int c) { return __ldg(reinterpret_cast<const uint4*>(P.in_b + (size_t)m * P.in_ld) + c); };
-        uint4 hq[XPRE], dq[XPRE];
-#pragma unroll
-        for (int q = 0; q < XPRE; ++q) {
-            const int i = threadIdx.x + q * GEMV_THREADS;
-            dq[q] = make_uint4(0, 0, 0, 0);
-            if (i < x_total) {
-                const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-                hq[q] = ld_h(m, c);
-                if (has_delta) dq[q] = ld_d(m, c);
-            }
-        }
+        // special inputs: computed while staged, out of line so that they do not weigh on the common path's code
         fill_table();
-        if (norm_branch) {                                             // sums of delta^2 per row
-            auto branch_total = [&](int i, const uint4& dd) {          // i < x_total is the same for all lanes of a warp
-                float d[8];
-                chunk_to_floats(dd, d);
-                const float s = warp_butterfly_sum(i < x_total ? chunk_sumsq(d) : 0.0f);
-                if (lane == 0 && i < x_total) tot_branch[i >> 5] = s;
-            };
-#pragma unroll
-            for (int q = 0; q < XPRE; ++q) branch_total(threadIdx.x + q * GEMV_THREADS, dq[q]);
-            for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
-                const int m = i / chunks_per_row;
-                branch_total(i, ld_d(m, i - m * chunks_per_row));
-            }
-            __syncthreads();
-        }
-        auto joined_chunk = [&](int m, int c, const uint4& hh, const uint4& dd, float (&v)[8]) {      // h' of one chunk
-            chunk_to_floats(hh, v);
-            if (has_delta) {
-                float d[8];
-                chunk_to_floats(dd, d);
-                if (norm_branch) {
-                    const float rb = row_rsqrt(tot_branch + m * groups, groups, P.N, P.in_eps);
-                    float wb[8];
-                    chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(P.in_wb) + c), wb);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) d[k] = branch_value(d[k], rb, wb[k]);
-                }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = joined_value(v[k], d[k]);
-            }
-        };
-        const bool writes_h = blockIdx.x == 0 && P.in_hout != nullptr;
-        auto joined_total = [&](int i, const float (&v)[8]) {
-            const float s = warp_butterfly_sum(i < x_total ? chunk_sumsq(v) : 0.0f);
-            if (lane == 0 && i < x_total) tot_joined[i >> 5] = s;
-            if (writes_h && i < x_total) {
-                const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-                reinterpret_cast<uint4*>(P.in_hout + (size_t)m * P.in_ld)[c] = floats_to_chunk(v);
-            }
-        };
-        float vk[XPRE][8];
-#pragma unroll
-        for (int q = 0; q < XPRE; ++q) {
-            const int i = threadIdx.x + q * GEMV_THREADS;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) vk[q][k] = 0.0f;
-            if (i < x_total) { const int m = i / chunks_per_row; joined_chunk(m, i - m * chunks_per_row, hq[q], dq[q], vk[q]); }
-            joined_total(i, vk[q]);
-        }
-        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {
-            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-            float v[8];
-            joined_chunk(m, c, ld_h(m, c), has_delta ? ld_d(m, c) : make_uint4(0, 0, 0, 0), v);
-            joined_total(i, v);
-        }
-        __syncthreads();
-        auto normed_chunk = [&](int m, int c, const float (&v)[8]) {
-            const float r = row_rsqrt(tot_joined + m * groups, groups, P.N, P.in_eps);
-            float wn[8], o[8];
-            chunk_to_floats(__ldg(reinterpret_cast<const uint4*>(P.in_w) + c), wn);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) o[k] = normed_value(v[k], r, wn[k], P.in_flavor);
-            stage_chunk(m, c, floats_to_chunk(o));
-        };
-#pragma unroll
-        for (int q = 0; q < XPRE; ++q) {
-            const int i = threadIdx.x + q * GEMV_THREADS;
-            if (i < x_total) { const int m = i / chunks_per_row; normed_chunk(m, i - m * chunks_per_row, vk[q]); }
-        }
-        for (int i = threadIdx.x + XPRE * GEMV_THREADS; i < x_total; i += GEMV_THREADS) {         // the rest is recomputed, not kept
-            const int m = i / chunks_per_row, c = i - m * chunks_per_row;
-            float v[8];
-            joined_chunk(m, c, ld_h(m, c), has_delta ? ld_d(m, c) : make_uint4(0, 0, 0, 0), v);
-            normed_chunk(m, c, v);
-        }
+        if ((P.mode & GEMV_MODE_IN_MASK) == GEMV_IN_GLU) gemv_stage_glu(P, xs);
+        else gemv_stage_addnorm(P, xs, red);
     }
     mbar_arrive(xbar);                                                 // releases this thread's table and x stores
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -473,6 +566,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
         mt.y = MAT_FIELD(mi, y); mt.y32 = MAT_FIELD(mi, y32); mt.bias = MAT_FIELD(mi, bias); mt.ldy = MAT_FIELD(mi, ldy);
         mt.K = MAT_FIELD(mi, K); mt.rb_start = MAT_FIELD(mi, rb_start);
         const int row0 = (rb - mt.rb_start) * TILE_ROWS + g, row1 = row0 + 8;
+        if (P.mode & GEMV_MODE_PUSH) {                                 // the partial goes straight into every rank's slot
+            gemv_push_rows<MT>(P, *push_epoch_s, (int)mt.ldy, mt.K, row0, acc);
+            return;
+        }
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
@@ -766,27 +863,29 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvPar
 
     // ---- row blocks shared by warps of this CTA only: first holder adds the parked fragments in warp order
     __syncthreads();
-    if (!healthy) return;
-    const int lane_tag = red_tag[lane];                                // GEMV_WARPS * 2 == 32 slots: one per lane
+    if (healthy) {
+        const int lane_tag = red_tag[lane];                            // GEMV_WARPS * 2 == 32 slots: one per lane
 #pragma unroll 1
-    for (int side = 0; side < 2; ++side) {
-        const int slot_id = warp * 2 + side;
-        const int tag = __shfl_sync(full, lane_tag, slot_id);
-        if (tag < 0) continue;
-        uint32_t holders = __ballot_sync(full, lane_tag == tag);       // parked fragments of this row block, in warp order
-        if ((int)__ffs(holders) - 1 != slot_id) continue;              // only the first holder reduces
-        clear_acc();
-        while (holders) {
-            const int k = __ffs(holders) - 1;
-            holders &= holders - 1u;
-            const float* src = red + k * FR;
+        for (int side = 0; side < 2; ++side) {
+            const int slot_id = warp * 2 + side;
+            const int tag = __shfl_sync(full, lane_tag, slot_id);
+            if (tag < 0) continue;
+            uint32_t holders = __ballot_sync(full, lane_tag == tag);   // parked fragments of this row block, in warp order
+            if ((int)__ffs(holders) - 1 != slot_id) continue;          // only the first holder reduces
+            clear_acc();
+            while (holders) {
+                const int k = __ffs(holders) - 1;
+                holders &= holders - 1u;
+                const float* src = red + k * FR;
 #pragma unroll
-            for (int b = 0; b < MT; ++b)
+                for (int b = 0; b < MT; ++b)
 #pragma unroll
-                for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
+                    for (int r = 0; r < 4; ++r) acc[b][r] += src[(b * 4 + r) * 32 + lane];
+            }
+            store_rows(tag);
         }
-        store_rows(tag);
     }
+    if (P.mode & GEMV_MODE_PUSH) gemv_push_publish(P, *push_epoch_s);
 }
 
 }  // namespace cb

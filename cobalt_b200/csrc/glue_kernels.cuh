@@ -421,9 +421,6 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* part, co
 // so replaying a captured graph advances it like eager calls do.  Two slots alternate, so that a rank that is ahead
 // never overwrites a row that a peer is still reading (a rank can only finish epoch e after every peer has started
 // it, i.e. has finished reading epoch e-1).
-constexpr int PEER_MAX_RANKS = 8;
-constexpr int PEER_EPOCH_INDEX = 16;       // u32 index of the local epoch counter behind the flags
-
 struct PeerParams {
     unsigned long long base[PEER_MAX_RANKS];   // every rank's symmetric buffer, as mapped into this process
     int rank, world;
@@ -433,12 +430,6 @@ struct PeerParams {
     float* out32;                              // or fp32 [n]
     uint32_t* status;
 };
-
-__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
 
 __global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P) {
     __shared__ uint32_t epoch_s;
@@ -501,6 +492,34 @@ __global__ void __launch_bounds__(1024) peer_allreduce_kernel(const PeerParams P
             o.x = (uint32_t)float_to_bf16(s.x) | ((uint32_t)float_to_bf16(s.y) << 16);
             o.y = (uint32_t)float_to_bf16(s.z) | ((uint32_t)float_to_bf16(s.w) << 16);
             reinterpret_cast<uint2*>(P.out)[i] = o;
+        }
+    }
+}
+
+// The summing half alone, for partials that a pushing GEMV already placed in every rank's slot and published: waits
+// (bounded) for all flags of the current epoch, adds the rows in rank order from local memory, rounds once.
+__global__ void __launch_bounds__(1024) peer_sum_kernel(const PeerParams P) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(P.base[P.rank] + P.flags_off);
+    const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(my_flags + PEER_EPOCH_INDEX);
+    if (!peer_wait_epoch(my_flags, P.world, epoch)) {
+        if (threadIdx.x == 0 && P.status) atomicCAS(P.status, 0u, (uint32_t)DEV_TIMEOUT_PEER);
+        return;
+    }
+    const uint8_t* row0 = reinterpret_cast<const uint8_t*>(P.base[P.rank] + (1ull + (unsigned long long)(epoch & 1u) * P.world) * P.slot_stride);
+    for (unsigned int i = threadIdx.x; i < (P.n >> 3); i += 1024) {    // n is a multiple of 8 (checked on the host)
+        if (P.out32) {
+            float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b = a;
+            for (int q = 0; q < P.world; ++q) {
+                const float* p = reinterpret_cast<const float*>(row0 + (unsigned long long)q * P.slot_stride) + 8 * (size_t)i;
+                const float4 u = ld_sys_f4(p), v = ld_sys_f4(p + 4);
+                a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w; b.x += v.x; b.y += v.y; b.z += v.z; b.w += v.w;
+            }
+            reinterpret_cast<float4*>(P.out32)[2 * i] = a;
+            reinterpret_cast<float4*>(P.out32)[2 * i + 1] = b;
+        } else {
+            reinterpret_cast<uint4*>(P.out)[i] = peer_sum_chunk(row0, P.slot_stride, P.world, 8 * (size_t)i);
         }
     }
 }

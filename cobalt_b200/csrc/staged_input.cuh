@@ -19,6 +19,66 @@ namespace cb {
 
 __device__ __forceinline__ float bf16_round(float f) { return bf16_to_float(float_to_bf16(f)); }
 
+// ---- partial sums of a row-parallel layer exchanged over peer memory (layout shared by the GEMV's pushing epilogue,
+// its summing activation staging and the stand-alone kernels in glue_kernels.cuh).  Every rank owns one buffer:
+//   [0, stride)                              staging area of the copy-based all-reduce
+//   (1 + s * world + r) * stride             row r (= the partial of rank r) of slot s, s = epoch & 1
+//   flags_off + 4 * r                        epoch of the last complete partial received from rank r
+//   flags_off + 4 * PEER_EPOCH_INDEX         epoch of the last all-reduce this rank started
+constexpr int PEER_MAX_RANKS = 8;
+constexpr int PEER_EPOCH_INDEX = 16;
+__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// waits (bounded, about a second) until flags[0 .. world) have all reached `epoch`; threads 0 .. world-1 poll, every
+// thread of the CTA gets the verdict
+__device__ __forceinline__ bool peer_wait_epoch(const uint32_t* flags, int world, uint32_t epoch) {
+    bool good = true;
+    if ((int)threadIdx.x < world) {
+        good = false;
+        for (uint32_t it = 0; it < (1u << 20); ++it) {
+            if ((int32_t)(ld_acquire_sys_u32(flags + threadIdx.x) - epoch) >= 0) { good = true; break; }
+            if (it > 1024) __nanosleep(128);
+        }
+    }
+    return __syncthreads_and(good ? 1 : 0) != 0;
+}
+// 8 consecutive values of the sum over ranks (rank order, fp32), rounded to bf16 once
+__device__ __forceinline__ uint4 peer_sum_chunk(const uint8_t* slot_row0, unsigned long long stride, int world, size_t first_float) {
+    float s[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+    for (int q0 = 0; q0 < world; q0 += 4) {                            // four ranks' loads in flight at a time
+        float4 v[4][2];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (q0 + q < world) {
+                const float* p = reinterpret_cast<const float*>(slot_row0 + (unsigned long long)(q0 + q) * stride) + first_float;
+                v[q][0] = ld_sys_f4(p);
+                v[q][1] = ld_sys_f4(p + 4);
+            }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (q0 + q < world) {
+                s[0] += v[q][0].x; s[1] += v[q][0].y; s[2] += v[q][0].z; s[3] += v[q][0].w;
+                s[4] += v[q][1].x; s[5] += v[q][1].y; s[6] += v[q][1].z; s[7] += v[q][1].w;
+            }
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w[k] = (uint32_t)float_to_bf16(s[2 * k]) | ((uint32_t)float_to_bf16(s[2 * k + 1]) << 16);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 __device__ __forceinline__ void chunk_to_floats(const uint4& c, float (&f)[8]) {
     const uint32_t w[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll

@@ -335,11 +335,14 @@ class FusedProjections:
 
     def staged(self, kind: int, a: torch.Tensor, b: Optional[torch.Tensor], flavor: int, w: Optional[torch.Tensor] = None,
                w_branch: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None, eps: float = 0.0,
-               out_fp32: bool = False, outs=None):
+               out_fp32: bool = False, outs=None, push=None, delta_slots=None):
         """One launch in which the kernel computes its activation rows while it stages them (``cobalt_gemv_fused_staged``):
         ``kind = _lib.IN_GLU``: rows ``act(a) * b``; ``kind = _lib.IN_ADDNORM``: rows ``RMSNorm(a + b) * w`` with
-        ``a + b`` written to ``h_out``.  ``a``, ``b``, ``h_out``: ``[M, in_features]`` bf16.  Returns the outputs, or
-        ``None`` when this shape cannot take the fused path (nothing was launched: call the separate steps)."""
+        ``a + b`` written to ``h_out``; ``kind = _lib.IN_PLAIN``: rows ``a``.  ``a``, ``b``, ``h_out``: ``[M, in_features]``
+        bf16.  Tensor parallelism: ``push`` (a ``tp.PeerReducer``) sends the fp32 sums of this rank into every rank's
+        slot instead of returning them (one matrix; returns ``[]``); ``delta_slots`` (a ``tp.PeerReducer``) takes
+        ``b`` = the sum over ranks of the partials pushed before.  Returns the outputs, or ``None`` when this shape cannot
+        take the fused path (nothing was launched: call the separate steps)."""
         M = a.shape[0]
         if M > GEMV_MAX_TOKENS or M == 0 or a.dim() != 2 or a.stride(-1) != 1:
             return None
@@ -349,14 +352,19 @@ class FusedProjections:
         lib = _lib.load()
         n = len(self.mods)
         descs = self._prepare(M, a.device)
-        ys = outs if outs is not None else [torch.empty(M, m.out_features, dtype=torch.float32 if out_fp32 else torch.bfloat16,
-                                                         device=a.device) for m in self.mods]
-        yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
-        ld = (ctypes.c_int64 * n)(*[m.out_features if y.dim() == 1 else y.stride(0) for y, m in zip(ys, self.mods)])
         ptr = lambda t: None if t is None else t.data_ptr()
-        inp = _lib.CobaltStagedInput(kind, flavor, a.data_ptr(), ptr(b), a.stride(0), ptr(w), ptr(w_branch), ptr(h_out), eps)
+        inp = _lib.CobaltStagedInput(kind, flavor, a.data_ptr(), ptr(b), a.stride(0), ptr(w), ptr(w_branch), ptr(h_out), eps,
+                                     None if delta_slots is None else ctypes.pointer(delta_slots.slots))
         sp = (self._scratch.data_ptr() + 255) // 256 * 256
-        rc = lib.cobalt_gemv_fused_staged(n, descs, ctypes.byref(inp), yp, ld, None, M, 1 if out_fp32 else 0, sp,
+        if push is not None:
+            ys, yp, ld, out_fp32 = [], None, None, True
+        else:
+            ys = outs if outs is not None else [torch.empty(M, m.out_features, dtype=torch.float32 if out_fp32 else torch.bfloat16,
+                                                             device=a.device) for m in self.mods]
+            yp = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+            ld = (ctypes.c_int64 * n)(*[m.out_features if y.dim() == 1 else y.stride(0) for y, m in zip(ys, self.mods)])
+        rc = lib.cobalt_gemv_fused_staged(n, descs, ctypes.byref(inp), yp, ld, None, M, 1 if out_fp32 else 0,
+                                          None if push is None else ctypes.byref(push.slots), sp,
                                           self._scratch.numel() - (sp - self._scratch.data_ptr()),
                                           torch.cuda.current_stream(a.device).cuda_stream)
         if rc == _lib.EUNSUPPORTED:

@@ -20,6 +20,8 @@ from __future__ import annotations
 
 from typing import Callable, Optional
 
+import ctypes
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -103,6 +105,7 @@ class PeerReducer:
         self.handle = symm.rendezvous(self.buf, self.group)
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self._ptrs = (ctypes.c_uint64 * self.world)(*ptrs)
+        self.slots = _lib.CobaltPeerSlots(ctypes.cast(self._ptrs, ctypes.c_void_p), self.rank, self.world, self.stride, self.flags_off)
         self.status = torch.zeros(64, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(self.group)                     # every buffer is zeroed before anyone publishes a flag
@@ -122,6 +125,17 @@ class PeerReducer:
                                              out.data_ptr(), 1 if out.dtype == torch.float32 else 0, self.status.data_ptr(),
                                              torch.cuda.current_stream(out.device).cuda_stream)
         _lib.check("cobalt_allreduce_peer", rc)
+        return out
+
+    def sum_pushed(self, n: int, out: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks of the partials that a pushing GEMV (``FusedProjections.staged(..., push=self)``) left in this
+        rank's buffer, into ``out`` (bf16 or fp32, ``n`` elements): the summing half of ``reduce`` as its own kernel."""
+        from . import _lib
+        if out.numel() != n or not out.is_contiguous() or out.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("`out` must be a contiguous bf16 or fp32 tensor of n elements")
+        rc = self._lib.cobalt_peer_sum(ctypes.byref(self.slots), n, out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+                                       self.status.data_ptr(), torch.cuda.current_stream(out.device).cuda_stream)
+        _lib.check("cobalt_peer_sum", rc)
         return out
 
     def device_status(self) -> int:

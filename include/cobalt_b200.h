@@ -106,23 +106,49 @@ size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, in
  * a, b, h_out are [M, in_features] bf16 with row stride ld (elements), 16-byte aligned; results are bit-identical
  * to the separate entry points followed by cobalt_gemv_fused().  Only launches that stage their activations can
  * take this path (M <= 8 and M * in_features * 2 bytes beside the weight ring; COBALT_IN_ADDNORM also needs
- * in_features % 256 == 0): otherwise COBALT_EUNSUPPORTED is returned and nothing is launched. */
+ * in_features % 256 == 0): otherwise COBALT_EUNSUPPORTED is returned and nothing is launched.  COBALT_IN_PLAIN
+ * (a = x) takes every shape.
+ *
+ * Tensor parallelism, the all-reduce of a row-parallel projection folded into the two kernels around it (the
+ * reference runs on one GPU; its column/row split is docs/FORMAT.md:126-151 and it has no counterpart of this exchange):
+ *   `push` (output side)   the raw fp32 sums of THIS rank go, row block by row block as they finish, into row `rank`
+ *                          of the current epoch's slot in EVERY rank's peer buffer (plain NVLink stores; layout as for
+ *                          cobalt_allreduce_peer()); the last CTA to finish publishes the epoch in every rank's flag
+ *                          block.  One matrix, out_fp32 = 1, y is not written (may hold NULLs).
+ *   `in->b_slots` (input side, COBALT_IN_ADDNORM)  delta = bf16( sum over ranks, in rank order, of the rows pushed
+ *                          into this rank's buffer ): the staging waits (bounded, about a second, then status
+ *                          COBALT_ETIMEOUT through cobalt_device_status) for every rank's flag, then adds the rows
+ *                          from local memory.  b must be NULL.
+ *   cobalt_peer_sum()      the same sum as a kernel of its own, for consumers that cannot take the staged form.
+ * Results equal cobalt_allreduce_peer() bit for bit.  All ranks must make the same sequence of calls on one buffer. */
+#define COBALT_IN_PLAIN    0
 #define COBALT_IN_GLU      1
 #define COBALT_IN_ADDNORM  2
+typedef struct CobaltPeerSlots {
+    const uint64_t* peer_base;      /* [world] every rank's buffer as mapped into this process, 16-byte aligned */
+    int rank, world;
+    size_t slot_stride_bytes;       /* bytes of one row; flags_off_bytes >= (1 + 2 * world) * slot_stride_bytes */
+    size_t flags_off_bytes;
+} CobaltPeerSlots;
 typedef struct CobaltStagedInput {
-    int kind;                       /* COBALT_IN_GLU or COBALT_IN_ADDNORM */
+    int kind;                       /* COBALT_IN_PLAIN (a = x), COBALT_IN_GLU or COBALT_IN_ADDNORM */
     int flavor;
-    const void* a;                  /* gate, or the residual stream h */
-    const void* b;                  /* up, or delta (NULL: h' = h) */
+    const void* a;                  /* x, gate, or the residual stream h */
+    const void* b;                  /* up, or delta (NULL: h' = h unless b_slots is given) */
     int64_t ld;
     const void* w;                  /* COBALT_IN_ADDNORM: norm weight [in_features] bf16 */
     const void* w_branch;           /* COBALT_IN_ADDNORM, flavor 1: weight of the norm applied to delta first, or NULL */
     void* h_out;                    /* COBALT_IN_ADDNORM: h' [M, in_features], or NULL */
     float eps;
+    const CobaltPeerSlots* b_slots; /* COBALT_IN_ADDNORM: delta is the sum of the ranks' pushed partials, or NULL */
 } CobaltStagedInput;
 int cobalt_gemv_fused_staged(int n_mats, const CobaltMat* const* w, const CobaltStagedInput* in, void* const* y,
-                             const int64_t* ldy, const void* const* bias, int M, int out_fp32, void* scratch,
-                             size_t scratch_bytes, void* stream);
+                             const int64_t* ldy, const void* const* bias, int M, int out_fp32,
+                             const CobaltPeerSlots* push, void* scratch, size_t scratch_bytes, void* stream);
+/* out[n] = bf16 (or fp32 when out_fp32) of the sum over ranks of the partials a pushing cobalt_gemv_fused_staged()
+ * left in this rank's buffer: waits (bounded) for every rank's flag of the current epoch.  `status` as for
+ * cobalt_allreduce_peer(). */
+int cobalt_peer_sum(const CobaltPeerSlots* slots, size_t n, void* out, int out_fp32, void* status, void* stream);
 
 /* cobalt_gemv() for callers that must not allocate device memory.
  *

@@ -722,6 +722,86 @@ def test_staging_refuses_shapes_it_cannot_hold():
     assert fused.staged(_lib.IN_ADDNORM, h, None, 0, w=h[0], eps=1e-5) is None
 
 
+class _LoopbackRanks:
+    """`world` peer buffers on ONE GPU laid out like tp.PeerReducer's symmetric buffers, so that the pushing epilogue, the
+    flags and the summing staging can be exercised rank after rank in one stream (no kernel ever waits for a kernel
+    that has not been launched: every push precedes the sums)."""
+
+    def __init__(self, world, max_floats):
+        import ctypes
+        from cobalt_b200 import _lib
+        self.world = world
+        self.stride = (max_floats * 4 + 255) // 256 * 256
+        self.flags_off = (1 + 2 * world) * self.stride
+        self.bufs = [torch.zeros((self.flags_off + 256) // 4, dtype=torch.float32, device="cuda") for _ in range(world)]
+        self._ptrs = (ctypes.c_uint64 * world)(*[b.data_ptr() for b in self.bufs])
+        self.ranks = []
+        for r in range(world):
+            ns = type("Rank", (), {})()
+            ns.slots = _lib.CobaltPeerSlots(ctypes.cast(self._ptrs, ctypes.c_void_p), r, world, self.stride, self.flags_off)
+            self.ranks.append(ns)
+        self.status = torch.zeros(64, dtype=torch.int32, device="cuda")
+
+    def sum(self, rank, n, dtype=torch.bfloat16):
+        import ctypes
+        from cobalt_b200 import _lib
+        out = torch.empty(n, dtype=dtype, device="cuda")
+        rc = _lib.load().cobalt_peer_sum(ctypes.byref(self.ranks[rank].slots), n, out.data_ptr(), 1 if dtype == torch.float32 else 0,
+                                         self.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        return out
+
+
+@pytest.mark.parametrize("world,M", [(1, 1), (2, 1), (2, 4), (4, 8)])
+def test_pushed_partials_and_summing_staging(world, M):
+    """Row-parallel projection split over `world` column shards, every shard's GEMV pushing its fp32 partial into every
+    rank's slot; then (a) cobalt_peer_sum and (b) the next projection's staging that adds the partials, joins the
+    residual and normalises.  Against: fp32 partials added in rank order and rounded once, then the separate kernels.
+    Three rounds, so both slots and several epochs are used."""
+    from cobalt_b200 import _lib, tp
+    from cobalt_b200.linear import FusedProjections
+    K, N = 512, 1024 * world
+    raw = O.synth_raw(K, N, 0.5, 4, seed=900 + world)
+    keep, q, sc, zr = raw["keep"], raw["q"], raw["scale"], raw["zero"]
+    shards = []
+    for r in range(world):
+        k, qq, s_, z = tp.shard_raw("row", keep, q, sc, zr, r, world)
+        shards.append(to_module(k, qq, s_, z, 4))
+    pushers = [FusedProjections([m]) for m in shards]
+    nxt_raw = O.synth_raw(128, K, 0.5, 4, seed=77)
+    nxt = FusedProjections([to_module(nxt_raw["keep"], nxt_raw["q"], nxt_raw["scale"], nxt_raw["zero"], 4)])
+    ranks = _LoopbackRanks(world, M * K)
+    g = torch.Generator().manual_seed(world * 10 + M)
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).bfloat16().cuda()
+    for rnd in range(3):
+        x = torch.randn(M, N, generator=g).bfloat16().cuda()
+        h = torch.randn(M, K, generator=g).bfloat16().cuda()
+        parts = []
+        for r in range(world):
+            c0, c1 = tp.shard_bounds(N, r, world, 128)
+            xr = x[:, c0:c1].contiguous()
+            parts.append(shards[r](xr, out_fp32=True))
+            assert pushers[r].staged(_lib.IN_PLAIN, xr, None, 0, push=ranks.ranks[r]) == []
+        want32 = torch.zeros_like(parts[0])
+        for p_ in parts:
+            want32 = want32 + p_                                       # rank order, fp32
+        want = want32.bfloat16()
+        for r in range(world):
+            assert torch.equal(ranks.sum(r, M * K).view(M, K), want), (rnd, r)
+            assert torch.equal(ranks.sum(r, M * K, torch.float32).view(M, K), want32), (rnd, r)
+        h_ref, x_ref = _separate_addnorm(h, want, w, None, 0, 1e-5)
+        y_ref = nxt(x_ref)
+        for r in range(world):
+            h_out = torch.empty_like(h)
+            got = nxt.staged(_lib.IN_ADDNORM, h, None, 0, w=w, h_out=h_out, eps=1e-5, delta_slots=ranks.ranks[r])
+            assert got is not None
+            assert torch.equal(h_out, h_ref) and torch.equal(got[0], y_ref[0]), (rnd, r)
+    torch.cuda.synchronize()
+    assert int(ranks.status[0]) == 0
+    for m in shards:
+        assert m.device_status() == 0
+
+
 def test_zz_exemption_summary():
     """Collected after the other tests of this file: how often the rounding-boundary exemption was used."""
     total = sum(t for _, t in EXEMPT)

@@ -116,7 +116,10 @@ def test_peer_memory_allreduce_matches_nccl():
         assert same, f"rank {rank}: peer all-reduce differs from NCCL"
 
 
-def _decoder_worker(rank, world, port, out, family, head_bits):
+def _decoder_worker(rank, world, port, out, family, head_bits, push):
+    import faulthandler
+    import sys
+    faulthandler.dump_traceback_later(300, exit=True, file=sys.stderr)   # a stuck rank ends with its stack instead of hanging the run
     import torch.distributed as dist
     from cobalt_b200 import SparseQuantConfig, tp
     from cobalt_b200.decoder import build_random_decoder
@@ -140,6 +143,7 @@ def _decoder_worker(rank, world, port, out, family, head_bits):
         # the same seeds on every rank: identical models
         full, raws = build_random_decoder(cfg, qcfg, 64, dev, keep_raw=True, head_bits=head_bits)
         part = build_random_decoder(cfg, qcfg, 64, dev, tp_rank=rank, tp_world=world, reducer=red, head_bits=head_bits)
+        part.push_partials = push
         g = torch.Generator().manual_seed(12)
         prompt = torch.randint(0, 1000, (24,), generator=g)
         n_new = 12
@@ -170,14 +174,24 @@ def _decoder_worker(rank, world, port, out, family, head_bits):
                          head_rows=None if part.head is None else part.head.out_features)
         dist.barrier()
     finally:
+        # a captured graph that holds NCCL kernels (the gathered head) must go before the communicator does,
+        # or destroy_process_group() never returns
+        for name in ("part", "full"):
+            if name in locals():
+                locals()[name]._graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,family,head_bits", [(2, "llama", 0), (2, "gemma", 0), (2, "llama", 4), (2, "gemma", 4),
-                                                    (4, "llama", 4), (4, "gemma", 0)])
-def test_tensor_parallel_decoder_against_cpu_oracle(world, family, head_bits):
+@pytest.mark.parametrize("world,family,head_bits,push", [(2, "llama", 0, False), (2, "gemma", 0, True), (2, "llama", 4, True),
+                                                         (2, "gemma", 4, False), (4, "llama", 4, False), (4, "gemma", 0, True)])
+def test_tensor_parallel_decoder_against_cpu_oracle(world, family, head_bits, push):
     """The decoder split over 2 and 4 GPUs (local heads, row-parallel o/down summed over peer memory inside the
-    captured decode step; with ``head_bits`` the compressed head split over the vocabulary and its logits gathered)
+    captured decode step - by the copy-based peer kernel or, with ``push``, by partial sums the GEMVs push into every
+    rank's slot and the next projection's staging adds up; with ``head_bits`` the compressed head split over the
+    vocabulary and its logits gathered)
     against the UNSHARDED oracle on the CPU, teacher-forced: logits as close to the oracle as the oracle's own
     control run (x2), arg-max equal at every step whose oracle margin is outside the noise band.  Beside it, the
     distance to the same model on one GPU (sum order only)."""
@@ -185,7 +199,7 @@ def test_tensor_parallel_decoder_against_cpu_oracle(world, family, head_bits):
     _need(world)
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_decoder_worker, args=(world, _free_port(), out, family, head_bits), nprocs=world, join=True)
+    mp.spawn(_decoder_worker, args=(world, _free_port(), out, family, head_bits, push), nprocs=world, join=True)
     for rank in range(world):
         r = out[rank]
         print(f"rank {rank}/{world}: max|dlogit| vs oracle {r['noise']:.4f} (control {r['ctl_noise']:.4f}), vs one GPU "
