@@ -490,6 +490,7 @@ def extra_legs(dev, steps=5):
             times = []
             for _ in range(steps):
                 flush.fill_(1)
+                torch.cuda._sleep(400_000)                     # device-side spacer: the host enqueues the launch meanwhile
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 mod(x)
@@ -637,7 +638,8 @@ def run_prefill(args):
                 times = []
                 for _ in range(args.steps if args.steps < 50 else 10):
                     flush.fill_(1)
-                    torch.cuda.nvtx.range_push("cobalt_timed")
+                    torch.cuda._sleep(400_000)                 # ~0.2 ms of device time: the host enqueues the launch meanwhile,
+                    torch.cuda.nvtx.range_push("cobalt_timed")  # so the events bracket the kernel, not the host's launch path
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
                     mod(x)

@@ -176,18 +176,24 @@ struct GemmCfg {
 
 int gemm_config(const CobaltMat* w, int M, int num_sms, GemmCfg* c) {
     const int row_tiles = (w->n_row_blocks + GEMM_RB - 1) / GEMM_RB;
-    // fewer tokens per CTA when the problem is too small to occupy the SMs with 512-token tiles
-    int tpc = GEMM_TOKENS;
-    while (tpc > 64 && (long)row_tiles * ((M + tpc - 1) / tpc) * 4 < (long)num_sms * 3) tpc /= 2;
+    // One token tile whenever the tokens fit one (M <= 512): a CTA decodes its 128-row slab of the weights whatever the
+    // number of tokens, so cutting the tokens would decode every weight tile several times.  SMs that such a grid
+    // leaves idle are filled by splitting the columns instead (split-K over whole column tiles, fp32 partial sums).
+    int tpc = 64;
+    while (tpc < GEMM_TOKENS && tpc < M) tpc *= 2;
     c->tok_per_cta = tpc;
     const int tok_tiles = (M + tpc - 1) / tpc;
     const long units = (long)row_tiles * tok_tiles;
     long splits = 1;
     if (g_tune_gemm_stages > 0) splits = g_tune_gemm_stages;                 // tuning key 2 overrides the split-K factor
-    else if (units * 2 < (long)num_sms) splits = num_sms / units;
-    if (splits > 8) splits = 8;
+    else if (units < (long)num_sms) splits = num_sms / units;
+    if (splits > 16) splits = 16;
     if (splits > w->n_col_tiles) splits = w->n_col_tiles;
     if (splits < 1) splits = 1;
+    {   // every split gets at least one column tile: the kernel hands out ceil(CT / splits) tiles per split
+        const long per = (w->n_col_tiles + splits - 1) / splits;
+        splits = (w->n_col_tiles + per - 1) / per;
+    }
     c->splits = (int)splits;
     c->grid = dim3((unsigned)row_tiles, (unsigned)tok_tiles, (unsigned)splits);
     c->counters_off = SCRATCH_STATUS_BYTES;

@@ -218,8 +218,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
         };
         bool healthy = true;
         int q = 0;                                        // stage counter of this CTA (both groups count every stage)
+        // Weight bytes are read by per-thread loads whose addresses depend on each other (tile offset -> masks -> code
+        // windows).  One thread per row block asks the L2 for whole tiles two column tiles ahead, so that those loads
+        // find their lines in the cache instead of paying a DRAM round trip each.
+        auto prefetch_tile = [&](int ct) {
+            if (have_rb && rr == 0 && group == 0 && ct < ct_end) {
+                const uint32_t* to = W.tile_off + (size_t)(rb0 + rbl) * W.CT + ct;
+                const uint32_t o0 = __ldg(to), o1 = __ldg(to + 1);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(W.tiles + (size_t)o0 * 16), "r"((o1 - o0) * 16u) : "memory");
+            }
+        };
+        prefetch_tile(ct_begin);
+        prefetch_tile(ct_begin + 1);
         for (int ct = ct_begin; ct < ct_end && healthy; ++ct) {
             const int w = tile_width(W, ct);
+            prefetch_tile(ct + 2);
             // this row's segments, and where its codes start inside the tile
             uint4 mk[TILE_GROUPS];
             uint32_t szv[TILE_GROUPS];
@@ -356,12 +369,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const Gem
                 __threadfence();
                 const float* base = P.partials + (size_t)tile_id * P.splits * ((size_t)GEMM_TOKENS * GEMM_ROWS);
                 if (row < W.K) {
-                    for (int tk = 0; tk < ntok_acc; ++tk) {
-                        float sum = 0.0f;
-                        for (int k = 0; k < P.splits; ++k)
-                            sum += __ldcg(base + (size_t)k * ((size_t)GEMM_TOKENS * GEMM_ROWS) + (size_t)(acc_id * GEMM_NT + tk) * GEMM_ROWS + r);
-                        if (P.y32) P.y32[(size_t)(tok_base + tk) * P.ldy + row] = sum;
-                        else P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(sum, P.bias, row);
+                    // eight tokens x four splits of loads in flight per thread: one thread per row walks up to 256 tokens,
+                    // and a token at a time would be one L2 latency per token (the whole cost of a small-M launch)
+                    constexpr int TU = 8, KU = 4;
+                    const size_t split_stride = (size_t)GEMM_TOKENS * GEMM_ROWS;
+                    for (int tk0 = 0; tk0 < ntok_acc; tk0 += TU) {
+                        float sum[TU];
+#pragma unroll
+                        for (int j = 0; j < TU; ++j) sum[j] = 0.0f;
+                        for (int k0 = 0; k0 < P.splits; k0 += KU) {
+                            float v[KU][TU];
+#pragma unroll
+                            for (int kk = 0; kk < KU; ++kk)
+#pragma unroll
+                                for (int j = 0; j < TU; ++j) {
+                                    const int tk = tk0 + j < ntok_acc ? tk0 + j : ntok_acc - 1;
+                                    v[kk][j] = k0 + kk < P.splits
+                                        ? __ldcg(base + (size_t)(k0 + kk) * split_stride + (size_t)(acc_id * GEMM_NT + tk) * GEMM_ROWS + r) : 0.0f;
+                                }
+#pragma unroll
+                            for (int kk = 0; kk < KU; ++kk)             // splits in order: the sum does not depend on the grid
+#pragma unroll
+                                for (int j = 0; j < TU; ++j)
+                                    if (k0 + kk < P.splits) sum[j] += v[kk][j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < TU; ++j) {
+                            const int tk = tk0 + j;
+                            if (tk < ntok_acc) {
+                                if (P.y32) P.y32[(size_t)(tok_base + tk) * P.ldy + row] = sum[j];
+                                else P.y[(size_t)(tok_base + tk) * P.ldy + row] = finish_output(sum[j], P.bias, row);
+                            }
+                        }
                     }
                 }
                 if (threadIdx.x == 0) P.counters[tile_id] = 0u;
