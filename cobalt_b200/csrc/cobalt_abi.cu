@@ -143,13 +143,16 @@ int gemv_config(const GemvGeom& g, int N, int M, int num_sms, GemvCfg* c) {
 
 template <int BITS, int MT, bool XS>
 int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
-    static bool configured[MAX_DEVICES];
+    // two kernels per shape class: the common launch, and the one that also carries the staged-input and push modes
+    const bool special = P.mode != 0;
+    void (*kernel)(const GemvParams) = special ? gemv_mma_special_kernel<BITS, MT, XS> : gemv_mma_kernel<BITS, MT, XS>;
+    static bool configured[MAX_DEVICES][2];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev]) {
-        if (cudaFuncSetAttribute(gemv_mma_kernel<BITS, MT, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
+    if (!configured[dev][special ? 1 : 0]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
             return COBALT_ELAUNCH;
-        configured[dev] = true;
+        configured[dev][special ? 1 : 0] = true;
     }
     // programmatic stream serialisation: the prologue of this kernel (barrier set-up, table fill, first weight
     // tiles) may overlap the tail of the previous kernel in the stream; the kernel itself waits before it
@@ -164,7 +167,7 @@ int launch_gemv(const GemvParams& P, const GemvCfg& c, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<BITS, MT, XS>, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
+    return cudaLaunchKernelEx(&cfg, kernel, P) == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
 // ----------------------------------------------------------------------------- GEMM configuration
@@ -247,6 +250,7 @@ int launch_gemm(const GemmParams& P, const CUtensorMap& xmap, const GemmCfg& c, 
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
+constexpr long STAGED_NORM_MAX_VALUES = 8192, STAGED_GLU_MAX_VALUES = 32768;     // M * in_features a staged input may compute
 constexpr size_t SCRATCH_PUSH_DONE_OFF = 128;            // CTA arrival counter of pushing launches, inside the status block
 
 int check_slots(const CobaltPeerSlots* s, size_t floats) {
@@ -309,8 +313,11 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
     GemvCfg c;
     rc = gemv_config(g, w[0]->N, M, sms, &c);
     if (rc) return rc;
+    // Staged inputs pay one L2 round trip per 512 chunks of 8 values in every CTA: worth it for the one or two tokens of a
+    // decode step, not for more (8 tokens of 5376 values measured slower than the norm kernel followed by the GEMV).
     if (in && in->kind != COBALT_IN_PLAIN &&
-        (!c.xs || w[0]->col_scale || (in->kind == COBALT_IN_ADDNORM && w[0]->N % 256 != 0))) return COBALT_EUNSUPPORTED;
+        (!c.xs || w[0]->col_scale || (in->kind == COBALT_IN_ADDNORM && (w[0]->N % 256 != 0 || (long)M * w[0]->N > STAGED_NORM_MAX_VALUES)) ||
+         (in->kind == COBALT_IN_GLU && (long)M * w[0]->N > STAGED_GLU_MAX_VALUES))) return COBALT_EUNSUPPORTED;
     if (!scratch || ((uintptr_t)scratch & 255) || scratch_bytes < c.total) return COBALT_ESCRATCH;
     cudaStream_t st = (cudaStream_t)stream;
     if (clear_counters) {

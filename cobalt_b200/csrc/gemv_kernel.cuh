@@ -399,8 +399,11 @@ struct GemvUnit {
     uint4 x[MT][2];                            // activations: 16 columns x token g (+8)
 };
 
-template <int BITS, int MT, bool XS>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const __grid_constant__ GemvParams P) {
+// SPECIAL = the launch computes its activations while staging them, adds pushed partial sums, or pushes its own
+// (GemvParams::mode != 0).  The common launch is a kernel of its own without any of that code, so that the
+// less common modes cost it neither a start-up test nor a register.
+template <int BITS, int MT, bool XS, bool SPECIAL>
+__device__ __forceinline__ void gemv_mma_body(const GemvParams& P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -507,7 +510,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const __grid_
     // pushing launches: the epoch of this all-reduce (the last CTA to finish advances the counter, after every CTA read it)
     // (kept in shared memory, word 2 of the counter block: it is needed only when rows are stored)
     volatile uint32_t* push_epoch_s = red_cnt + 2;
-    if ((P.mode & GEMV_MODE_PUSH) && threadIdx.x == 0) *push_epoch_s = *reinterpret_cast<volatile uint32_t*>(P.push_flags + PEER_EPOCH_INDEX) + 1u;
+    if (SPECIAL && (P.mode & GEMV_MODE_PUSH) && threadIdx.x == 0) *push_epoch_s = *reinterpret_cast<volatile uint32_t*>(P.push_flags + PEER_EPOCH_INDEX) + 1u;
     // x -> shared memory, rows of N bf16, 16-byte chunk c of token m stored at chunk c ^ swizzle(group, m).  The
     // first chunks of every thread are requested before the table is built, so that their latency hides behind it.
     constexpr int XPRE = 2;
@@ -525,7 +528,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const __grid_
         const int pc = c ^ (((c >> 4) & 3) | ((m & 1) << 2));
         *reinterpret_cast<uint4*>(xs + ((size_t)m * chunks_per_row + pc) * 16) = v;
     };
-    if (!XS || (P.mode & GEMV_MODE_IN_MASK) == 0) {
+    if (!SPECIAL || !XS || (P.mode & GEMV_MODE_IN_MASK) == 0) {
         uint4 xpre[XPRE];
 #pragma unroll
         for (int q = 0; q < XPRE; ++q) {
@@ -566,7 +569,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const __grid_
         mt.y = MAT_FIELD(mi, y); mt.y32 = MAT_FIELD(mi, y32); mt.bias = MAT_FIELD(mi, bias); mt.ldy = MAT_FIELD(mi, ldy);
         mt.K = MAT_FIELD(mi, K); mt.rb_start = MAT_FIELD(mi, rb_start);
         const int row0 = (rb - mt.rb_start) * TILE_ROWS + g, row1 = row0 + 8;
-        if (P.mode & GEMV_MODE_PUSH) {                                 // the partial goes straight into every rank's slot
+        if (SPECIAL && (P.mode & GEMV_MODE_PUSH)) {                    // the partial goes straight into every rank's slot
             gemv_push_rows<MT>(P, *push_epoch_s, (int)mt.ldy, mt.K, row0, acc);
             return;
         }
@@ -885,7 +888,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const __grid_
             store_rows(tag);
         }
     }
-    if (P.mode & GEMV_MODE_PUSH) gemv_push_publish(P, *push_epoch_s);
+    if (SPECIAL && (P.mode & GEMV_MODE_PUSH)) gemv_push_publish(P, *push_epoch_s);
+}
+
+template <int BITS, int MT, bool XS>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvParams P) {
+    gemv_mma_body<BITS, MT, XS, false>(P);
+}
+// parameters in place (their address is handed to the out-of-line staging and push functions)
+template <int BITS, int MT, bool XS>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_special_kernel(const __grid_constant__ GemvParams P) {
+    gemv_mma_body<BITS, MT, XS, true>(P);
 }
 
 }  // namespace cb

@@ -105,8 +105,9 @@ size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, in
  *                      (src/cobaltkernel/csrc/megakernel.cu:270-288, 1904-1915).
  * a, b, h_out are [M, in_features] bf16 with row stride ld (elements), 16-byte aligned; results are bit-identical
  * to the separate entry points followed by cobalt_gemv_fused().  Only launches that stage their activations can
- * take this path (M <= 8 and M * in_features * 2 bytes beside the weight ring; COBALT_IN_ADDNORM also needs
- * in_features % 256 == 0): otherwise COBALT_EUNSUPPORTED is returned and nothing is launched.  COBALT_IN_PLAIN
+ * take this path (M <= 8 and M * in_features * 2 bytes beside the weight ring), and only while every CTA repeating the
+ * step is cheaper than a kernel of its own: M * in_features <= 32768 for COBALT_IN_GLU, <= 8192 and in_features % 256 == 0
+ * for COBALT_IN_ADDNORM.  Otherwise COBALT_EUNSUPPORTED is returned and nothing is launched.  COBALT_IN_PLAIN
  * (a = x) takes every shape.
  *
  * Tensor parallelism, the all-reduce of a row-parallel projection folded into the two kernels around it (the

@@ -649,7 +649,7 @@ def _separate_addnorm(h, delta, w, w_branch, flavor, eps):
     return (h if delta is None else h_out), y
 
 
-@pytest.mark.parametrize("N,M", [(4096, 1), (4096, 3), (4096, 8), (5376, 1), (5376, 4), (512, 2)])
+@pytest.mark.parametrize("N,M", [(4096, 1), (4096, 2), (1024, 8), (5376, 1), (2048, 3), (512, 2)])
 @pytest.mark.parametrize("mode", ["llama", "llama_first", "gemma", "gemma_branch"])
 def test_norm_folded_into_staging_equals_separate_kernels(N, M, mode):
     """Residual add + RMSNorm computed by the GEMV while it stages its activations (cobalt_gemv_fused_staged) against
@@ -719,6 +719,10 @@ def test_staging_refuses_shapes_it_cannot_hold():
     raw = O.synth_raw(64, 1152, 0.5, 4, seed=4)                   # 1152 = 4.5 * 256: rows the norm's sum order does not cover
     fused = FusedProjections([to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
     h = torch.zeros(1, 1152, dtype=torch.bfloat16, device="cuda")
+    assert fused.staged(_lib.IN_ADDNORM, h, None, 0, w=h[0], eps=1e-5) is None
+    raw = O.synth_raw(64, 4096, 0.5, 4, seed=5)                   # eight tokens: every CTA repeating the norm costs more than its kernel
+    fused = FusedProjections([to_module(raw["keep"], raw["q"], raw["scale"], raw["zero"], 4)])
+    h = torch.zeros(8, 4096, dtype=torch.bfloat16, device="cuda")
     assert fused.staged(_lib.IN_ADDNORM, h, None, 0, w=h[0], eps=1e-5) is None
 
 
