@@ -29,6 +29,11 @@ multi-GPU run goes through the same tensor-parallel step, host copies included.
 The line also carries two short extra legs (single GPU, skipped with --no-extra): `prefill` - the tcgen05 GEMM on
 two 7B shapes at M = 128 and 2048 against the measured bf16 peak - and `model` - a reduced-depth (4-layer)
 Mistral-7B-shaped greedy decode with ms per layer and the 32-layer tokens/s extrapolated from it (labelled).
+
+Other workloads: `--workload prefill` (tcgen05 GEMM sweep over the 7B shapes, M in --prefill-m, 3-bit/70 % and
+2-bit/50 %) and `--workload model` (full greedy decode of a random-init model: `--model mistral7b|gemma27b`,
+`--context`, `--new-tokens`, `--batch` sequences decoded together, `--head-bits` for a compressed and, with several
+GPUs, vocabulary-split head, `--prefill-tokens` for the timed prompt; tensor-parallel under torch.distributed.run).
 """
 from __future__ import annotations
 
