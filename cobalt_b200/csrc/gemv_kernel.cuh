@@ -20,8 +20,10 @@
 //
 // Activations: when M * N * 2 bytes fit beside the ring (always for one token), the CTA copies x into shared
 // memory once, 16-byte chunks XOR-swizzled so that the 32 lanes of a fragment load hit 8 distinct bank groups
-// per quarter warp; otherwise every lane reads its fragment from global memory (read-only path), also one
-// unit ahead.
+// per quarter warp; otherwise every lane reads its fragment from a fragment-ordered copy of x in global memory
+// (x_permute_kernel: 512 contiguous bytes per warp and fragment), also one unit ahead.  A second instantiation
+// of the kernel (gemv_mma_special_kernel) can compute the staged rows itself - residual add + RMSNorm, the gated
+// activation, the sum of tensor-parallel partial sums - and can push its own fp32 sums into peer buffers.
 //
 // Row blocks covered by several warps.  Every warp holds at most two partial sums: of the row block its range
 // starts in and of the one it ends in.  They are combined deterministically, in warp order:
