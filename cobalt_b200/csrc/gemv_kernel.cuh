@@ -2,8 +2,9 @@
 //
 // Persistent kernel, one CTA per SM.  The matrix is a sequence of tiles (row-block-major); a tile is four
 // "words" of 32 columns x 4 groups x 16 rows.  The words of the launch are cut into one contiguous range
-// per warp, balanced to +-1 word over all warps of the grid, so every SM gets the same share whatever the
-// matrix shape and no warp waits for a neighbour that drew a whole extra tile.  Each warp pulls the tiles its
+// per warp: either every CTA takes whole row blocks (no partial sums cross CTAs) or the words are balanced to
+// +-1 over all warps of the grid; the host picks the cheaper one per launch (cost model in words per warp,
+// gemv_config() in cobalt_abi.cu).  Each warp pulls the tiles its
 // range touches with 1-D bulk async copies into a private shared-memory ring (mbarrier completion), locates
 // every segment's survivor codes with a popcount prefix sum over the warp, expands them to dense bf16 weights
 // in registers (decode_core.cuh) and contracts them against the activations with mma.sync m16n8k16
