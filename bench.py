@@ -13,9 +13,11 @@ the 126 MB L2).
              activations in/out) with all inputs resident in HBM, timed with CUDA events
              around K steps replayed from a CUDA graph.  q|k|v and gate|up read the same
              activations and go out as one fused launch each (4 launches per step).
-  e2e        the same metric through cobalt_linear_host_async(): pinned host activations
-             copied in and the result copied back by every call; the seven calls of a step
-             alternate between two streams and the caller waits for both once per step.
+  e2e        the same metric through the library's host-buffer entry points: pinned host
+             activations copied in and the results copied back by every call
+             (cobalt_gemv_fused_host_async for q|k|v and gate|up, cobalt_linear_host_async for o and
+             down); the four calls of a step alternate between two streams and the caller waits
+             for both once per step.
   roofline   the GEMV kernel against the measured HBM copy bandwidth.
   cpu_baseline  the reference path (dense bf16 weight, torch.matmul) on the host cores.
 
@@ -383,15 +385,41 @@ def run_ours(args):
 
     dx = {n: torch.empty_like(xs[n]) for n in xs}             # device staging of the tensor-parallel end-to-end step
 
+    # single GPU: the calls of the device-timed step (q|k|v and gate|up as one fused call each, o, down), each fed from
+    # pinned host activations and read back to pinned host outputs by the library's host entry points
+    fused_scr, fused_args = {}, {}
+    for g in fuse_groups:
+        descs = (ctypes.POINTER(_lib.CobaltMat) * len(g))(*[ctypes.pointer(mods0[n]._descriptor()) for n in g])
+        need = lib.cobalt_gemv_fused_scratch_bytes(len(g), descs, M)
+        fused_scr[g] = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+
     def e2e_step(blk, fused):
         if world == 1:
-            for i, (name, _, _) in enumerate(SHAPES_7B):
-                m = blk[name]
-                sp = (scr[name].data_ptr() + 255) // 256 * 256
-                rc = lib.cobalt_linear_host_async(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
-                                                  xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256,
-                                                  e2e_streams[i & 1].cuda_stream)
-                _lib.check("cobalt_linear_host_async", rc)
+            done, k = set(), 0
+            for name in names:
+                if name in done:
+                    continue
+                st = e2e_streams[k & 1].cuda_stream
+                k += 1
+                if name in fused_of:
+                    g = fused_of[name]
+                    key = (id(blk), g)
+                    if key not in fused_args:                # descriptor and pointer arrays of a call, built once per block copy
+                        fused_args[key] = ((ctypes.POINTER(_lib.CobaltMat) * len(g))(*[ctypes.pointer(blk[n]._descriptor()) for n in g]),
+                                           (ctypes.c_void_p * len(g))(*[hy[n].data_ptr() for n in g]),
+                                           (ctypes.c_void_p * len(g))(*[ys[n].data_ptr() for n in g]))
+                    descs, yh, yd = fused_args[key]
+                    sp = (fused_scr[g].data_ptr() + 255) // 256 * 256
+                    rc = lib.cobalt_gemv_fused_host_async(len(g), descs, hx[name].data_ptr(), yh, M, xs[name].data_ptr(), yd, sp,
+                                                          fused_scr[g].numel() - 256, st)
+                    _lib.check("cobalt_gemv_fused_host_async", rc)
+                    done.update(g)
+                else:
+                    m = blk[name]
+                    sp = (scr[name].data_ptr() + 255) // 256 * 256
+                    rc = lib.cobalt_linear_host_async(ctypes.byref(m._descriptor()), hx[name].data_ptr(), hy[name].data_ptr(), None, M,
+                                                      xs[name].data_ptr(), ys[name].data_ptr(), sp, scr[name].numel() - 256, st)
+                    _lib.check("cobalt_linear_host_async", rc)
             stream.synchronize()                              # the caller reads the results: one wait per block
             side.synchronize()
             return
@@ -454,9 +482,9 @@ def run_ours(args):
                    "bytes_per_step": int(wbytes + abytes), "peak": peak_kind},
         "clocks": clocks,
         "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
-                "path": "cobalt_linear_host_async per projection, two streams, one wait per step" if world == 1 else
+                "path": "cobalt_gemv_fused_host_async (q|k|v, gate|up) and cobalt_linear_host_async (o, down), two streams, one wait per step" if world == 1 else
                         "tensor-parallel step through the module API: pinned host x in, fused launches, all-reduce of o and down, pinned host y out",
-                "h2d_bytes_per_step": int(sum(M * v["N"] * 2 for v in info.values())),
+                "h2d_bytes_per_step": int(sum(M * info[n]["N"] * 2 for n in names if n not in fused_of or fused_of[n][0] == n)),
                 "d2h_bytes_per_step": int(sum(M * v["K"] * 2 for v in info.values()))},
         "gpu_launches": int(args.steps * launches_per_step),
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",

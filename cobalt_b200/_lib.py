@@ -70,6 +70,8 @@ EXPORTS = {
     "cobalt_gemv_fused_scratch_bytes": (c_size_t, [c_int, c_void_p, c_int]),
     "cobalt_gemv_fused_staged": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                          c_void_p, c_size_t, c_void_p]),
+    "cobalt_gemv_fused_host_async": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
+                                             c_void_p]),
     "cobalt_peer_sum": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p]),
     "cobalt_gemv_rowwalk": (c_int, [POINTER(CobaltMat), c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                     c_void_p]),

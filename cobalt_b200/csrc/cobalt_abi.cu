@@ -682,6 +682,26 @@ int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_hos
     return COBALT_OK;
 }
 
+int cobalt_gemv_fused_host_async(int n_mats, const CobaltMat* const* w, const void* x_host, void* const* y_host, int M,
+                                 void* dev_x, void* const* dev_y, void* scratch, size_t scratch_bytes, void* stream) {
+    if (n_mats < 1 || n_mats > GEMV_MAX_MATS || !w || !x_host || !y_host || !dev_x || !dev_y) return COBALT_EINVAL;
+    if (M <= 0 || M > MAX_GEMV_M) return COBALT_EINVAL;
+    GemvOut o[GEMV_MAX_MATS];
+    for (int i = 0; i < n_mats; ++i) {
+        int rc = check_mat(w[i]);
+        if (rc) return rc;
+        if (!y_host[i] || !dev_y[i]) return COBALT_EINVAL;
+        o[i].y = dev_y[i]; o[i].ldy = w[i]->K; o[i].bias = nullptr;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(dev_x, x_host, (size_t)M * w[0]->N * 2, cudaMemcpyHostToDevice, st) != cudaSuccess) return COBALT_ELAUNCH;
+    int rc = gemv_launch(n_mats, w, o, dev_x, w[0]->N, M, false, scratch, scratch_bytes, false, stream);
+    if (rc) return rc;
+    for (int i = 0; i < n_mats; ++i)
+        if (cudaMemcpyAsync(y_host[i], dev_y[i], (size_t)M * w[i]->K * 2, cudaMemcpyDeviceToHost, st) != cudaSuccess) return COBALT_ELAUNCH;
+    return COBALT_OK;
+}
+
 int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M, void* dev_x,
                        void* dev_y, void* scratch, size_t scratch_bytes, void* stream) {
     int rc = cobalt_linear_host_async(w, x_host, y_host, bias, M, dev_x, dev_y, scratch, scratch_bytes, stream);

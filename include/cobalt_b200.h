@@ -229,6 +229,14 @@ int cobalt_linear_host(const CobaltMat* w, const void* x_host, void* y_host, con
  * wait once. */
 int cobalt_linear_host_async(const CobaltMat* w, const void* x_host, void* y_host, const void* bias, int M,
                              void* dev_x, void* dev_y, void* scratch, size_t scratch_bytes, void* stream);
+/* cobalt_gemv_fused() for activations in host memory: ONE copy of x[M, in_features] host->device, one launch for up to
+ * four matrices that read it (q|k|v, gate|up), one copy of every y[i] device->host; stream-ordered, no
+ * synchronisation (buffers pinned and valid until the caller has synchronised).  dev_y[i] holds M * K_i bf16,
+ * scratch at least cobalt_gemv_fused_scratch_bytes().  M <= 16.  Same results as cobalt_linear_host_async() per
+ * matrix; it saves the repeated copy of x and the small launches (the reference packs q|k|v and gate|up as one
+ * matrix for the same reason: docs/FORMAT.md:126-151). */
+int cobalt_gemv_fused_host_async(int n_mats, const CobaltMat* const* w, const void* x_host, void* const* y_host, int M,
+                                 void* dev_x, void* const* dev_y, void* scratch, size_t scratch_bytes, void* stream);
 
 /* Fused element-wise steps of a decoder block around the linears, with the dtype policy of the
  * reference's executable specs (src/cobaltkernel/ref_llama.py:82-97, 139-143; src/cobaltkernel/ref_gemma3.py:138-143,

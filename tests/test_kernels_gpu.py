@@ -453,6 +453,42 @@ def test_host_buffer_entry_points(M):
     assert torch.equal(hy2, want)
 
 
+@pytest.mark.parametrize("M", [1, 7])
+def test_fused_host_buffer_entry_point(M):
+    """cobalt_gemv_fused_host_async: one copy of the activations in, one launch for three matrices, three copies out,
+    equal bit for bit to the modules' forwards on device tensors."""
+    import ctypes
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    mods = []
+    for j, K in enumerate((384, 128, 64)):
+        W, norm = O.seeded_matrix(K, 1024, 31 + j)
+        keep, q, sc, zr = O.compress(W, norm, 4, 0.5, 0.5)
+        mods.append(CobaltSparseLinear(q.to(dev), sc.to(dev), zr.to(dev), keep.to(dev), None, None, {"nbits": 4}))
+    x = O.seeded_activation(M, 1024, 35)
+    want = [m(x.to(dev)).cpu() for m in mods]
+    hx = x.pin_memory()
+    hy = [torch.empty(M, m.out_features, dtype=torch.bfloat16).pin_memory() for m in mods]
+    dx = torch.empty(M, 1024, dtype=torch.bfloat16, device=dev)
+    dy = [torch.empty(M, m.out_features, dtype=torch.bfloat16, device=dev) for m in mods]
+    n = len(mods)
+    descs = (ctypes.POINTER(_lib.CobaltMat) * n)(*[ctypes.pointer(m._descriptor()) for m in mods])
+    need = lib.cobalt_gemv_fused_scratch_bytes(n, descs, M)
+    scr = torch.zeros(need + 256, dtype=torch.uint8, device=dev)
+    sp = (scr.data_ptr() + 255) // 256 * 256
+    yh = (ctypes.c_void_p * n)(*[t.data_ptr() for t in hy])
+    yd = (ctypes.c_void_p * n)(*[t.data_ptr() for t in dy])
+    rc = lib.cobalt_gemv_fused_host_async(n, descs, hx.data_ptr(), yh, M, dx.data_ptr(), yd, sp, need,
+                                          torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    for got, w in zip(hy, want):
+        assert torch.equal(got, w)
+    assert lib.cobalt_gemv_fused_host_async(n, descs, hx.data_ptr(), yh, 17, dx.data_ptr(), yd, sp, need,
+                                            torch.cuda.current_stream().cuda_stream) == -1      # more than 16 tokens: GEMV only
+
+
 @pytest.mark.gpu
 def test_one_scratch_serves_gemv_and_gemm_in_any_order():
     """A scratch buffer zeroed once is reused by GEMM-sized (split-K) and GEMV-sized host calls in turn: every kernel
