@@ -359,7 +359,9 @@ int gemv_launch(int n, const CobaltMat* const* w, const GemvOut* out, const void
         P.push_stride = push->slot_stride_bytes; P.push_flags_off = push->flags_off_bytes;
         P.push_flags = (uint32_t*)(push->peer_base[push->rank] + push->flags_off_bytes);
         P.push_done = (uint32_t*)((uint8_t*)scratch + SCRATCH_PUSH_DONE_OFF);
-        P.mat[0].ldy = w[0]->K;                              // rows of the slot are [M, K] fp32, dense
+        P.mat[0].y32 = (float*)push->peer_base[push->rank];  // the local staging area: [M, K] fp32, dense
+        P.mat[0].y = nullptr;
+        P.mat[0].ldy = w[0]->K;
     }
     if (in && in->kind != COBALT_IN_PLAIN) {
         if (in->b_slots) {

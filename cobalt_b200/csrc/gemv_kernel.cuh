@@ -105,8 +105,9 @@ struct GemvParams {
     // (in_world > 0; in_b unused): the staging waits for every rank's flag of the current epoch, then adds the rows
     int in_world;
     const uint8_t* in_slots; unsigned long long in_stride; const uint32_t* in_flags;
-    // Row-parallel output (raw fp32 sums) pushed into row `push_rank` of the epoch's slot in EVERY rank's peer buffer
-    // instead of y32 (push_world > 0; single-matrix launches); the last CTA to finish publishes the epoch to all ranks
+    // Row-parallel output (raw fp32 sums, written to mat[0].y32 = the local staging area) copied by the last CTA of the
+    // launch into row `push_rank` of the epoch's slot in EVERY rank's peer buffer and published to all ranks
+    // (push_world > 0; single-matrix launches)
     int push_world, push_rank;
     unsigned long long push_base[PEER_MAX_RANKS];
     unsigned long long push_stride, push_flags_off;
@@ -350,47 +351,40 @@ __device__ __noinline__ void gemv_stage_addnorm(const GemvParams& P, uint8_t* xs
     }
 }
 
-// rows of one finished row block of a pushing launch -> row `push_rank` of the epoch's slot in every rank's buffer
-template <int MT>
-__device__ __noinline__ void gemv_push_rows(const GemvParams& P, uint32_t epoch, int ldy, int K, int row0, const float (&acc)[MT][4]) {
-    const int t = threadIdx.x & 3, row1 = row0 + 8;
-    const unsigned long long row_off = (1ull + (unsigned long long)(epoch & 1u) * P.push_world + P.push_rank) * P.push_stride;
-#pragma unroll
-    for (int q = 0; q < PEER_MAX_RANKS; ++q) {
-        if (q >= P.push_world) break;
-        float* dst = reinterpret_cast<float*>(P.push_base[q] + row_off);
-#pragma unroll
-        for (int b = 0; b < MT; ++b) {
-            const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
-            if (row0 < K) {
-                if (tok0 < P.M) dst[(size_t)tok0 * ldy + row0] = acc[b][0];
-                if (tok1 < P.M) dst[(size_t)tok1 * ldy + row0] = acc[b][1];
-            }
-            if (row1 < K) {
-                if (tok0 < P.M) dst[(size_t)tok0 * ldy + row1] = acc[b][2];
-                if (tok1 < P.M) dst[(size_t)tok1 * ldy + row1] = acc[b][3];
-            }
-        }
-    }
-}
-
-// Every row this CTA pushed is on its way; the last CTA of the launch to get here tells every rank that this rank's
-// partial of the epoch is complete (the consumer - the next projection's staging or the summing kernel - waits for
-// these flags).  A launch that gave up (status word set) still publishes: its peers then read rows it did not finish,
-// which the status word reports, instead of running into their own time-out.
-__device__ __noinline__ void gemv_push_publish(const GemvParams& P, uint32_t epoch) {
+// Pushing launches write their fp32 sums into the local staging area like any fp32 launch.  The LAST CTA of the launch
+// to get here (arrival counter in scratch) copies the complete partial into row `push_rank` of the epoch's slot in
+// every rank's buffer (posted NVLink stores), advances the local epoch and tells every rank that this rank's partial is
+// complete - one system-scope fence per launch.  The consumer (the next projection's staging or the summing kernel)
+// waits for these flags.  A launch that gave up (status word set) still publishes: its peers then read rows it did
+// not finish, which the status word reports, instead of running into their own time-out.
+__device__ __noinline__ void gemv_push_publish(const GemvParams& P, uint32_t* s_last) {
     __syncthreads();                                                   // the CTA's stores are ordered before thread 0's fence
     if (threadIdx.x == 0) {
-        __threadfence_system();                                        // one system-scope fence per CTA, cumulative over the barrier
-        const uint32_t old = atom_add_acq_rel_gpu(P.push_done, 1u);
-        if (old == gridDim.x - 1u) {
-            *P.push_done = 0u;
-            P.push_flags[PEER_EPOCH_INDEX] = epoch;
+        __threadfence();
+        *s_last = atom_add_acq_rel_gpu(P.push_done, 1u) == gridDim.x - 1u ? 1u : 0u;
+    }
+    __syncthreads();
+    if (*reinterpret_cast<volatile uint32_t*>(s_last) == 0u) return;
+    __threadfence();
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(P.push_flags + PEER_EPOCH_INDEX) + 1u;
+    const unsigned long long row_off = (1ull + (unsigned long long)(epoch & 1u) * P.push_world + P.push_rank) * P.push_stride;
+    const float4* src = reinterpret_cast<const float4*>(P.mat[0].y32);
+    const uint32_t n4 = (uint32_t)((size_t)P.M * P.mat[0].K / 4);     // K is a multiple of 16
+    for (uint32_t i = threadIdx.x; i < n4; i += GEMV_THREADS) {
+        const float4 v = __ldcg(src + i);
 #pragma unroll
-            for (int q = 0; q < PEER_MAX_RANKS; ++q)
-                if (q < P.push_world)
-                    st_release_sys_u32(reinterpret_cast<uint32_t*>(P.push_base[q] + P.push_flags_off) + P.push_rank, epoch);
-        }
+        for (int q = 0; q < PEER_MAX_RANKS; ++q)
+            if (q < P.push_world) reinterpret_cast<float4*>(P.push_base[q] + row_off)[i] = v;
+    }
+    __syncthreads();                                                   // the release below covers every thread's stores
+    if (threadIdx.x == 0) {
+        *P.push_done = 0u;
+        P.push_flags[PEER_EPOCH_INDEX] = epoch;
+        __threadfence_system();
+#pragma unroll
+        for (int q = 0; q < PEER_MAX_RANKS; ++q)
+            if (q < P.push_world)
+                st_release_sys_u32(reinterpret_cast<uint32_t*>(P.push_base[q] + P.push_flags_off) + P.push_rank, epoch);
     }
 }
 
@@ -510,10 +504,6 @@ __device__ __forceinline__ void gemv_mma_body(const GemvParams& P) {
     // Programmatic dependent launch: everything above touched only the weights and this CTA's shared
     // memory.  From here on the activations and the scratch of the previous kernel in the stream are used.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // pushing launches: the epoch of this all-reduce (the last CTA to finish advances the counter, after every CTA read it)
-    // (kept in shared memory, word 2 of the counter block: it is needed only when rows are stored)
-    volatile uint32_t* push_epoch_s = red_cnt + 2;
-    if (SPECIAL && (P.mode & GEMV_MODE_PUSH) && threadIdx.x == 0) *push_epoch_s = *reinterpret_cast<volatile uint32_t*>(P.push_flags + PEER_EPOCH_INDEX) + 1u;
     // x -> shared memory, rows of N bf16, 16-byte chunk c of token m stored at chunk c ^ swizzle(group, m).  The
     // first chunks of every thread are requested before the table is built, so that their latency hides behind it.
     constexpr int XPRE = 2;
@@ -572,10 +562,6 @@ __device__ __forceinline__ void gemv_mma_body(const GemvParams& P) {
         mt.y = MAT_FIELD(mi, y); mt.y32 = MAT_FIELD(mi, y32); mt.bias = MAT_FIELD(mi, bias); mt.ldy = MAT_FIELD(mi, ldy);
         mt.K = MAT_FIELD(mi, K); mt.rb_start = MAT_FIELD(mi, rb_start);
         const int row0 = (rb - mt.rb_start) * TILE_ROWS + g, row1 = row0 + 8;
-        if (SPECIAL && (P.mode & GEMV_MODE_PUSH)) {                    // the partial goes straight into every rank's slot
-            gemv_push_rows<MT>(P, *push_epoch_s, (int)mt.ldy, mt.K, row0, acc);
-            return;
-        }
 #pragma unroll
         for (int b = 0; b < MT; ++b) {
             const int tok0 = 8 * b + 2 * t, tok1 = tok0 + 1;
@@ -891,7 +877,7 @@ __device__ __forceinline__ void gemv_mma_body(const GemvParams& P) {
             store_rows(tag);
         }
     }
-    if (SPECIAL && (P.mode & GEMV_MODE_PUSH)) gemv_push_publish(P, *push_epoch_s);
+    if (SPECIAL && (P.mode & GEMV_MODE_PUSH)) gemv_push_publish(P, red_cnt + 2);
 }
 
 template <int BITS, int MT, bool XS>

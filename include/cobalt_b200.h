@@ -112,10 +112,11 @@ size_t cobalt_gemv_fused_scratch_bytes(int n_mats, const CobaltMat* const* w, in
  *
  * Tensor parallelism, the all-reduce of a row-parallel projection folded into the two kernels around it (the
  * reference runs on one GPU; its column/row split is docs/FORMAT.md:126-151 and it has no counterpart of this exchange):
- *   `push` (output side)   the raw fp32 sums of THIS rank go, row block by row block as they finish, into row `rank`
- *                          of the current epoch's slot in EVERY rank's peer buffer (plain NVLink stores; layout as for
- *                          cobalt_allreduce_peer()); the last CTA to finish publishes the epoch in every rank's flag
- *                          block.  One matrix, out_fp32 = 1, y is not written (may hold NULLs).
+ *   `push` (output side)   the raw fp32 sums of THIS rank are written to the staging area of its own peer buffer; the
+ *                          last CTA of the launch to finish copies them into row `rank` of the current epoch's slot in
+ *                          EVERY rank's peer buffer (plain NVLink stores; layout as for cobalt_allreduce_peer()) and
+ *                          publishes the epoch in every rank's flag block.  One matrix, out_fp32 = 1, y is not
+ *                          written (may be NULL).
  *   `in->b_slots` (input side, COBALT_IN_ADDNORM)  delta = bf16( sum over ranks, in rank order, of the rows pushed
  *                          into this rank's buffer ): the staging waits (bounded, about a second, then status
  *                          COBALT_ETIMEOUT through cobalt_device_status) for every rank's flag, then adds the rows
