@@ -286,11 +286,11 @@ def run_ours(args):
         if timed_graph is not None:
             timed_graph.replay()                             # first replay uploads the graph; it is warm-up too
         stream.synchronize()
-        if dist is not None:
-            dist.barrier()
         sampler = ClockSampler(local)
         if rank == 0:
-            sampler.start()
+            sampler.start()                                  # before the barrier: starting the sampler takes rank 0 about a
+        if dist is not None:                                 # millisecond, which the other ranks would spend waiting in their
+            dist.barrier()                                   # first all-reduce inside the timed region
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.nvtx.range_push("cobalt_timed")          # lets a profiler restrict itself to the timed region
