@@ -94,6 +94,9 @@ EXPORTS = {
     "cobalt_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "cobalt_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_int,
                                    c_int, c_float, c_int, c_int64, c_void_p]),
+    "cobalt_attn_decode_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_int, c_int,
+                                         c_int, c_int, c_float, c_int, c_int64, c_void_p]),
+    "cobalt_attn_decode_fused_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "cobalt_allreduce_peer": (c_int, [c_void_p, c_int, c_int, c_size_t, c_size_t, c_size_t, c_void_p, c_int, c_void_p,
                                       c_void_p]),
     "cobalt_device_status": (c_int, [c_void_p, c_void_p, POINTER(c_uint32)]),

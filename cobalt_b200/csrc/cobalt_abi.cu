@@ -822,6 +822,53 @@ int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
     return cudaGetLastError() == cudaSuccess ? COBALT_OK : COBALT_ELAUNCH;
 }
 
+// one-kernel attention: [status 256 B][counters n_seq * n_kv * 2 u32][chunk statistics][partial contexts]
+size_t cobalt_attn_decode_fused_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int max_ctx, int n_seq) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || max_ctx <= 0 || n_seq <= 0) return 0;
+    const size_t chunks = ((size_t)max_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    return SCRATCH_STATUS_BYTES + round_up((size_t)n_seq * n_kv_heads * 8, 256) + round_up((size_t)n_seq * n_heads * chunks * 8, 256) +
+           round_up((size_t)n_seq * chunks * n_heads * head_dim * 4, 256);
+}
+
+int cobalt_attn_decode_fused(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions, void* scratch,
+                             size_t scratch_bytes, void* out, int n_heads, int n_kv_heads, int head_dim, int max_ctx,
+                             int window, float scale, int n_seq, int64_t cache_seq_stride, void* stream) {
+    if (!q || !k_cache || !v_cache || !positions || !scratch || !out) return COBALT_EINVAL;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads / n_kv_heads > ATTN_MAX_REP) return COBALT_EINVAL;
+    if (n_seq < 1 || n_seq > 65535 || cache_seq_stride < 0) return COBALT_EINVAL;
+    if (head_dim < 64 || head_dim > 256 || head_dim % 64 != 0 || max_ctx <= 0) return COBALT_EINVAL;
+    if (((uintptr_t)k_cache & 3) || ((uintptr_t)q & 3) || ((uintptr_t)scratch & 255)) return COBALT_EINVAL;
+    const int chunks = (max_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    if (chunks > ATTN_MAX_CHUNKS) return COBALT_ETOOBIG;
+    if (scratch_bytes < cobalt_attn_decode_fused_scratch_bytes(n_heads, n_kv_heads, head_dim, max_ctx, n_seq)) return COBALT_ESCRATCH;
+    int sms = 0;
+    int rc = device_info(&sms);
+    if (rc) return rc;
+    // every CTA must be resident at once (they wait for each other): otherwise the three-kernel entry point is the way
+    static int per_sm[MAX_DEVICES];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return COBALT_ELAUNCH;
+    if (per_sm[dev] == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_fused_kernel, ATTN_THREADS, 0) != cudaSuccess || n < 1) return COBALT_ELAUNCH;
+        per_sm[dev] = n;
+    }
+    if ((long)chunks * n_kv_heads * n_seq > (long)per_sm[dev] * sms) return COBALT_EUNSUPPORTED;
+    int rep = n_heads / n_kv_heads;
+    uint32_t* status = (uint32_t*)scratch;
+    uint32_t* counters = (uint32_t*)((uint8_t*)scratch + SCRATCH_STATUS_BYTES);
+    float* stat = (float*)((uint8_t*)counters + round_up((size_t)n_seq * n_kv_heads * 8, 256));
+    float* part = (float*)((uint8_t*)stat + round_up((size_t)n_seq * n_heads * chunks * 8, 256));
+    const uint16_t* qp = (const uint16_t*)q; const uint16_t* kp = (const uint16_t*)k_cache; const uint16_t* vp = (const uint16_t*)v_cache;
+    const long long* pp = (const long long*)positions;
+    uint16_t* op = (uint16_t*)out;
+    long long stride = (long long)cache_seq_stride;
+    void* args[] = {&qp, &kp, &vp, &pp, &stat, &part, &counters, &status, &op, &rep, &head_dim, &max_ctx, &window, &scale, &stride};
+    const dim3 grid((unsigned)chunks, (unsigned)n_kv_heads, (unsigned)n_seq);
+    return cudaLaunchCooperativeKernel((const void*)attn_decode_fused_kernel, grid, dim3(ATTN_THREADS), args, 0, (cudaStream_t)stream) == cudaSuccess
+               ? COBALT_OK : COBALT_ELAUNCH;
+}
+
 int cobalt_swiglu(const void* gate, const void* up, void* out, int64_t n, int act, void* stream) {
     if (!gate || !up || !out || n <= 0 || act < 0 || act > 1) return COBALT_EINVAL;
     int sms = 0;

@@ -56,6 +56,7 @@ enum : uint32_t {
     DEV_TIMEOUT_ACC = 4,       // GEMM: accumulator never completed
     DEV_TIMEOUT_STAGE = 5,     // GEMM: compressed tile group never arrived
     DEV_TIMEOUT_PEER = 6,      // peer all-reduce: a peer never published its partial
+    DEV_TIMEOUT_ATTN = 7,      // one-kernel decode attention: a chunk of the head group never published its statistics
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers

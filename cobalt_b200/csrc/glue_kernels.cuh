@@ -411,6 +411,186 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* part, co
     out[i] = float_to_bf16(a);
 }
 
+// The three steps above as ONE kernel (cooperative launch: every CTA of the grid is resident, so CTAs may wait for each
+// other).  grid (chunks, n_kv, n_seq).  A CTA computes the scores of its chunk and keeps them in shared memory, publishes
+// the chunk's max / sum of exp, arrives on a counter of its (sequence, KV head) and waits - with an iteration limit -
+// until all chunks in range have arrived; then it reads the statistics, forms the probabilities of its chunk and the
+// partial context, and arrives on a second counter: the last CTA to do so adds the partial contexts in chunk order and
+// rounds once.  Same arithmetic, in the same order, as the three kernels.  counters: [n_seq][n_kv][2] u32, zero before
+// the first launch; the last CTA returns both to zero.  status: set to DEV_TIMEOUT_ATTN when the wait gives up (the
+// outputs of that head group are then not written).
+__device__ __forceinline__ void attn_chunk_range(long long pos, int window, int nchunks, int& c0, int& c1) {
+    c1 = (int)(pos / ATTN_CHUNK) + 1;
+    if (c1 > nchunks) c1 = nchunks;
+    c0 = 0;
+    if (window > 0 && pos - window + 1 > 0) c0 = (int)((pos - window + 1) / ATTN_CHUNK);
+}
+
+__global__ void __launch_bounds__(ATTN_THREADS) attn_decode_fused_kernel(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache,
+                                                                         const long long* positions, float* chunk_stat, float* part,
+                                                                         uint32_t* counters, uint32_t* status, uint16_t* out, int rep, int D,
+                                                                         int max_ctx, int window, float scale, long long seq_stride) {
+    __shared__ float sc[ATTN_MAX_REP][ATTN_CHUNK];
+    __shared__ float gm[ATTN_MAX_REP], gz[ATTN_MAX_REP];
+    __shared__ float red[ATTN_WARPS][ATTN_MAX_REP][32];
+    __shared__ uint32_t flag_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kvh = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x, n_kv = gridDim.y;
+    const int n_heads = n_kv * rep;
+    q += (size_t)blockIdx.z * n_heads * D;
+    out += (size_t)blockIdx.z * n_heads * D;
+    k_cache += (size_t)blockIdx.z * seq_stride;
+    v_cache += (size_t)blockIdx.z * seq_stride;
+    chunk_stat += (size_t)blockIdx.z * n_heads * nchunks * 2;
+    part += (size_t)blockIdx.z * nchunks * n_heads * D;
+    uint32_t* cnt = counters + ((size_t)blockIdx.z * n_kv + kvh) * 2;
+    const long long pos = positions[blockIdx.z];
+    int c0, c1;
+    attn_chunk_range(pos, window, nchunks, c0, c1);
+    if (chunk < c0 || chunk >= c1) return;                              // nothing allowed in this chunk: it takes no part
+    const uint32_t expected = (uint32_t)(c1 - c0);
+    const int s0 = chunk * ATTN_CHUNK;
+    float* stat = chunk_stat + ((size_t)(kvh * rep) * nchunks + chunk) * 2;     // [head][chunk][max, sum]
+    const int per = D / 32;
+    {   // ---- scores of the chunk (as attn_scores_kernel), kept in shared memory
+        uint32_t kraw[8][4], qraw[ATTN_MAX_REP][4];
+        bool ok[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int s = s0 + warp + ATTN_WARPS * i;
+            ok[i] = attn_allowed(s, pos, window, max_ctx);
+            const uint32_t* kp = reinterpret_cast<const uint32_t*>(k_cache + ((size_t)kvh * max_ctx + (ok[i] ? s : 0)) * D + lane * per);
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) kraw[i][e2] = (ok[i] && e2 * 2 < per) ? __ldg(kp + e2) : 0u;
+        }
+#pragma unroll
+        for (int h = 0; h < ATTN_MAX_REP; ++h) {
+            const uint32_t* qp = reinterpret_cast<const uint32_t*>(q + ((size_t)kvh * rep + (h < rep ? h : 0)) * D + lane * per);
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) qraw[h][e2] = (h < rep && e2 * 2 < per) ? __ldg(qp + e2) : 0u;
+        }
+#pragma unroll
+        for (int h = 0; h < ATTN_MAX_REP; ++h) {
+            if (h >= rep) break;
+            float acc[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                acc[i] = 0.0f;
+#pragma unroll
+                for (int e2 = 0; e2 < 4; ++e2) {
+                    acc[i] = fmaf(__uint_as_float(qraw[h][e2] << 16), __uint_as_float(kraw[i][e2] << 16), acc[i]);
+                    acc[i] = fmaf(__uint_as_float(qraw[h][e2] & 0xFFFF0000u), __uint_as_float(kraw[i][e2] & 0xFFFF0000u), acc[i]);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xFFFFFFFFu, acc[i], o);
+            if (lane < 8) {
+                float mine = 0.0f;
+                bool w_ok = false;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (lane == i) { mine = acc[i]; w_ok = ok[i]; }
+                sc[h][warp + ATTN_WARPS * lane] = w_ok ? bf16_round(bf16_round(mine) * scale) : -INFINITY;
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < rep) {                                                   // warp h: max and sum of exp of head h over the chunk
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < ATTN_CHUNK; j += 32) m = fmaxf(m, sc[warp][lane + j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        float z = 0.0f;
+#pragma unroll
+        for (int j = 0; j < ATTN_CHUNK; j += 32) { const float a = sc[warp][lane + j]; z += a == -INFINITY ? 0.0f : expf(a - m); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xFFFFFFFFu, z, o);
+        if (lane == 0) { stat[(size_t)warp * nchunks * 2] = m; stat[(size_t)warp * nchunks * 2 + 1] = z; }
+    }
+    // ---- every chunk of this (sequence, KV head) has published its statistics?  bounded wait
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(&cnt[0], 1u);
+        uint32_t good = 0u;
+        for (uint32_t it = 0; it < (1u << 20); ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+            if (v >= expected) { good = 1u; break; }
+            if (it > 256) __nanosleep(64);
+        }
+        if (!good && status) atomicCAS(status, 0u, (uint32_t)DEV_TIMEOUT_ATTN);
+        flag_s = good;
+    }
+    __syncthreads();
+    if (flag_s == 0u) return;
+    __threadfence();
+    if (warp < rep) {                                                   // global max and sum of head `warp` from the chunk statistics
+        const float* st = chunk_stat + (size_t)(kvh * rep + warp) * nchunks * 2;
+        // same lanes, same order as attn_context_kernel (chunks outside the range count as empty there too)
+        float m = -INFINITY;
+        for (int c = lane; c < nchunks; c += 32)
+            if (c >= c0 && c < c1) m = fmaxf(m, __ldcg(st + 2 * c));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        float z = 0.0f;
+        for (int c = lane; c < nchunks; c += 32)
+            if (c >= c0 && c < c1) { const float mc = __ldcg(st + 2 * c); if (mc != -INFINITY) z += __ldcg(st + 2 * c + 1) * expf(mc - m); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xFFFFFFFFu, z, o);
+        if (lane == 0) { gm[warp] = m; gz[warp] = z; }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rep * ATTN_CHUNK; i += ATTN_THREADS) {        // probabilities of the chunk, rounded to bf16 (in place)
+        const int h = i / ATTN_CHUNK, j = i - h * ATTN_CHUNK;
+        const float a = sc[h][j];
+        sc[h][j] = a == -INFINITY ? 0.0f : bf16_round(expf(a - gm[h]) / gz[h]);
+    }
+    __syncthreads();
+    float* mine = part + ((size_t)chunk * n_heads + (size_t)kvh * rep) * D;
+    for (int d0 = 0; d0 < D; d0 += 32) {
+        float vv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int s = s0 + warp + ATTN_WARPS * i;
+            vv[i] = attn_allowed(s, pos, window, max_ctx) ? bf16_to_float(v_cache[((size_t)kvh * max_ctx + s) * D + d0 + lane]) : 0.0f;
+        }
+#pragma unroll
+        for (int h = 0; h < ATTN_MAX_REP; ++h) {
+            if (h >= rep) break;
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a = fmaf(sc[h][warp + ATTN_WARPS * i], vv[i], a);
+            red[warp][h][lane] = a;
+        }
+        __syncthreads();
+        if (warp < rep) {
+            float a = 0.0f;
+#pragma unroll
+            for (int w = 0; w < ATTN_WARPS; ++w) a += red[w][warp][lane];
+            mine[(size_t)warp * D + d0 + lane] = a;
+        }
+        __syncthreads();
+    }
+    // ---- the last chunk to finish adds the partial contexts in chunk order
+    if (threadIdx.x == 0) {
+        __threadfence();
+        flag_s = atomicAdd(&cnt[1], 1u) == expected - 1u ? 1u : 0u;
+    }
+    __syncthreads();
+    if (flag_s == 0u) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < rep * D; i += ATTN_THREADS) {
+        float a = 0.0f;
+        for (int c = c0; c < c1; ++c) a += __ldcg(part + ((size_t)c * n_heads + (size_t)kvh * rep) * D + i);
+        out[(size_t)kvh * rep * D + i] = float_to_bf16(a);
+    }
+    if (threadIdx.x == 0) { cnt[0] = 0u; cnt[1] = 0u; }
+}
+
 // ----------------------------------------------------------------------------- all-reduce over peer memory
 // Sum of the fp32 partial outputs of a row-parallel layer, one [n]-vector per GPU, added in rank order and rounded
 // to bf16 once.  Every rank runs this kernel (one CTA) on its own GPU.  It PUSHES: the partial goes from the local

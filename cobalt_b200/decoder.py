@@ -154,6 +154,12 @@ class CobaltDecoder:
         need = _lib.load().cobalt_attn_decode_scratch_bytes(self.nh, D, max_ctx) * self.B
         self.att_scratch = torch.empty(need, dtype=torch.uint8, device=device) if self.nh // self.nkv <= 8 and D % 64 == 0 and D <= 256 \
             and max_ctx <= 65536 else None
+        # One-kernel attention (cooperative launch; its scratch starts zeroed; only while its whole grid fits on the GPU).
+        # Off by default: bit-identical to the three kernels but slower inside the decode graph (4-layer 7B-shaped step
+        # 0.574 ms against 0.524 ms) - a cooperative launch does not overlap its neighbours.  Set the flag before the
+        # first decode step to use it.
+        self.att_fused = None
+        self.one_kernel_attention = False
         self.tok = torch.zeros(self.B, dtype=torch.long, device=device)   # next token of every sequence
         self.pos = torch.zeros(self.B, dtype=torch.long, device=device)   # its position
         self.qkv = [FusedProjections([linears[(i, "self_attn.q_proj")], linears[(i, "self_attn.k_proj")],
@@ -212,6 +218,20 @@ class CobaltDecoder:
         window = int(cfg.get("sliding_window") or 0) if self.types[layer] == "sliding_attention" else 0
         kc = self.k_cache[layer] if seq is None else self.k_cache[layer][seq]
         vc = self.v_cache[layer] if seq is None else self.v_cache[layer][seq]
+        if self.one_kernel_attention and self.att_scratch is not None:
+            if self.att_fused is None:
+                nf = self._lib.cobalt_attn_decode_fused_scratch_bytes(self.nh, self.nkv, cfg["head_dim"], self.max_ctx, self.B)
+                self.att_fused = torch.zeros(nf, dtype=torch.uint8, device=self.dev)
+            rc = self._lib.cobalt_attn_decode_fused(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), positions.data_ptr(),
+                                                    self.att_fused.data_ptr(), self.att_fused.numel(), ctx.data_ptr(),
+                                                    self.nh, self.nkv, cfg["head_dim"], self.max_ctx, window, self.scale,
+                                                    q.shape[0], self.seq_stride if seq is None else 0,
+                                                    torch.cuda.current_stream(self.dev).cuda_stream)
+            if rc == 0:
+                return ctx
+            if rc != _lib.EUNSUPPORTED:
+                _lib.check("cobalt_attn_decode_fused", rc)
+            self.one_kernel_attention = False                 # the grid does not fit on this GPU at once: three kernels from now on
         rc = self._lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                           positions.data_ptr(), self.att_scratch.data_ptr(), self.att_scratch.numel(), ctx.data_ptr(),
                                           self.nh, self.nkv, cfg["head_dim"], self.max_ctx, window, self.scale,

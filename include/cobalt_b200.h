@@ -275,6 +275,17 @@ size_t cobalt_attn_decode_scratch_bytes(int n_heads, int head_dim, int max_ctx);
 int cobalt_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions, void* scratch,
                        size_t scratch_bytes, void* out, int n_heads, int n_kv_heads, int head_dim, int max_ctx, int window,
                        float scale, int n_seq, int64_t cache_seq_stride, void* stream);
+/* cobalt_attn_decode() as ONE kernel instead of three (cooperative launch: the CTAs of a head group wait for each other's
+ * softmax statistics, with an iteration limit).  Same arguments and bit-identical results.  Differences: `scratch`
+ * (cobalt_attn_decode_fused_scratch_bytes(), 256-byte aligned) must be ZERO before its first use - it starts with a
+ * status word (cobalt_device_status(scratch, ...) reports COBALT_ETIMEOUT if a wait gave up) and arrival counters that
+ * every launch returns to zero; and the whole grid (ceil(max_ctx / 128) * n_kv_heads * n_seq CTAs) must fit on the GPU
+ * at once, else COBALT_EUNSUPPORTED is returned, nothing is launched and cobalt_attn_decode() is the way.  The reference
+ * runs attention as a phase of its cooperative megakernel (src/cobaltkernel/csrc/megakernel.cu:842-1150). */
+size_t cobalt_attn_decode_fused_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int max_ctx, int n_seq);
+int cobalt_attn_decode_fused(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions, void* scratch,
+                             size_t scratch_bytes, void* out, int n_heads, int n_kv_heads, int head_dim, int max_ctx,
+                             int window, float scale, int n_seq, int64_t cache_seq_stride, void* stream);
 
 /* All-reduce (sum) of the fp32 partial outputs of a row-parallel layer over peer memory, for tensor-parallel decode
  * (the reference has no distributed code; this replaces the NCCL all-reduce that would follow cobalt_linear_f32).

@@ -616,6 +616,62 @@ def test_attn_decode_matches_torch(nh, nkv, D, ctx, pos, window):
     assert float(d.abs().max()) <= 0.02 * float(ref.float().abs().max()), float(d.abs().max())
 
 
+@pytest.mark.parametrize("nh,nkv,D,ctx,positions,window", [(32, 8, 128, 2304, [2047], 0), (32, 8, 128, 300, [0], 0), (16, 16, 64, 512, [511], 0),
+                                                           (32, 16, 128, 1024, [700], 256), (8, 2, 128, 640, [5, 639, 130], 0),
+                                                           (8, 4, 64, 1024, [1000, 77], 200)])
+def test_attn_decode_one_kernel_equals_three(nh, nkv, D, ctx, positions, window):
+    """cobalt_attn_decode_fused (one cooperative kernel whose CTAs wait for each other's softmax statistics) gives the
+    bits of the three-kernel cobalt_attn_decode, for single sequences, batches and sliding windows; it leaves its
+    counters at zero (three calls in a row on one scratch) and its status word clean."""
+    import ctypes
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    B = len(positions)
+    g = torch.Generator(device="cpu").manual_seed(77 + nh + ctx)
+    q = torch.randn(B, nh * D, generator=g).to(torch.bfloat16).to(dev)
+    kc = torch.randn(B, nkv, ctx, D, generator=g).to(torch.bfloat16).to(dev)
+    vc = torch.randn(B, nkv, ctx, D, generator=g).to(torch.bfloat16).to(dev)
+    pos = torch.tensor(positions, dtype=torch.long, device=dev)
+    stride = nkv * ctx * D if B > 1 else 0
+    scale = float(D) ** -0.5
+    st = torch.cuda.current_stream().cuda_stream
+    need = lib.cobalt_attn_decode_scratch_bytes(nh, D, ctx) * B
+    scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+    want = torch.empty_like(q)
+    assert lib.cobalt_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), scratch.data_ptr(), need, want.data_ptr(),
+                                  nh, nkv, D, ctx, window, scale, B, stride, st) == 0
+    nf = lib.cobalt_attn_decode_fused_scratch_bytes(nh, nkv, D, ctx, B)
+    fs = torch.zeros(nf, dtype=torch.uint8, device=dev)
+    for rnd in range(3):
+        got = torch.zeros_like(q)
+        rc = lib.cobalt_attn_decode_fused(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), fs.data_ptr(), nf, got.data_ptr(),
+                                          nh, nkv, D, ctx, window, scale, B, stride, st)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), rnd
+    status = ctypes.c_uint32(0)
+    assert lib.cobalt_device_status(fs.data_ptr(), st, ctypes.byref(status)) == 0 and status.value == 0
+    assert int(fs[256:256 + B * nkv * 8].view(torch.int32).abs().sum()) == 0       # counters back at zero
+
+
+def test_attn_decode_one_kernel_refuses_grids_that_do_not_fit():
+    """The CTAs of the one-kernel attention wait for each other, so all of them must be resident: a grid beyond that is
+    refused (nothing launched) and the caller uses the three-kernel entry point."""
+    from cobalt_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    nh, nkv, D, ctx, B = 32, 16, 128, 8192, 4                     # 64 chunks x 16 KV heads x 4 sequences = 4096 CTAs
+    nf = lib.cobalt_attn_decode_fused_scratch_bytes(nh, nkv, D, ctx, B)
+    fs = torch.zeros(nf, dtype=torch.uint8, device=dev)
+    q = torch.zeros(B, nh * D, dtype=torch.bfloat16, device=dev)
+    kc = torch.zeros(B, nkv, ctx, D, dtype=torch.bfloat16, device=dev)
+    pos = torch.zeros(B, dtype=torch.long, device=dev)
+    rc = lib.cobalt_attn_decode_fused(q.data_ptr(), kc.data_ptr(), kc.data_ptr(), pos.data_ptr(), fs.data_ptr(), nf, q.data_ptr(),
+                                      nh, nkv, D, ctx, 0, 1.0, B, nkv * ctx * D, torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.EUNSUPPORTED
+
+
 @pytest.mark.gpu
 def test_attn_decode_batch_equals_single_sequences():
     """n_seq sequences in one call (own caches, own positions) give the bits of n_seq single-sequence calls."""

@@ -191,6 +191,23 @@ def test_folded_steps_equal_separate_kernels(family, batch):
     assert torch.equal(la, lb)
 
 
+def test_one_kernel_attention_equals_three_kernels_in_the_decoder():
+    """The decoder with the cooperative one-kernel attention switched on against the default three kernels: identical logits."""
+    from cobalt_b200.decoder import build_random_decoder
+    cfg = gemma_small(layers=2, vocab=1008)
+    qcfg = SparseQuantConfig(4, 0.5, 0.5)
+    dev = torch.device("cuda")
+    a = build_random_decoder(cfg, qcfg, 64, dev)
+    b = build_random_decoder(cfg, qcfg, 64, dev)
+    b.one_kernel_attention = True
+    g = torch.Generator().manual_seed(14)
+    prompt = torch.randint(0, 1000, (21,), generator=g)
+    ta, la = a.generate(prompt, 8, use_graph=True)
+    tb, lb = b.generate(prompt, 8, use_graph=True)
+    assert b.one_kernel_attention and b.att_fused is not None
+    assert torch.equal(ta, tb) and torch.equal(la, lb)
+
+
 def test_config3_one_layer_at_7b_width_against_cpu_oracle():
     """One block at the 7B widths (hidden 4096, 32/8 heads of 128, intermediate 14336, vocabulary 32000; 4-bit, 50 %)
     against the oracle on the CPU -- another device, another matmul library: a 64-token prefill within twice the
