@@ -666,6 +666,9 @@ def run_prefill(args):
     shapes = [("q", 4096, 4096), ("kv", 1024, 4096), ("gate_up", 14336, 4096), ("down", 4096, 14336)]
     if args.shapes:
         shapes = [t for t in shapes if t[0] in args.shapes.split(",")]
+    if args.probe_shape:                                     # one custom matrix, e.g. 128,512 = a single CTA with 8 stages
+        K, N = (int(v) for v in args.probe_shape.split(","))
+        shapes = [("probe", K, N)]
     Ms = [int(m) for m in args.prefill_m.split(",")]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     cases = []
@@ -831,6 +834,7 @@ def main():
     ap.add_argument("--head-bits", type=int, default=0, help="--workload model: compress the head with group-128 RTN at this width (0 = dense bf16)")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="--workload model: tokens of the timed prefill (0 = the whole context)")
     ap.add_argument("--prefill-m", default="128,512,2048")
+    ap.add_argument("--probe-shape", default="", help="--workload prefill: K,N of one custom matrix instead of the 7B shapes")
     ap.add_argument("--shapes", default="", help="comma-separated subset of q,k,v,o,gate,up,down (profiling aid)")
     ap.add_argument("--copies", type=int, default=0, help="block copies to rotate (0 = enough for 4 x L2)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
