@@ -37,6 +37,27 @@ def test_struct_layout_and_strerror(lib):
     assert b"invalid" in lib.cobalt_strerror(-1)
 
 
+def test_ctypes_mirrors_match_the_header(tmp_path):
+    """Sizes and field offsets of the ctypes mirrors against the C compiler's view of include/cobalt_b200.h."""
+    from cobalt_b200 import _lib
+    structs = {"CobaltMat": _lib.CobaltMat, "CobaltStagedInput": _lib.CobaltStagedInput, "CobaltPeerSlots": _lib.CobaltPeerSlots}
+    lines = []
+    for name, cls in structs.items():
+        lines.append(f'printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in cls._fields_:
+            lines.append(f'printf("{name}.{field} %zu\\n", offsetof({name}, {field}));')
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "cobalt_b200.h"\nint main(void) {\n' + "\n".join(lines) + "\nreturn 0; }\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout
+    seen = dict(line.split() for line in out.strip().splitlines())
+    for name, cls in structs.items():
+        assert int(seen[name]) == ctypes.sizeof(cls), name
+        for field, _ in cls._fields_:
+            assert int(seen[f"{name}.{field}"]) == getattr(cls, field).offset, f"{name}.{field}"
+
+
 def test_argument_validation_without_gpu(lib):
     """Host-side validation rejects bad descriptors before any CUDA call."""
     from cobalt_b200 import _lib
