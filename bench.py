@@ -486,7 +486,10 @@ def run_ours(args):
                         "tensor-parallel step through the module API: pinned host x in, fused launches, all-reduce of o and down, pinned host y out",
                 "h2d_bytes_per_step": int(sum(M * info[n]["N"] * 2 for n in names if n not in fused_of or fused_of[n][0] == n)),
                 "d2h_bytes_per_step": int(sum(M * v["K"] * 2 for v in info.values()))},
-        "gpu_launches": int(args.steps * launches_per_step),
+        # this library's kernels inside the timed region: the GEMVs, a fragment-ordering copy in front of each GEMV that
+        # cannot stage its activations (more than 8 tokens), and the peer all-reduce kernels of a tensor-parallel step
+        "gpu_launches": int(args.steps * (launches_per_step * (2 if M > 8 else 1) +
+                                          (len([n for n in names if n in ROW_PARALLEL]) if (world > 1 and reducer is not None) else 0))),
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(value / world / peak, 4),
                      # DRAM bytes per launch: 1.005 x algorithmic, from an ncu capture of the gate projection
